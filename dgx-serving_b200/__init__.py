@@ -1,0 +1,182 @@
+"""Host-side Python binding of libw4a8_b200.so, the B200 (sm_100a) W4A8 quantized-matmul library.
+
+The product is the C-ABI shared library (include/w4a8_b200.h) plus the C++ shim launchers in
+kernels/*.cuh that carry the reference's launcher names.  This module is the thin ctypes layer the
+tests and the benchmark use to call that ABI with torch tensors as device memory; torch is plumbing
+(allocation, streams, torch.distributed), never a compute path.  There is no CPU or torch fallback:
+if the library is missing or the device is not sm_100 every call raises.
+
+Function names and argument order mirror the reference launchers
+(kernels/quantize_x.cuh:41, kernels/gemv_w4a8.cuh:155,168, kernels/gemm_batch.cuh:228,
+kernels/gemm_mmq.cuh:230, kernels/gemm_mmq_raster.cuh:115).
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libw4a8_b200.so")
+QBLK = 32
+
+OK, ERR_ARG, ERR_ALIGN, ERR_CUDA, ERR_IO, ERR_DEVICE, ERR_UNSUPPORTED, ERR_WORKSPACE = range(8)
+
+_lib = None
+
+
+class W4A8Error(RuntimeError):
+    def __init__(self, code, text):
+        super().__init__("w4a8 error %d: %s" % (code, text))
+        self.code = code
+
+
+class QMat(ctypes.Structure):
+    """Mirror of w4a8_qmat (the N-sharded form of the reference's QMat, runtime/weights_qwen.h:8)."""
+    _fields_ = [("wq", ctypes.c_void_p), ("sc", ctypes.c_void_p), ("row0", ctypes.c_int64),
+                ("rows", ctypes.c_int64), ("N", ctypes.c_int64), ("K", ctypes.c_int64),
+                ("scale_dtype", ctypes.c_int)]
+
+
+_P, _I, _Z, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t, ctypes.c_int64
+_SIGNATURES = {
+    "w4a8_version": (_I, []),
+    "w4a8_last_error": (ctypes.c_char_p, []),
+    "w4a8_device_status": (_I, [ctypes.POINTER(ctypes.c_uint32)]),
+    "w4a8_quantize_x_q8": (_I, [_P, _P, _P, _P, _I, _I, _P]),
+    "w4a8_gemv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "w4a8_gemm": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "w4a8_gemm_splitk_workspace_bytes": (_Z, [_I, _I, _I, _I]),
+    "w4a8_gemm_splitk": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _Z, _P]),
+    "w4a8_group_dots": (_I, [_P, _P, _P, _I, _I, _I, _I, _P]),
+    "w4a8_linear": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "w4a8_moe_gemv": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P]),
+    "w4a8_shard_rows": (_I, [_L, _I, _I, ctypes.POINTER(_L), ctypes.POINTER(_L)]),
+    "w4a8_load_qmat_shard": (_I, [ctypes.c_char_p, ctypes.c_char_p, _L, _L, _I, _I, _I, ctypes.POINTER(QMat)]),
+    "w4a8_upload_qmat_shard": (_I, [_P, _P, _L, _L, _I, _I, _I, ctypes.POINTER(QMat)]),
+    "w4a8_free_qmat": (_I, [ctypes.POINTER(QMat)]),
+}
+EXPORTS = tuple(_SIGNATURES)
+
+
+def lib():
+    """Loads the C-ABI library (once).  Raises if it has not been built: there is no fallback."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError("%s not built; run python dgx-serving_b200/build.py (needs nvcc). "
+                               "This library has no CPU or PyTorch fallback." % LIB_PATH)
+        l = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(l, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = l
+    return _lib
+
+
+def _check(rc):
+    if rc != OK:
+        raise W4A8Error(rc, lib().w4a8_last_error().decode())
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    return t.data_ptr()
+
+
+def _stream(stream):
+    if stream is None:
+        import torch
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream
+
+
+def device_status():
+    """Synchronises and raises if a kernel recorded a device-side error (a bounded wait ran out)."""
+    d = ctypes.c_uint32(0)
+    _check(lib().w4a8_device_status(ctypes.byref(d)))
+
+
+def launch_quantize_x_q8(X, xq, xs, xsum, IN, S, stream=None):
+    _check(lib().w4a8_quantize_x_q8(_ptr(X), _ptr(xq), _ptr(xs), _ptr(xsum), IN, S, _stream(stream)))
+
+
+def launch_gemv_w4a8(xq, xs, xsum, Wq, sw, Y, IN, OUT, S, scale_dtype=0, stream=None):
+    """xsum is accepted and ignored, as in the reference (kernels/gemv_w4a8.cuh:23-25)."""
+    _check(lib().w4a8_gemv(_ptr(xq), _ptr(xs), _ptr(Wq), _ptr(sw), _ptr(Y), IN, OUT, S, scale_dtype, _stream(stream)))
+
+
+def launch_gemv_w4a8_sb(xq, xs, Wq, sw, Y, IN, OUT, S, scale_dtype=0, stream=None):
+    _check(lib().w4a8_gemv(_ptr(xq), _ptr(xs), _ptr(Wq), _ptr(sw), _ptr(Y), IN, OUT, S, scale_dtype, _stream(stream)))
+
+
+launch_gemv_w4a8_mlp = launch_gemv_w4a8_mlp_auto = launch_gemv_w4a8_g4 = launch_gemv_w4a8
+launch_gemv_w4a8_sb_g4 = launch_gemv_w4a8_sb
+
+
+def launch_gemm_batch_w4a8(xq, xs, Wq, sw, Y, IN, OUT, B, scale_dtype=0, stream=None):
+    _check(lib().w4a8_gemv(_ptr(xq), _ptr(xs), _ptr(Wq), _ptr(sw), _ptr(Y), IN, OUT, B, scale_dtype, _stream(stream)))
+
+
+def launch_gemm_mmq_w4a8(X, xs, Wq, sw, Y, M, N, K, scale_dtype=0, stream=None):
+    _check(lib().w4a8_gemm(_ptr(X), _ptr(xs), _ptr(Wq), _ptr(sw), _ptr(Y), M, N, K, scale_dtype, _stream(stream)))
+
+
+launch_gemm_mmq_w4a8_auto = launch_gemm_mma_w4a8 = launch_gemm_mmq_w4a8
+
+
+def launch_gemm_mmq_raster_w4a8(X, xs, Wq, sw, Y, M, N, K, scale_dtype, raster, group, stream=None):
+    """raster/group only re-order tiles in the reference (kernels/gemm_mmq_raster.cuh:16-27); results are equal."""
+    launch_gemm_mmq_w4a8(X, xs, Wq, sw, Y, M, N, K, scale_dtype, stream)
+
+
+def gemm_splitk_workspace_bytes(M, N, K, splitk=0):
+    return int(lib().w4a8_gemm_splitk_workspace_bytes(M, N, K, splitk))
+
+
+def launch_gemm_bm16_splitk(X, xs, Wq, sw, Y, M, N, K, scale_dtype=0, splitk=0, workspace=None, stream=None):
+    nbytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    _check(lib().w4a8_gemm_splitk(_ptr(X), _ptr(xs), _ptr(Wq), _ptr(sw), _ptr(Y), M, N, K, scale_dtype, splitk,
+                                  _ptr(workspace), nbytes, _stream(stream)))
+
+
+def group_dots(xq, Wq, D, M, N, K, path=0, stream=None):
+    _check(lib().w4a8_group_dots(_ptr(xq), _ptr(Wq), _ptr(D), M, N, K, path, _stream(stream)))
+
+
+def linear(X, xq, xs, xsum, Wq, sw, Y, S, N, K, scale_dtype=0, skip_quantize=0, stream=None):
+    """The mm() dispatcher of the model graphs (models/qwen35_decode.cu:51-62)."""
+    _check(lib().w4a8_linear(_ptr(X), _ptr(xq), _ptr(xs), _ptr(xsum), _ptr(Wq), _ptr(sw), _ptr(Y), S, N, K,
+                             scale_dtype, skip_quantize, _stream(stream)))
+
+
+def moe_gemv(xq, xs, Wq, sw, idx, Y, nslots, topk, x_per_slot, N, K, num_experts, scale_dtype=0, stream=None):
+    _check(lib().w4a8_moe_gemv(_ptr(xq), _ptr(xs), _ptr(Wq), _ptr(sw), _ptr(idx), _ptr(Y), nslots, topk, x_per_slot,
+                               N, K, num_experts, scale_dtype, _stream(stream)))
+
+
+def shard_rows(N, rank, world):
+    r0, rows = _L(0), _L(0)
+    _check(lib().w4a8_shard_rows(N, rank, world, ctypes.byref(r0), ctypes.byref(rows)))
+    return r0.value, rows.value
+
+
+def load_qmat_shard(q4_path, scale_path, N, K, scale_dtype, rank, world):
+    m = QMat()
+    _check(lib().w4a8_load_qmat_shard(os.fsencode(q4_path), os.fsencode(scale_path), N, K, scale_dtype, rank, world,
+                                      ctypes.byref(m)))
+    return m
+
+
+def upload_qmat_shard(host_wq, host_sc, N, K, scale_dtype, rank, world):
+    """host_wq / host_sc: numpy arrays (or anything with .ctypes) holding the full [N] tensors."""
+    m = QMat()
+    _check(lib().w4a8_upload_qmat_shard(host_wq.ctypes.data, host_sc.ctypes.data, N, K, scale_dtype, rank, world,
+                                        ctypes.byref(m)))
+    return m
+
+
+def free_qmat(m):
+    _check(lib().w4a8_free_qmat(ctypes.byref(m)))

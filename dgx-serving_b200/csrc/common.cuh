@@ -1,0 +1,77 @@
+// Shared host/device helpers of the W4A8 library (sm_100a only).
+#pragma once
+#include <cstdint>
+#include <cstdio>
+#include <cstdarg>
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include "../../include/w4a8_b200.h"
+
+#define W4A8_API extern "C" __attribute__((visibility("default")))
+
+namespace w4a8 {
+
+constexpr int QBLK = W4A8_QBLK;
+
+// ---- host-side error text ----------------------------------------------------------------------
+char *err_buf();  // thread-local 512-byte buffer (api.cu)
+inline int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(err_buf(), 512, fmt, ap);
+    va_end(ap);
+    return code;
+}
+inline int cuda_fail(cudaError_t e, const char *what) {
+    return fail(W4A8_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+// After a kernel launch: reports launch-configuration errors without synchronising.
+inline int launch_status(const char *what) {
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) { cudaGetLastError(); return cuda_fail(e, what); }
+    return W4A8_OK;
+}
+inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+// Number of SMs of the current device (148 on B200), cached per device.
+int sm_count();
+// W4A8_OK if the current device is compute capability 10.x, else W4A8_ERR_UNSUPPORTED.
+int require_sm100();
+
+// ---- device-side error word (set when a bounded wait runs out) ---------------------------------
+__device__ unsigned int g_dev_error = 0u;  // one translation unit: w4a8_b200.cu includes every kernel file
+__device__ __forceinline__ void dev_set_error(unsigned int code) { atomicCAS(&g_dev_error, 0u, code); }
+
+#ifdef __CUDACC__
+// ---- weight scale read: float, or __half widened (reference: kernels/qscale.cuh:5-6) -----------
+__device__ __forceinline__ float sval(float x) { return x; }
+__device__ __forceinline__ float sval(__half x) { return __half2float(x); }
+
+// ---- int4 -> int8 expansion ------------------------------------------------------------------
+// One 32-bit word of packed weights holds 8 nibbles: byte j = element 2j (low) and 2j+1 (high).
+// Instead of (nibble - 8) the expansion produces 16*(nibble - 8) in each int8 byte: XOR with 8
+// turns the nibble into the 4-bit two's-complement code of (nibble - 8), and a nibble sitting in
+// the HIGH half of a byte with a zero low half is that value times 16.  Integer dot products are
+// then 16x the true ones (still exact: |16*D| <= 520,192) and the factor 1/16 is folded into the
+// fp32 scale, where it is exact.  Cost: 3 logic ops per 8 weights, no per-byte subtraction.
+//   even: bytes = 16*w[0], 16*w[2], 16*w[4], 16*w[6]   (the word's low nibbles)
+//   odd : bytes = 16*w[1], 16*w[3], 16*w[5], 16*w[7]   (the word's high nibbles)
+__device__ __forceinline__ void unpack8_x16(uint32_t w, uint32_t &even, uint32_t &odd) {
+    odd = (w & 0xF0F0F0F0u) ^ 0x80808080u;
+    even = ((w << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
+}
+// The same 8 weights in element order (for tensor-core operands): lo = 16*w[0..3], hi = 16*w[4..7].
+__device__ __forceinline__ void unpack8_x16_seq(uint32_t w, uint32_t &lo, uint32_t &hi) {
+    uint32_t even, odd;
+    unpack8_x16(w, even, odd);
+    lo = __byte_perm(even, odd, 0x5140);  // e0 o0 e1 o1
+    hi = __byte_perm(even, odd, 0x7362);  // e2 o2 e3 o3
+}
+// Activation bytes x[0..7] (two words) split the same way: even = x0 x2 x4 x6, odd = x1 x3 x5 x7.
+__device__ __forceinline__ void split_even_odd(uint32_t x0, uint32_t x1, uint32_t &even, uint32_t &odd) {
+    even = __byte_perm(x0, x1, 0x6420);
+    odd = __byte_perm(x0, x1, 0x7531);
+}
+#endif
+
+}  // namespace w4a8

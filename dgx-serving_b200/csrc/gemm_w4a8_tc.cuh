@@ -1,0 +1,419 @@
+// W4A8 prefill / verify GEMM for sm_100a on the 5th-generation tensor cores.
+//   Y[m,n] = sum_b ((float)D[m,n,b] * xs[m,b]) * sw[n,b],   D[m,n,b] = sum_{k in group b} X[m,k]*(Wq[n,k]-8)
+// Semantics and fp32 evaluation order of the reference's kernels/gemm_mmq.cuh:38-120 (t = (float)c*xs,
+// acc = fma(t, sw, acc), groups ascending, :104-105), shared by gemm_mma.cuh, gemm_mmq_tmpl.cuh,
+// gemm_mmq_raster.cuh and gemm_mmq_ms.cuh.  Because both operands carry a scale per 32-element group,
+// the tensor core can only produce ONE group's int32 dot per MMA (K = 32); the scaling and the sum over
+// groups run on the CUDA cores, and that epilogue — three lane-operations per (m,n,group) — bounds the
+// kernel, not the MMA rate.
+//
+// Persistent kernel, one CTA per SM, 128x128 output tile per step, warp-specialised:
+//   warp 0      TMA producer: int8 activations [128 x 128 B] (128-byte swizzle) and packed int4 weights
+//               [128 x 64 B] per K-tile of 128 elements, each behind its own mbarrier ring
+//   warp 1      MMA issuer: one tcgen05.mma kind::i8 (128x128x32) per group into one of four 128-column
+//               accumulator buffers in tensor memory; tcgen05.commit signals operand release / result ready
+//   warps 2-5   expand int4 -> int8 (as 16*(w-8), see unpack8_x16) from the packed stage into the swizzled
+//               K-major operand stage the MMA reads (generic-proxy writes + fence.proxy.async), and stage
+//               the weight scales of the K-tile (pre-multiplied by the exact 1/16) transposed to [group][n]
+//   warps 6-13  epilogue: tcgen05.ld the int32 group dots (lane = row, 64 columns per warp), convert,
+//               scale and accumulate in registers; store the fp32 tile at the end of the K loop
+// Ragged M, N and a last partial K-tile are handled by TMA zero fill plus guards on scales and stores.
+#pragma once
+#include <cuda.h>
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace w4a8 {
+namespace gemm {
+
+constexpr int BM = 128, BN = 128, KT = 128;
+constexpr int GPK = KT / QBLK;  // groups (MMAs) per K-tile = 4
+constexpr int SA = 4;           // activation stages
+constexpr int SB = 4;           // packed-weight stages
+constexpr int S8 = 3;           // expanded-weight stages
+constexpr int SS = 4;           // weight-scale stages
+constexpr int TB = 4;           // TMEM accumulator buffers (TB * BN = 512 columns = all of tensor memory)
+constexpr int A_STAGE = BM * KT;       // 16 KB
+constexpr int BP_STAGE = BN * KT / 2;  // 8 KB
+constexpr int B8_STAGE = BN * KT;      // 16 KB
+constexpr int SW_STAGE = GPK * BN * 4; // 2 KB
+constexpr int DEQ_WARPS = 4, EPI_WARPS = 8;
+constexpr int THREADS = (2 + DEQ_WARPS + EPI_WARPS) * 32;  // 448
+constexpr int OFF_A = 0;
+constexpr int OFF_B8 = OFF_A + SA * A_STAGE;
+constexpr int OFF_BP = OFF_B8 + S8 * B8_STAGE;
+constexpr int OFF_SW = OFF_BP + SB * BP_STAGE;
+constexpr int OFF_BAR = OFF_SW + SS * SW_STAGE;
+constexpr int NUM_BARS = 2 * (SA + SB + S8 + SS + TB);
+constexpr int OFF_TMEM = OFF_BAR + NUM_BARS * 8;
+constexpr int SMEM_BYTES = OFF_TMEM + 16 + 1024;  // + slack to align the base to 1024 B
+
+// Device error codes (w4a8_device_status detail): 0x100 | role << 4 | which wait.
+enum : unsigned { ERR_PRODUCER = 0x110, ERR_MMA = 0x120, ERR_DEQUANT = 0x130, ERR_EPILOGUE = 0x140 };
+
+struct Ring {
+    int stage = 0;
+    uint32_t phase = 0;
+    const int depth;
+    __device__ explicit Ring(int d) : depth(d) {}
+    __device__ __forceinline__ void advance() {
+        if (++stage == depth) { stage = 0; phase ^= 1u; }
+    }
+};
+
+// One unit of work = (output tile, K split).  Tiles are numbered M-fastest so that CTAs running at the
+// same time share weight tiles in L2; split s covers groups [s*gsplit, min(nb, (s+1)*gsplit)).
+struct Work {
+    int m0, n0, g0, g1, nkt, split;
+};
+__device__ __forceinline__ Work decode_work(int w, int m_tiles, int num_tiles, int nb, int gsplit) {
+    Work k;
+    const int tile = w % num_tiles;
+    k.split = w / num_tiles;
+    k.m0 = (tile % m_tiles) * BM;
+    k.n0 = (tile / m_tiles) * BN;
+    k.g0 = k.split * gsplit;
+    k.g1 = min(nb, k.g0 + gsplit);
+    const int ng = max(0, k.g1 - k.g0);
+    k.nkt = (ng + GPK - 1) / GPK;
+    return k;
+}
+
+template <typename ST, bool DUMP>
+__global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
+    const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+    const float *__restrict__ xs, const ST *__restrict__ sw, float *__restrict__ Y, int32_t *__restrict__ Dout,
+    int M, int N, int K, int nsplit, int gsplit) {
+    extern __shared__ unsigned char smem_dyn[];
+    const uint32_t raw = ptx::smem_u32(smem_dyn);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char *base_ptr = smem_dyn + (base - raw);
+
+    const uint32_t bar0 = base + OFF_BAR;
+    auto BAR = [&](int idx) { return bar0 + 8u * idx; };
+    // barrier index map
+    constexpr int A_FULL = 0, A_EMPTY = A_FULL + SA, BP_FULL = A_EMPTY + SA, BP_EMPTY = BP_FULL + SB,
+                  B8_FULL = BP_EMPTY + SB, B8_EMPTY = B8_FULL + S8, SW_FULL = B8_EMPTY + S8, SW_EMPTY = SW_FULL + SS,
+                  TM_FULL = SW_EMPTY + SS, TM_EMPTY = TM_FULL + TB;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + OFF_TMEM);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nb = K / QBLK;
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+    const int num_tiles = m_tiles * n_tiles;
+    const int num_work = num_tiles * nsplit;
+
+    if (tid == 0) {
+        for (int i = 0; i < SA; i++) { ptx::mbar_init(BAR(A_FULL + i), 1); ptx::mbar_init(BAR(A_EMPTY + i), 1); }
+        for (int i = 0; i < SB; i++) { ptx::mbar_init(BAR(BP_FULL + i), 1); ptx::mbar_init(BAR(BP_EMPTY + i), DEQ_WARPS); }
+        for (int i = 0; i < S8; i++) { ptx::mbar_init(BAR(B8_FULL + i), DEQ_WARPS); ptx::mbar_init(BAR(B8_EMPTY + i), 1); }
+        for (int i = 0; i < SS; i++) { ptx::mbar_init(BAR(SW_FULL + i), DEQ_WARPS); ptx::mbar_init(BAR(SW_EMPTY + i), EPI_WARPS); }
+        for (int i = 0; i < TB; i++) { ptx::mbar_init(BAR(TM_FULL + i), 1); ptx::mbar_init(BAR(TM_EMPTY + i), EPI_WARPS); }
+        ptx::mbar_fence_init();
+        ptx::tma_prefetch_desc(&tmA);
+        ptx::tma_prefetch_desc(&tmB);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t *>(tmem_slot)), TB * BN);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            Ring ra(SA), rb(SB);
+            bool ok = true;
+            for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
+                const Work wk = decode_work(wi, m_tiles, num_tiles, nb, gsplit);
+                const int m0 = wk.m0, n0 = wk.n0;
+                for (int kt = 0; kt < wk.nkt && ok; kt++) {
+                    const int kbyte = (wk.g0 + kt * GPK) * QBLK;   // first K element of this K-tile (multiple of 32)
+                    if (!ptx::mbar_wait(BAR(A_EMPTY + ra.stage), ra.phase ^ 1u)) { dev_set_error(ERR_PRODUCER | 1); ok = false; break; }
+                    ptx::mbar_arrive_expect_tx(BAR(A_FULL + ra.stage), A_STAGE);
+                    ptx::tma_load_2d(base + OFF_A + ra.stage * A_STAGE, &tmA, kbyte, m0, BAR(A_FULL + ra.stage));
+                    ra.advance();
+                    if (!ptx::mbar_wait(BAR(BP_EMPTY + rb.stage), rb.phase ^ 1u)) { dev_set_error(ERR_PRODUCER | 2); ok = false; break; }
+                    ptx::mbar_arrive_expect_tx(BAR(BP_FULL + rb.stage), BP_STAGE);
+                    ptx::tma_load_2d(base + OFF_BP + rb.stage * BP_STAGE, &tmB, kbyte / 2, n0, BAR(BP_FULL + rb.stage));
+                    rb.advance();
+                }
+            }
+            if (!ok) {  // give copies already in flight time to land before the CTA's shared memory goes away
+                const long long t0 = clock64();
+                while (clock64() - t0 < (1ll << 21)) { }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            Ring ra(SA), r8(S8), rt(TB);
+            const uint32_t idesc = ptx::umma_idesc_s8(BM, BN);
+            bool ok = true;
+            for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
+                const Work wk = decode_work(wi, m_tiles, num_tiles, nb, gsplit);
+                for (int kt = 0; kt < wk.nkt && ok; kt++) {
+                    if (!ptx::mbar_wait(BAR(A_FULL + ra.stage), ra.phase)) { dev_set_error(ERR_MMA | 1); ok = false; break; }
+                    if (!ptx::mbar_wait(BAR(B8_FULL + r8.stage), r8.phase)) { dev_set_error(ERR_MMA | 2); ok = false; break; }
+                    ptx::tc_fence_after_sync();
+                    const uint64_t adesc = ptx::umma_desc_k_sw128(base + OFF_A + ra.stage * A_STAGE);
+                    const uint64_t bdesc = ptx::umma_desc_k_sw128(base + OFF_B8 + r8.stage * B8_STAGE);
+                    const int ng = min(GPK, wk.g1 - (wk.g0 + kt * GPK));
+                    for (int g = 0; g < ng; g++) {
+                        if (!ptx::mbar_wait(BAR(TM_EMPTY + rt.stage), rt.phase ^ 1u)) { dev_set_error(ERR_MMA | 3); ok = false; break; }
+                        ptx::tc_fence_after_sync();
+                        // group g = bytes [32g, 32g+32) of every 128-byte operand row: advance the start address
+                        ptx::umma_i8(tmem_base + rt.stage * BN, adesc + (uint64_t)(g * 2), bdesc + (uint64_t)(g * 2), idesc, 0u);
+                        ptx::umma_commit(BAR(TM_FULL + rt.stage));
+                        rt.advance();
+                    }
+                    ptx::umma_commit(BAR(A_EMPTY + ra.stage));
+                    ptx::umma_commit(BAR(B8_EMPTY + r8.stage));
+                    ra.advance();
+                    r8.advance();
+                }
+            }
+        }
+    } else if (warp < 2 + DEQ_WARPS) {
+        // ---------------- int4 -> int8 expansion + weight-scale staging ----------------
+        const int dt = tid - 64;  // 0..127
+        Ring rb(SB), r8(S8), rs(SS);
+        bool ok = true;
+        for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
+            const Work wk = decode_work(wi, m_tiles, num_tiles, nb, gsplit);
+            const int n0 = wk.n0;
+            for (int kt = 0; kt < wk.nkt && ok; kt++) {
+                bool w = ptx::mbar_wait(BAR(BP_FULL + rb.stage), rb.phase) && ptx::mbar_wait(BAR(B8_EMPTY + r8.stage), r8.phase ^ 1u);
+                if (!__all_sync(0xffffffffu, w)) { dev_set_error(ERR_DEQUANT | 1); ok = false; break; }
+                const unsigned char *src = base_ptr + OFF_BP + rb.stage * BP_STAGE;
+                unsigned char *dst = base_ptr + OFF_B8 + r8.stage * B8_STAGE;
+#pragma unroll
+                for (int i = 0; i < (BN * 8) / (DEQ_WARPS * 32); i++) {
+                    const int j = dt + i * DEQ_WARPS * 32;
+                    const int n = j >> 3, c = j & 7;  // row n, 8 packed bytes = 16 weights = one 16-byte chunk
+                    const uint2 p = *reinterpret_cast<const uint2 *>(src + n * (KT / 2) + c * 8);
+                    uint4 o;
+                    unpack8_x16_seq(p.x, o.x, o.y);
+                    unpack8_x16_seq(p.y, o.z, o.w);
+                    *reinterpret_cast<uint4 *>(dst + n * KT + ((c ^ (n & 7)) << 4)) = o;
+                }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) { ptx::mbar_arrive(BAR(B8_FULL + r8.stage)); ptx::mbar_arrive(BAR(BP_EMPTY + rb.stage)); }
+                rb.advance();
+                r8.advance();
+
+                w = ptx::mbar_wait(BAR(SW_EMPTY + rs.stage), rs.phase ^ 1u);
+                if (!__all_sync(0xffffffffu, w)) { dev_set_error(ERR_DEQUANT | 2); ok = false; break; }
+                float *ssw = reinterpret_cast<float *>(base_ptr + OFF_SW + rs.stage * SW_STAGE);
+                const int n = n0 + dt;
+#pragma unroll
+                for (int g = 0; g < GPK; g++) {
+                    const int b = wk.g0 + kt * GPK + g;
+                    float v = 0.f;
+                    if (!DUMP && n < N && b < wk.g1) v = sval(sw[(size_t)n * nb + b]) * 0.0625f;  // exact: undoes the 16x of the expansion
+                    ssw[g * BN + dt] = v;
+                }
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(BAR(SW_FULL + rs.stage));
+                rs.advance();
+            }
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int ew = warp - (2 + DEQ_WARPS);  // 0..7
+        const int quad = warp & 3;              // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
+        const int half = ew >> 2;               // columns [64*half, 64*half+64)
+        Ring rs(SS), rt(TB);
+        bool ok = true;
+        for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
+            const Work wk = decode_work(wi, m_tiles, num_tiles, nb, gsplit);
+            const int m0 = wk.m0, n0 = wk.n0;
+            const int m = m0 + quad * 32 + lane;
+            // a warp whose 32 rows all lie beyond M only keeps the barriers moving
+            const bool rows_live = (m0 + quad * 32) < M;
+            const float *xsrow = xs + (size_t)(m < M ? m : 0) * nb;
+            float acc[64];
+#pragma unroll
+            for (int j = 0; j < 64; j++) acc[j] = 0.f;
+            float xnext[GPK];
+#pragma unroll
+            for (int g = 0; g < GPK; g++) xnext[g] = (!DUMP && m < M && wk.g0 + g < wk.g1) ? xsrow[wk.g0 + g] : 0.f;
+            for (int kt = 0; kt < wk.nkt && ok; kt++) {
+                float xcur[GPK];
+#pragma unroll
+                for (int g = 0; g < GPK; g++) {
+                    xcur[g] = xnext[g];
+                    const int b = wk.g0 + (kt + 1) * GPK + g;
+                    xnext[g] = (!DUMP && m < M && b < wk.g1) ? xsrow[b] : 0.f;
+                }
+                bool w = ptx::mbar_wait(BAR(SW_FULL + rs.stage), rs.phase);
+                if (!__all_sync(0xffffffffu, w)) { dev_set_error(ERR_EPILOGUE | 1); ok = false; break; }
+                const float *ssw = reinterpret_cast<const float *>(base_ptr + OFF_SW + rs.stage * SW_STAGE) + half * 64;
+                const int ng = min(GPK, wk.g1 - (wk.g0 + kt * GPK));
+#pragma unroll
+                for (int g = 0; g < GPK; g++) {
+                    if (g < ng) {
+                        w = ptx::mbar_wait(BAR(TM_FULL + rt.stage), rt.phase);
+                        if (!__all_sync(0xffffffffu, w)) { dev_set_error(ERR_EPILOGUE | 2); ok = false; break; }
+                        ptx::tc_fence_after_sync();
+                        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + rt.stage * BN + half * 64;
+                        const float x = xcur[g];
+                        if (!rows_live) {
+                            ptx::tc_fence_before_sync();
+                            __syncwarp();
+                            if (lane == 0) ptx::mbar_arrive(BAR(TM_EMPTY + rt.stage));
+                        } else {
+#pragma unroll
+                        for (int c = 0; c < 2; c++) {
+                            uint32_t d[32];
+                            ptx::tmem_ld_32x32b_x32(taddr + c * 32, d);
+                            ptx::tmem_ld_wait();
+                            if (c == 1) {  // both halves are in registers: the buffer may be overwritten
+                                ptx::tc_fence_before_sync();
+                                __syncwarp();
+                                if (lane == 0) ptx::mbar_arrive(BAR(TM_EMPTY + rt.stage));
+                            }
+                            if (DUMP) {
+                                if (m < M) {
+                                    const int b = wk.g0 + kt * GPK + g;
+#pragma unroll
+                                    for (int j = 0; j < 32; j++) {
+                                        const int n = n0 + half * 64 + c * 32 + j;
+                                        if (n < N) Dout[((size_t)m * N + n) * nb + b] = ((int)d[j]) >> 4;
+                                    }
+                                }
+                            } else {
+#pragma unroll
+                                for (int j4 = 0; j4 < 8; j4++) {
+                                    const float4 s4 = *reinterpret_cast<const float4 *>(ssw + g * BN + c * 32 + j4 * 4);
+                                    const int j = c * 32 + j4 * 4;
+                                    float t0 = __int2float_rn((int)d[j4 * 4 + 0]) * x;
+                                    float t1 = __int2float_rn((int)d[j4 * 4 + 1]) * x;
+                                    float t2 = __int2float_rn((int)d[j4 * 4 + 2]) * x;
+                                    float t3 = __int2float_rn((int)d[j4 * 4 + 3]) * x;
+                                    acc[j + 0] = fmaf(t0, s4.x, acc[j + 0]);
+                                    acc[j + 1] = fmaf(t1, s4.y, acc[j + 1]);
+                                    acc[j + 2] = fmaf(t2, s4.z, acc[j + 2]);
+                                    acc[j + 3] = fmaf(t3, s4.w, acc[j + 3]);
+                                }
+                            }
+                        }
+                        }
+                        rt.advance();
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(BAR(SW_EMPTY + rs.stage));
+                rs.advance();
+            }
+            if (!DUMP && ok && m < M) {
+                float *yrow = Y + (size_t)wk.split * ((size_t)M * N) + (size_t)m * N + n0 + half * 64;
+                const int nleft = N - (n0 + half * 64);
+                if (nleft >= 64 && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0)) {
+#pragma unroll
+                    for (int j = 0; j < 64; j += 4)
+                        *reinterpret_cast<float4 *>(yrow + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 64; j++)
+                        if (j < nleft) yrow[j] = acc[j];
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, TB * BN);
+    }
+}
+
+// Adds the split-K partial sums in ascending split order (the order of the reference's
+// reduce_splitk_kernel, kernels/gemm_mmq.cuh:201-204): Y[i] = ((0 + P0[i]) + P1[i]) + ...
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ P, float *__restrict__ Y, long MN, int nsplit) {
+    const long stride = (long)gridDim.x * blockDim.x;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < MN; i += stride) {
+        float s = 0.f;
+        for (int sp = 0; sp < nsplit; sp++) s += P[(size_t)sp * MN + i];
+        Y[i] = s;
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D byte tensor [rows][row_bytes] (pitch = row_bytes), box [box_rows][box_bytes].
+inline int make_tmap_u8(CUtensorMap *tm, const void *ptr, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes,
+                        uint32_t box_rows, CUtensorMapSwizzle swz) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(W4A8_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    cuuint64_t dims[2] = {row_bytes, rows};
+    cuuint64_t strides[1] = {row_bytes};
+    cuuint32_t box[2] = {box_bytes, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(W4A8_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d)", (int)r);
+    return W4A8_OK;
+}
+
+template <typename ST, bool DUMP>
+inline int launch_tc_t(const int8_t *X, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int32_t *D,
+                       int M, int N, int K, int nsplit, int gsplit, cudaStream_t st) {
+    CUtensorMap tmA, tmB;
+    int rc = make_tmap_u8(&tmA, X, (uint64_t)K, (uint64_t)M, KT, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != W4A8_OK) return rc;
+    rc = make_tmap_u8(&tmB, Wq, (uint64_t)K / 2, (uint64_t)N, KT / 2, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc != W4A8_OK) return rc;
+    auto kern = gemm_w4a8_tc_kernel<ST, DUMP>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return cuda_fail(e, "gemm smem opt-in");
+        configured = true;
+    }
+    const long tiles = (long)((M + BM - 1) / BM) * ((N + BN - 1) / BN) * nsplit;
+    const int sms = sm_count();
+    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, xs, sw, Y, D, M, N, K, nsplit, gsplit);
+    return launch_status("gemm_w4a8_tc");
+}
+
+// Needs X and Wq 16-byte aligned (TMA global address rule); the caller checks.
+// nsplit = 1: Y is the output.  nsplit > 1: Y is the [nsplit][M][N] partial-sum workspace and gsplit the
+// number of groups per split.
+inline int launch_tc(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int M, int N, int K,
+                     int scale_dtype, int nsplit, int gsplit, cudaStream_t st) {
+    if (scale_dtype == 1)
+        return launch_tc_t<__half, false>(X, xs, Wq, (const __half *)sw, Y, nullptr, M, N, K, nsplit, gsplit, st);
+    return launch_tc_t<float, false>(X, xs, Wq, (const float *)sw, Y, nullptr, M, N, K, nsplit, gsplit, st);
+}
+inline int launch_tc_dump(const int8_t *X, const uint8_t *Wq, int32_t *D, int M, int N, int K, cudaStream_t st) {
+    return launch_tc_t<float, true>(X, nullptr, Wq, (const float *)nullptr, nullptr, D, M, N, K, 1, K / QBLK, st);
+}
+
+}  // namespace gemm
+}  // namespace w4a8

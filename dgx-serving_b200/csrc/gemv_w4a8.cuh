@@ -1,0 +1,225 @@
+// W4A8 decode GEMV family for sm_100a: Y[s,o] = sum_b xs[s,b]*sw[o,b] * D[s,o,b],
+// D[s,o,b] = sum_{k in group b} xq[s,k] * (Wq[o,k] - 8), the semantics of the reference's
+// kernels/gemv_w4a8.cuh:24-49 (plain), :54-110 (mlp), :119-151 (SB), :182-347 (g4) and
+// kernels/gemm_batch.cuh:177-231 (batch).  HBM-bound: the packed weights and their scales are read
+// exactly once per launch for all S rows.
+//
+// Work layout.  One quantization group (32 int4 = 16 bytes) is one 128-bit load.  A warp owns one
+// output row o; lane l owns groups b = l, l+32, l+64, ... so each warp-wide load covers 512 contiguous
+// bytes of the row.  The lane computes the whole 32-element integer dot of its group (8 dp4a per
+// activation row), converts it once and scales it with xs[s,b]*sw[o,b].
+//
+// fp32 evaluation order (fixed, independent of S and of which kernel variant runs):
+//   chain c = b mod 32:  acc_c = fma(xs[s,b]*sw[o,b], (float)D[s,o,b], acc_c), b = c, c+32, ... ascending
+//   result = tree over the 32 chains exactly as a shfl_down 16,8,4,2,1 reduction leaves it in lane 0.
+// (The reference's own GEMV order, tied to its 4-byte-per-lane loads, differs in the last bits; its
+// tests compare families with max|d|/rms < 1e-5, tests/test_gemm_mmq.cu:28.)
+#pragma once
+#include "common.cuh"
+
+namespace w4a8 {
+
+constexpr int GEMV_WARPS = 8;      // warps (= output rows) per CTA
+constexpr int GEMV_MT_MAX = 4;     // activation rows handled per pass of the dp4a kernel
+
+// Grouped-expert addressing (idx == nullptr: plain dense GEMV).  Expert e's weights start
+// e*(OUT*IN/2) bytes into Wq and its scales e*(OUT*IN/32) elements into sw, the indexing of the
+// reference's kernels/moe_fused.cuh:21-24; slot = token*topk + k.
+struct GroupedArgs {
+    const int32_t *idx = nullptr;
+    int topk = 1, x_per_slot = 0, num_experts = 0, nslots = 1;
+};
+
+__device__ __forceinline__ uint4 ldg_w16(const uint8_t *p, bool a16) {
+    if (a16) return __ldcs(reinterpret_cast<const uint4 *>(p));  // streamed once: evict-first
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(p);
+    return make_uint4(q[0], q[1], q[2], q[3]);
+}
+
+// MT  activation rows per pass (1..4), U = groups per lane loaded before any is consumed.
+// Shared memory: the MT activation rows, re-ordered once per CTA so that every group is two 16-byte
+// pieces [e0 o0 e1 o1] and [e2 o2 e3 o3] (ew/ow = even/odd elements of the w-th 8-element chunk), the
+// order unpack8_x16 produces for the weights; the pieces live in two planes so that consecutive lanes
+// read consecutive 16-byte words (no bank conflicts).  Then xs[MT][nb].
+template <int MT, int U, typename ST>
+__global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_dp4a_kernel(
+    const int8_t *__restrict__ xq, const float *__restrict__ xs, const uint8_t *__restrict__ Wq,
+    const ST *__restrict__ sw, float *__restrict__ Y, int IN, int OUT, int S, bool w_a16, GroupedArgs ga) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int nb = IN / QBLK;
+    if (ga.idx) {  // grouped experts: blockIdx.y = slot, one activation row against that slot's expert
+        const int slot = blockIdx.y;
+        const int e = ga.idx[slot];
+        if (e < 0 || e >= ga.num_experts) return;   // invalid id: the slot's output row is left untouched
+        const int row = ga.x_per_slot ? slot : slot / ga.topk;
+        xq += (size_t)row * IN;
+        xs += (size_t)row * nb;
+        Wq += (size_t)e * ((size_t)OUT * (IN / 2));
+        sw += (size_t)e * ((size_t)OUT * nb);
+        Y += (size_t)slot * OUT;
+    }
+    uint4 *plane0 = reinterpret_cast<uint4 *>(smem_raw);            // [MT][nb]
+    uint4 *plane1 = plane0 + (size_t)MT * nb;                       // [MT][nb]
+    float *sxs = reinterpret_cast<float *>(plane1 + (size_t)MT * nb);  // [MT][nb]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int o = blockIdx.x * GEMV_WARPS + warp;
+    const bool row_ok = o < OUT;
+    const uint8_t *wrow = Wq + (size_t)(row_ok ? o : 0) * (IN / 2);
+    const ST *swrow = sw + (size_t)(row_ok ? o : 0) * nb;
+
+    // First batch of weight loads goes out before the activations are staged.
+    uint4 wv[U];
+    float sv[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        const int b = lane + 32 * u;
+        if (row_ok && b < nb) { wv[u] = ldg_w16(wrow + 16 * b, w_a16); sv[u] = sval(swrow[b]); }
+        else { wv[u] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u); sv[u] = 0.f; }
+    }
+
+    // Stage activations: one task = one 8-element chunk (two 4-byte loads, like the reference's x0/x1).
+    for (int t = tid; t < MT * (IN / 8); t += GEMV_WARPS * 32) {
+        const int m = t / (IN / 8), c = t % (IN / 8);   // chunk c of row m
+        uint32_t x0 = 0, x1 = 0;
+        if (m < S) {
+            const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + (size_t)m * IN + 8 * c);
+            x0 = src[0]; x1 = src[1];
+        }
+        uint32_t e, od;
+        split_even_odd(x0, x1, e, od);
+        const int b = c >> 2, w = c & 3;
+        uint2 *dst = reinterpret_cast<uint2 *>((w < 2 ? plane0 : plane1) + (size_t)m * nb + b) + (w & 1);
+        *dst = make_uint2(e, od);
+    }
+    for (int t = tid; t < MT * nb; t += GEMV_WARPS * 32) {
+        const int m = t / nb, b = t % nb;
+        sxs[t] = (m < S) ? xs[(size_t)m * nb + b] : 0.f;
+    }
+    __syncthreads();
+    if (!row_ok) return;
+
+    float acc[MT];
+#pragma unroll
+    for (int m = 0; m < MT; m++) acc[m] = 0.f;
+
+    for (int i0 = 0; i0 * 32 < nb; i0 += U) {
+        if (i0 > 0) {
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int b = lane + 32 * (i0 + u);
+                if (b < nb) { wv[u] = ldg_w16(wrow + 16 * b, w_a16); sv[u] = sval(swrow[b]); }
+                else sv[u] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int b = lane + 32 * (i0 + u);
+            if (b < nb) {
+                uint32_t e0, o0, e1, o1, e2, o2, e3, o3;
+                unpack8_x16(wv[u].x, e0, o0); unpack8_x16(wv[u].y, e1, o1);
+                unpack8_x16(wv[u].z, e2, o2); unpack8_x16(wv[u].w, e3, o3);
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    const uint4 xa = plane0[(size_t)m * nb + b], xb = plane1[(size_t)m * nb + b];
+                    int d = __dp4a((int)xa.x, (int)e0, 0);
+                    d = __dp4a((int)xa.y, (int)o0, d);
+                    d = __dp4a((int)xa.z, (int)e1, d);
+                    d = __dp4a((int)xa.w, (int)o1, d);
+                    d = __dp4a((int)xb.x, (int)e2, d);
+                    d = __dp4a((int)xb.y, (int)o2, d);
+                    d = __dp4a((int)xb.z, (int)e3, d);
+                    d = __dp4a((int)xb.w, (int)o3, d);      // d = 16 * D[m,o,b], exact
+                    const float sc = (sxs[m * nb + b] * sv[u]) * 0.0625f;   // exact 1/16
+                    acc[m] = fmaf(sc, (float)d, acc[m]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+        float v = acc[m];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
+        if (lane == 0 && m < S) Y[(size_t)m * OUT + o] = v;
+    }
+}
+
+template <int MT, int U, typename ST>
+inline int launch_gemv_dp4a_t(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y,
+                              int IN, int OUT, int S, cudaStream_t st, const GroupedArgs &ga) {
+    const int nb = IN / QBLK;
+    const size_t smem = (size_t)MT * IN + (size_t)MT * nb * sizeof(float);
+    auto kern = gemv_w4a8_dp4a_kernel<MT, U, ST>;
+    if (smem > 48 * 1024) {
+        static size_t configured = 0;   // grow-only; single host thread per device (library convention)
+        if (smem > configured) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return cuda_fail(e, "gemv smem opt-in");
+            configured = smem;
+        }
+    }
+    const dim3 grid((unsigned)((OUT + GEMV_WARPS - 1) / GEMV_WARPS), (unsigned)(ga.idx ? ga.nslots : 1));
+    // every expert's base stays 16-byte aligned when Wq is, because OUT*IN/2 is a multiple of 16
+    kern<<<grid, GEMV_WARPS * 32, smem, st>>>(xq, xs, Wq, sw, Y, IN, OUT, S, aligned(Wq, 16), ga);
+    return launch_status("gemv_w4a8");
+}
+
+template <int MT, typename ST>
+inline int launch_gemv_dp4a_u(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y,
+                              int IN, int OUT, int S, cudaStream_t st, const GroupedArgs &ga = GroupedArgs()) {
+    const int nslots = (IN / QBLK + 31) / 32;
+    // Loads in flight per lane: the whole row when it has at most 5 slots, else the divisor of the slot
+    // count that wastes no predicated slot (5 for K = 15360), else 4.
+    int u = nslots <= 5 ? nslots : (nslots % 5 == 0 ? 5 : (nslots % 3 == 0 ? 3 : 4));
+    switch (u) {
+        case 1: return launch_gemv_dp4a_t<MT, 1, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga);
+        case 2: return launch_gemv_dp4a_t<MT, 2, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga);
+        case 3: return launch_gemv_dp4a_t<MT, 3, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga);
+        case 4: return launch_gemv_dp4a_t<MT, 4, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga);
+        default: return launch_gemv_dp4a_t<MT, 5, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga);
+    }
+}
+
+template <typename ST>
+inline int launch_gemv_st(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y,
+                          int IN, int OUT, int S, cudaStream_t st) {
+    const int nb = IN / QBLK;
+    // Rows beyond GEMV_MT_MAX go in further passes over the weights (which then come from L2).
+    for (int s0 = 0; s0 < S; s0 += GEMV_MT_MAX) {
+        const int s = S - s0 < GEMV_MT_MAX ? S - s0 : GEMV_MT_MAX;
+        const int8_t *xq_p = xq + (size_t)s0 * IN;
+        const float *xs_p = xs + (size_t)s0 * nb;
+        float *y_p = Y + (size_t)s0 * OUT;
+        int rc;
+        switch (s) {
+            case 1: rc = launch_gemv_dp4a_u<1, ST>(xq_p, xs_p, Wq, sw, y_p, IN, OUT, s, st); break;
+            case 2: rc = launch_gemv_dp4a_u<2, ST>(xq_p, xs_p, Wq, sw, y_p, IN, OUT, s, st); break;
+            case 3: rc = launch_gemv_dp4a_u<3, ST>(xq_p, xs_p, Wq, sw, y_p, IN, OUT, s, st); break;
+            default: rc = launch_gemv_dp4a_u<4, ST>(xq_p, xs_p, Wq, sw, y_p, IN, OUT, s, st); break;
+        }
+        if (rc != W4A8_OK) return rc;
+    }
+    return W4A8_OK;
+}
+
+inline int launch_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y,
+                       int IN, int OUT, int S, int scale_dtype, cudaStream_t st) {
+    if (S == 0 || OUT == 0) return W4A8_OK;
+    if (scale_dtype == 1) return launch_gemv_st<__half>(xq, xs, Wq, (const __half *)sw, Y, IN, OUT, S, st);
+    return launch_gemv_st<float>(xq, xs, Wq, (const float *)sw, Y, IN, OUT, S, st);
+}
+
+// Grouped experts: one launch, grid.y = slots, each slot one activation row against its expert.
+inline int launch_moe_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, const int32_t *idx,
+                           float *Y, int nslots, int topk, int x_per_slot, int N, int K, int num_experts,
+                           int scale_dtype, cudaStream_t st) {
+    if (nslots == 0 || N == 0) return W4A8_OK;
+    if (nslots > 65535) return fail(W4A8_ERR_UNSUPPORTED, "moe_gemv: at most 65535 slots per launch (got %d)", nslots);
+    GroupedArgs ga;
+    ga.idx = idx; ga.topk = topk; ga.x_per_slot = x_per_slot; ga.num_experts = num_experts; ga.nslots = nslots;
+    if (scale_dtype == 1) return launch_gemv_dp4a_u<1, __half>(xq, xs, Wq, (const __half *)sw, Y, K, N, 1, st, ga);
+    return launch_gemv_dp4a_u<1, float>(xq, xs, Wq, (const float *)sw, Y, K, N, 1, st, ga);
+}
+
+}  // namespace w4a8

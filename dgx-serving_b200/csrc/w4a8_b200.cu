@@ -1,0 +1,338 @@
+// The single translation unit of libw4a8_b200.so: includes every kernel file and defines the C ABI
+// declared in include/w4a8_b200.h.  Build (see dgx-serving_b200/build.py):
+//   nvcc -gencode arch=compute_100a,code=sm_100a -O3 -std=c++17 -lineinfo -Xcompiler -fPIC -shared
+#include <cerrno>
+#include <cstdlib>
+#include <cstring>
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include "common.cuh"
+#include "quantize_x.cuh"
+#include "gemv_w4a8.cuh"
+#include "gemm_w4a8_tc.cuh"
+
+namespace w4a8 {
+
+char *err_buf() {
+    static thread_local char buf[512] = {0};
+    return buf;
+}
+
+int sm_count() {
+    static int cached_dev = -1, cached = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev != cached_dev) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached = n;
+        cached_dev = dev;
+    }
+    return cached;
+}
+
+int require_sm100() {
+    static int cached_dev = -1, cached_rc = W4A8_OK;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "no CUDA device (this library has no CPU path)");
+    if (dev != cached_dev) {
+        int major = 0;
+        e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+        cached_rc = (major == 10) ? W4A8_OK : W4A8_ERR_UNSUPPORTED;
+        cached_dev = dev;
+        if (cached_rc != W4A8_OK)
+            return fail(W4A8_ERR_UNSUPPORTED, "device %d is compute capability %d.x; this build targets sm_100a only", dev, major);
+    }
+    if (cached_rc != W4A8_OK) return fail(W4A8_ERR_UNSUPPORTED, "device %d is not an sm_100 device", dev);
+    return W4A8_OK;
+}
+
+// Exact integer group dots through the dp4a path of the GEMV kernels: one thread per (m, n, group).
+__global__ void __launch_bounds__(256) group_dots_dp4a_kernel(const int8_t *__restrict__ xq, const uint8_t *__restrict__ Wq,
+                                                              int32_t *__restrict__ D, int M, int N, int K) {
+    const int nb = K / QBLK;
+    const long total = (long)M * N * nb;
+    const long stride = (long)gridDim.x * blockDim.x;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int b = (int)(i % nb);
+        const long mn = i / nb;
+        const int n = (int)(mn % N), m = (int)(mn / N);
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(Wq + (size_t)n * (K / 2) + 16 * b);
+        const uint32_t *x = reinterpret_cast<const uint32_t *>(xq + (size_t)m * K + 32 * b);
+        int d = 0;
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            uint32_t we, wo, xe, xo;
+            unpack8_x16(w[c], we, wo);
+            split_even_odd(x[2 * c], x[2 * c + 1], xe, xo);
+            d = __dp4a((int)xe, (int)we, d);
+            d = __dp4a((int)xo, (int)wo, d);
+        }
+        D[i] = d >> 4;
+    }
+}
+
+static int check_common(const void *a, const void *b, const void *c, const void *d, const void *e, int K, int scale_dtype,
+                        const char *who) {
+    if (!a || !b || !c || !d || !e) return fail(W4A8_ERR_ARG, "%s: null pointer argument", who);
+    if (K < 0 || K % QBLK != 0) return fail(W4A8_ERR_ARG, "%s: K=%d must be a non-negative multiple of %d", who, K, QBLK);
+    if (scale_dtype != 0 && scale_dtype != 1) return fail(W4A8_ERR_ARG, "%s: scale_dtype=%d (0 fp32, 1 fp16)", who, scale_dtype);
+    return W4A8_OK;
+}
+
+}  // namespace w4a8
+
+using namespace w4a8;
+
+W4A8_API int w4a8_version(void) { return 100; }
+W4A8_API const char *w4a8_last_error(void) { return err_buf(); }
+
+W4A8_API int w4a8_device_status(uint32_t *detail) {
+    unsigned int v = 0, zero = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceSynchronize");
+    e = cudaMemcpyFromSymbol(&v, g_dev_error, sizeof(v));
+    if (e != cudaSuccess) return cuda_fail(e, "read device error word");
+    if (v != 0) {
+        cudaMemcpyToSymbol(g_dev_error, &zero, sizeof(zero));
+        if (detail) *detail = v;
+        return fail(W4A8_ERR_DEVICE, "a kernel's bounded wait ran out (code 0x%x)", v);
+    }
+    if (detail) *detail = 0;
+    return W4A8_OK;
+}
+
+W4A8_API int w4a8_quantize_x_q8(const float *X, int8_t *xq, float *xs, int32_t *xsum, int IN, int S, void *stream) {
+    if (S < 0 || IN < 0 || IN % QBLK != 0) return fail(W4A8_ERR_ARG, "quantize_x_q8: IN=%d S=%d (IN must be a multiple of %d)", IN, S, QBLK);
+    if (S == 0 || IN == 0) return W4A8_OK;
+    if (!X || !xq || !xs) return fail(W4A8_ERR_ARG, "quantize_x_q8: null pointer argument");
+    int rc = require_sm100();
+    if (rc != W4A8_OK) return rc;
+    return launch_quantize_x(X, xq, xs, xsum, IN, S, (cudaStream_t)stream);
+}
+
+W4A8_API int w4a8_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int IN, int OUT,
+                       int S, int scale_dtype, void *stream) {
+    if (S < 0 || OUT < 0) return fail(W4A8_ERR_ARG, "gemv: negative size S=%d OUT=%d", S, OUT);
+    if (S == 0 || OUT == 0) return W4A8_OK;
+    int rc = check_common(xq, xs, Wq, sw, Y, IN, scale_dtype, "gemv");
+    if (rc != W4A8_OK) return rc;
+    if (!aligned(xq, 4) || !aligned(Wq, 4)) return fail(W4A8_ERR_ALIGN, "gemv: xq and Wq must be 4-byte aligned");
+    rc = require_sm100();
+    if (rc != W4A8_OK) return rc;
+    if (IN == 0) {
+        cudaError_t e = cudaMemsetAsync(Y, 0, (size_t)S * OUT * sizeof(float), (cudaStream_t)stream);
+        return e == cudaSuccess ? W4A8_OK : cuda_fail(e, "gemv: memset");
+    }
+    return launch_gemv(xq, xs, Wq, sw, Y, IN, OUT, S, scale_dtype, (cudaStream_t)stream);
+}
+
+W4A8_API int w4a8_gemm(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int M, int N, int K,
+                       int scale_dtype, void *stream) {
+    if (M < 0 || N < 0) return fail(W4A8_ERR_ARG, "gemm: negative size M=%d N=%d", M, N);
+    if (M == 0 || N == 0) return W4A8_OK;   // reference: kernels/gemm_mmq_raster.cuh:118
+    int rc = check_common(X, xs, Wq, sw, Y, K, scale_dtype, "gemm");
+    if (rc != W4A8_OK) return rc;
+    if (!aligned(X, 16) || !aligned(Wq, 16))
+        return fail(W4A8_ERR_ALIGN, "gemm: X and Wq must be 16-byte aligned (TMA); use w4a8_gemv for unaligned operands");
+    rc = require_sm100();
+    if (rc != W4A8_OK) return rc;
+    if (K == 0) {
+        cudaError_t e = cudaMemsetAsync(Y, 0, (size_t)M * N * sizeof(float), (cudaStream_t)stream);
+        return e == cudaSuccess ? W4A8_OK : cuda_fail(e, "gemm: memset");
+    }
+    return gemm::launch_tc(X, xs, Wq, sw, Y, M, N, K, scale_dtype, 1, K / QBLK, (cudaStream_t)stream);
+}
+
+// Split count and groups per split.  Boundaries follow the reference: K-tiles of 64 (2 groups), ranges of
+// ceil(niter/splitk) K-tiles (kernels/gemm_mmq.cuh:138-139), default split count ~96 CTAs clamp 1..8 (:209-210).
+static void splitk_plan(int N, int K, int splitk_in, int *nsplit, int *gsplit) {
+    const int nb = K / QBLK;
+    const int niter = (nb + 1) / 2;
+    int sk = splitk_in;
+    if (sk <= 0) {
+        const int ntile = (N + 127) / 128;
+        const int want = 96 / ntile;
+        sk = want > 1 ? (want < 8 ? want : 8) : 1;
+    }
+    const int itper = (niter + sk - 1) / sk;
+    *nsplit = sk;
+    *gsplit = (itper > 0 ? itper : 1) * 2;
+}
+
+W4A8_API size_t w4a8_gemm_splitk_workspace_bytes(int M, int N, int K, int splitk) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    int ns, gs;
+    splitk_plan(N, K, splitk, &ns, &gs);
+    return ns > 1 ? (size_t)ns * M * N * sizeof(float) : 0;
+}
+
+W4A8_API int w4a8_gemm_splitk(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int M, int N,
+                              int K, int scale_dtype, int splitk, void *workspace, size_t workspace_bytes, void *stream) {
+    if (M < 0 || N < 0) return fail(W4A8_ERR_ARG, "gemm_splitk: negative size M=%d N=%d", M, N);
+    if (M == 0 || N == 0) return W4A8_OK;
+    int rc = check_common(X, xs, Wq, sw, Y, K, scale_dtype, "gemm_splitk");
+    if (rc != W4A8_OK) return rc;
+    if (!aligned(X, 16) || !aligned(Wq, 16)) return fail(W4A8_ERR_ALIGN, "gemm_splitk: X and Wq must be 16-byte aligned (TMA)");
+    if (K == 0) return w4a8_gemm(X, xs, Wq, sw, Y, M, N, K, scale_dtype, stream);
+    rc = require_sm100();
+    if (rc != W4A8_OK) return rc;
+    int ns, gs;
+    splitk_plan(N, K, splitk, &ns, &gs);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (ns == 1) return gemm::launch_tc(X, xs, Wq, sw, Y, M, N, K, scale_dtype, 1, K / QBLK, st);
+    const size_t need = (size_t)ns * M * N * sizeof(float);
+    if (!workspace || workspace_bytes < need)
+        return fail(W4A8_ERR_WORKSPACE, "gemm_splitk: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    if (!aligned(workspace, 16)) return fail(W4A8_ERR_ALIGN, "gemm_splitk: workspace must be 16-byte aligned");
+    rc = gemm::launch_tc(X, xs, Wq, sw, (float *)workspace, M, N, K, scale_dtype, ns, gs, st);
+    if (rc != W4A8_OK) return rc;
+    const long MN = (long)M * N;
+    long want = (MN + 255) / 256, cap = (long)sm_count() * 8;
+    gemm::splitk_reduce_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>((const float *)workspace, Y, MN, ns);
+    return launch_status("splitk_reduce");
+}
+
+W4A8_API int w4a8_group_dots(const int8_t *xq, const uint8_t *Wq, int32_t *D, int M, int N, int K, int path, void *stream) {
+    if (M < 0 || N < 0 || K < 0 || K % QBLK != 0) return fail(W4A8_ERR_ARG, "group_dots: bad shape M=%d N=%d K=%d", M, N, K);
+    if (M == 0 || N == 0 || K == 0) return W4A8_OK;
+    if (!xq || !Wq || !D) return fail(W4A8_ERR_ARG, "group_dots: null pointer argument");
+    int rc = require_sm100();
+    if (rc != W4A8_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (path == 1) {
+        if (!aligned(xq, 16) || !aligned(Wq, 16)) return fail(W4A8_ERR_ALIGN, "group_dots: tensor-core path needs 16-byte aligned operands");
+        return gemm::launch_tc_dump(xq, Wq, D, M, N, K, st);
+    }
+    if (path != 0) return fail(W4A8_ERR_ARG, "group_dots: path=%d (0 dp4a, 1 tcgen05)", path);
+    if (!aligned(xq, 4) || !aligned(Wq, 4)) return fail(W4A8_ERR_ALIGN, "group_dots: operands must be 4-byte aligned");
+    const long total = (long)M * N * (K / QBLK);
+    long want = (total + 255) / 256, cap = (long)sm_count() * 8;
+    group_dots_dp4a_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(xq, Wq, D, M, N, K);
+    return launch_status("group_dots");
+}
+
+W4A8_API int w4a8_linear(const float *X, int8_t *xq, float *xs, int32_t *xsum, const uint8_t *Wq, const void *sw, float *Y,
+                         int S, int N, int K, int scale_dtype, int skip_quantize, void *stream) {
+    if (!skip_quantize) {
+        int rc = w4a8_quantize_x_q8(X, xq, xs, xsum, K, S, stream);
+        if (rc != W4A8_OK) return rc;
+    }
+    if (S <= 16 || !aligned(xq, 16) || !aligned(Wq, 16)) return w4a8_gemv(xq, xs, Wq, sw, Y, K, N, S, scale_dtype, stream);
+    return w4a8_gemm(xq, xs, Wq, sw, Y, S, N, K, scale_dtype, stream);
+}
+
+W4A8_API int w4a8_moe_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, const int32_t *idx, float *Y,
+                           int nslots, int topk, int x_per_slot, int N, int K, int num_experts, int scale_dtype, void *stream) {
+    if (nslots < 0 || N < 0 || topk <= 0 || num_experts <= 0)
+        return fail(W4A8_ERR_ARG, "moe_gemv: bad sizes nslots=%d N=%d topk=%d experts=%d", nslots, N, topk, num_experts);
+    if (nslots == 0 || N == 0) return W4A8_OK;
+    int rc = check_common(xq, xs, Wq, sw, Y, K, scale_dtype, "moe_gemv");
+    if (rc != W4A8_OK) return rc;
+    if (!idx) return fail(W4A8_ERR_ARG, "moe_gemv: null expert index");
+    if (K == 0) return fail(W4A8_ERR_ARG, "moe_gemv: K must be positive");
+    if (!aligned(xq, 4) || !aligned(Wq, 4)) return fail(W4A8_ERR_ALIGN, "moe_gemv: xq and Wq must be 4-byte aligned");
+    rc = require_sm100();
+    if (rc != W4A8_OK) return rc;
+    return launch_moe_gemv(xq, xs, Wq, sw, idx, Y, nslots, topk, x_per_slot, N, K, num_experts, scale_dtype, (cudaStream_t)stream);
+}
+
+// ---- N-sharded weight upload ---------------------------------------------------------------------------
+W4A8_API int w4a8_shard_rows(int64_t N, int rank, int world, int64_t *row0, int64_t *rows) {
+    if (N < 0 || world <= 0 || rank < 0 || rank >= world || !row0 || !rows)
+        return fail(W4A8_ERR_ARG, "shard_rows: N=%lld rank=%d world=%d", (long long)N, rank, world);
+    const int64_t base = N / world, rem = N % world;
+    const int64_t first_big = world - rem;   // ranks >= first_big hold base+1 rows
+    *rows = base + (rank >= first_big ? 1 : 0);
+    *row0 = base * rank + (rank > first_big ? rank - first_big : 0);
+    return W4A8_OK;
+}
+
+static int upload_range(void **dev, const void *host, size_t bytes, const char *what) {
+    *dev = nullptr;
+    if (bytes == 0) return W4A8_OK;
+    cudaError_t e = cudaMalloc(dev, bytes);
+    if (e != cudaSuccess) return cuda_fail(e, what);
+    e = cudaMemcpy(*dev, host, bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { cudaFree(*dev); *dev = nullptr; return cuda_fail(e, what); }
+    return W4A8_OK;
+}
+
+static int shard_shape(int64_t N, int64_t K, int scale_dtype, int rank, int world, w4a8_qmat *out, const char *who) {
+    if (!out) return fail(W4A8_ERR_ARG, "%s: null output", who);
+    memset(out, 0, sizeof(*out));
+    if (N < 0 || K < 0 || K % QBLK != 0) return fail(W4A8_ERR_ARG, "%s: bad shape N=%lld K=%lld", who, (long long)N, (long long)K);
+    if (scale_dtype != 0 && scale_dtype != 1) return fail(W4A8_ERR_ARG, "%s: scale_dtype=%d", who, scale_dtype);
+    int rc = w4a8_shard_rows(N, rank, world, &out->row0, &out->rows);
+    if (rc != W4A8_OK) return rc;
+    out->N = N; out->K = K; out->scale_dtype = scale_dtype;
+    return W4A8_OK;
+}
+
+W4A8_API int w4a8_upload_qmat_shard(const uint8_t *host_wq, const void *host_sc, int64_t N, int64_t K, int scale_dtype, int rank,
+                                    int world, w4a8_qmat *out) {
+    int rc = shard_shape(N, K, scale_dtype, rank, world, out, "upload_qmat_shard");
+    if (rc != W4A8_OK) return rc;
+    if (!host_wq || !host_sc) return fail(W4A8_ERR_ARG, "upload_qmat_shard: null host pointer");
+    const size_t esz = scale_dtype == 1 ? 2 : 4;
+    const size_t wrow = (size_t)K / 2, srow = (size_t)(K / QBLK) * esz;
+    rc = upload_range((void **)&out->wq, host_wq + (size_t)out->row0 * wrow, (size_t)out->rows * wrow, "upload q4 rows");
+    if (rc != W4A8_OK) return rc;
+    rc = upload_range(&out->sc, (const uint8_t *)host_sc + (size_t)out->row0 * srow, (size_t)out->rows * srow, "upload scale rows");
+    if (rc != W4A8_OK) { cudaFree(out->wq); out->wq = nullptr; }
+    return rc;
+}
+
+// Reads bytes [off, off+bytes) of `path` into a host buffer and uploads them.
+static int load_range(const char *path, size_t off, size_t bytes, size_t file_need, void **dev) {
+    *dev = nullptr;
+    int fd = open(path, O_RDONLY);
+    if (fd < 0) return fail(W4A8_ERR_IO, "cannot open %s: %s", path, strerror(errno));
+    struct stat sb;
+    if (fstat(fd, &sb) != 0 || (size_t)sb.st_size < file_need) {
+        close(fd);
+        return fail(W4A8_ERR_IO, "%s: size mismatch (%lld bytes, need %zu)", path, (long long)sb.st_size, file_need);
+    }
+    if (bytes == 0) { close(fd); return W4A8_OK; }
+    void *host = nullptr;
+    cudaError_t e = cudaMallocHost(&host, bytes);
+    if (e != cudaSuccess) { close(fd); return cuda_fail(e, "pinned staging buffer"); }
+    size_t done = 0;
+    while (done < bytes) {
+        ssize_t r = pread(fd, (char *)host + done, bytes - done, (off_t)(off + done));
+        if (r <= 0) { close(fd); cudaFreeHost(host); return fail(W4A8_ERR_IO, "%s: short read at %zu", path, off + done); }
+        done += (size_t)r;
+    }
+    posix_fadvise(fd, (off_t)off, (off_t)bytes, POSIX_FADV_DONTNEED);   // like runtime/weights_qwen.cu:18
+    close(fd);
+    int rc = upload_range(dev, host, bytes, path);
+    cudaFreeHost(host);
+    return rc;
+}
+
+W4A8_API int w4a8_load_qmat_shard(const char *q4_path, const char *scale_path, int64_t N, int64_t K, int scale_dtype, int rank,
+                                  int world, w4a8_qmat *out) {
+    int rc = shard_shape(N, K, scale_dtype, rank, world, out, "load_qmat_shard");
+    if (rc != W4A8_OK) return rc;
+    if (!q4_path || !scale_path) return fail(W4A8_ERR_ARG, "load_qmat_shard: null path");
+    const size_t esz = scale_dtype == 1 ? 2 : 4;
+    const size_t wrow = (size_t)K / 2, srow = (size_t)(K / QBLK) * esz;
+    rc = load_range(q4_path, (size_t)out->row0 * wrow, (size_t)out->rows * wrow, (size_t)N * wrow, (void **)&out->wq);
+    if (rc != W4A8_OK) return rc;
+    rc = load_range(scale_path, (size_t)out->row0 * srow, (size_t)out->rows * srow, (size_t)N * srow, &out->sc);
+    if (rc != W4A8_OK) { cudaFree(out->wq); out->wq = nullptr; }
+    return rc;
+}
+
+W4A8_API int w4a8_free_qmat(w4a8_qmat *m) {
+    if (!m) return W4A8_OK;
+    if (m->wq) cudaFree(m->wq);
+    if (m->sc) cudaFree(m->sc);
+    m->wq = nullptr;
+    m->sc = nullptr;
+    return W4A8_OK;
+}

@@ -1,0 +1,152 @@
+/*
+ * w4a8_b200 — C ABI of the B200 (sm_100a) W4A8 quantized-matmul library.
+ *
+ * Drop-in replacement for the header-only `launch_*` kernel launchers of hyunlord/dgx-serving's
+ * W4A8 path (kernels/quantize_x.cuh, gemv_w4a8.cuh, gemm_batch.cuh, gemm_mma.cuh, gemm_mmq*.cuh)
+ * and for the whole-file weight upload of runtime/weights*.cu.  Each entry point cites the
+ * reference interface it replaces.  Same-named C++ shim launchers that forward to this ABI live in
+ * dgx-serving_b200/kernels/.
+ *
+ * Conventions (they mirror the reference's):
+ *   - Every pointer is a DEVICE pointer owned by the caller unless the name says `host`.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the default stream).  Launch entry points
+ *     only enqueue work: no synchronisation, no allocation, no host-side branching on device data,
+ *     so they may be called under CUDA-graph stream capture like the reference launchers
+ *     (models/gemma4_decode.cu:180-189).
+ *   - Data formats are the reference's: Wq[N][K/2] uint8, byte j of a row = element 2j in the low
+ *     nibble and 2j+1 in the high nibble, value = nibble - 8 (kernels/gemv_w4a8.cuh:16-21);
+ *     sw[N][K/32] per-group scales, fp32 (scale_dtype 0) or fp16 (scale_dtype 1)
+ *     (runtime/config.h:44-45); xq[S][K] int8 with xs[S][K/32] fp32 per-32-block scales
+ *     (kernels/quantize_x.cuh:6-11).  K must be a multiple of 32.
+ *   - The reference launchers return void and never check errors (callers synchronise and exit on
+ *     any CUDA error, models/qwen35_decode.cu:24-25,229).  These return an int status instead:
+ *     0 on success, a W4A8_ERR_* code otherwise, with w4a8_last_error() giving the text.  There is
+ *     no CPU fallback: without a usable sm_100 device every launch entry point fails.
+ *   - Single host thread per device, like the reference.
+ */
+#ifndef W4A8_B200_H
+#define W4A8_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define W4A8_QBLK 32 /* runtime/config.h:9-11 */
+
+enum {
+    W4A8_OK = 0,
+    W4A8_ERR_ARG = 1,         /* null pointer, K % 32 != 0, negative size, unknown scale_dtype ... */
+    W4A8_ERR_ALIGN = 2,       /* a pointer or pitch misses the alignment the entry point documents */
+    W4A8_ERR_CUDA = 3,        /* a CUDA runtime / driver call failed (text in w4a8_last_error) */
+    W4A8_ERR_IO = 4,          /* weight file missing or shorter than the shape requires */
+    W4A8_ERR_DEVICE = 5,      /* a kernel recorded a device-side error (bounded wait ran out) */
+    W4A8_ERR_UNSUPPORTED = 6, /* not an sm_100 device, or a size beyond a documented maximum */
+    W4A8_ERR_WORKSPACE = 7    /* caller-provided workspace too small */
+};
+
+/* Library version (major*10000 + minor*100 + patch). */
+int w4a8_version(void);
+/* Text of the last failure on this host thread ("" if none). */
+const char *w4a8_last_error(void);
+/* Reads and clears the device-side error word that kernels with bounded waits set when a wait runs
+ * out.  Synchronises the device.  Returns W4A8_OK or W4A8_ERR_DEVICE (detail in *detail if given). */
+int w4a8_device_status(uint32_t *detail);
+
+/* ---- a1: activation quantization ------------------------------------------------------------------
+ * Replaces launch_quantize_x_q8 (kernels/quantize_x.cuh:41-47).
+ * X[S,IN] fp32 -> xq[S,IN] int8, xs[S,IN/32] fp32 (= amax/127), xsum[S,IN/32] int32 (= sum of xq over
+ * the block; may be NULL).  Bit-exact with the reference: d = amax/127.0f, q = rintf(x/d) clamped to
+ * +-127, all-zero block -> q = 0, d = 0. */
+int w4a8_quantize_x_q8(const float *X, int8_t *xq, float *xs, int32_t *xsum, int IN, int S, void *stream);
+
+/* ---- a4-a8: decode GEMV family (S = 1..16 rows; any S >= 1 is accepted) --------------------------
+ * Replaces launch_gemv_w4a8 / _mlp<U> / _mlp_auto / _g4 (kernels/gemv_w4a8.cuh:93,102,155,316; their
+ * unused xsum argument is dropped), launch_gemv_w4a8_sb / _sb_g4 (:168,:337) and
+ * launch_gemm_batch_w4a8 (kernels/gemm_batch.cuh:228).
+ * Y[s,o] = sum_b xs[s,b]*sw[o,b] * sum_{k in b} xq[s,k]*(Wq[o,k]-8).  Weights are streamed once for
+ * all S rows.  Integer group dots are exact; every row's fp32 result is independent of S and of the
+ * row's position, and bitwise reproducible. */
+int w4a8_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y,
+              int IN, int OUT, int S, int scale_dtype, void *stream);
+
+/* ---- a9-a12: prefill / verify GEMM family ---------------------------------------------------------
+ * Replaces launch_gemm_mmq_w4a8 / _kt<KT> / _auto, launch_gemm_mmq_tmpl<...>
+ * (kernels/gemm_mmq.cuh:222-233, gemm_mmq_tmpl.cuh:100-119), launch_gemm_mmq_raster_w4a8
+ * (kernels/gemm_mmq_raster.cuh:115-130), launch_gemm_mma_w4a8 / _bm<BM> (kernels/gemm_mma.cuh:119-132)
+ * and launch_gemm_mmq_ms (kernels/gemm_mmq_ms.cuh).  Note the (M,N,K) argument order of this family.
+ * Y[M,N] fp32 row-major.  Integer group dots come from tcgen05 kind::i8 MMAs and are exact; the fp32
+ * epilogue evaluates t = (float)D*xs[m,b]; acc = fma(t, sw[n,b], acc) for b ascending, the order of
+ * kernels/gemm_mmq.cuh:104-105, so results match the reference MMQ kernels bit for bit.
+ * Needs X and Wq 16-byte aligned (TMA); M, N arbitrary. */
+int w4a8_gemm(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y,
+              int M, int N, int K, int scale_dtype, void *stream);
+
+/* ---- a13: split-K GEMM for skinny M -----------------------------------------------------------------
+ * Replaces launch_gemm_bm16_splitk (kernels/gemm_mmq.cuh:205-219), whose workspace is a grow-only
+ * static cudaMalloc inside the launcher (:206,:215; not capture-safe).  Here the caller owns it.
+ * K is cut into `splitk` contiguous ranges of ceil(ceil(K/64)/splitk) 64-wide K-tiles; each range is
+ * summed in MMQ order into workspace[split][M][N]; a second kernel adds the partials in ascending
+ * split order.  splitk <= 0 picks the reference's heuristic (about 96 CTAs, clamp 1..8). */
+size_t w4a8_gemm_splitk_workspace_bytes(int M, int N, int K, int splitk);
+int w4a8_gemm_splitk(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y,
+                     int M, int N, int K, int scale_dtype, int splitk,
+                     void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---- exact integer group dots (debug / parity) ------------------------------------------------------
+ * D[m,n,b] = sum_{k in b} xq[m,k]*(Wq[n,k]-8) as int32, D laid out [M][N][K/32].  `path` selects the
+ * producer: 0 = the GEMV kernels' dp4a path, 1 = the GEMM kernel's tcgen05 path (accumulators read
+ * back from tensor memory).  Checks the bit-exactness the fp32 entry points rest on
+ * (tests/test_mma_b0.cu:46-49). */
+int w4a8_group_dots(const int8_t *xq, const uint8_t *Wq, int32_t *D, int M, int N, int K, int path,
+                    void *stream);
+
+/* ---- mm(): quantize + matmul dispatch ---------------------------------------------------------------
+ * Replaces the static mm()/MMs()/mmb() dispatchers of the model graphs (models/qwen35_decode.cu:51-62,
+ * models/qwen35_batch.cu:120-139, models/gemma4_decode.cu:113-129): quantize X[S,K] into the caller's
+ * scratch (xq, xs, xsum as for w4a8_quantize_x_q8) unless skip_quantize != 0 (the G4_QUANT_SHARE case,
+ * models/gemma4_decode.cu:115), then S <= 16 -> w4a8_gemv, else -> w4a8_gemm. */
+int w4a8_linear(const float *X, int8_t *xq, float *xs, int32_t *xsum, const uint8_t *Wq, const void *sw,
+                float *Y, int S, int N, int K, int scale_dtype, int skip_quantize, void *stream);
+
+/* ---- grouped experts (W4A8 semantics per expert) ----------------------------------------------------
+ * The reference's expert kernels take fp32 activations (kernels/moe_fused.cuh:14-33); this keeps their
+ * weight indexing — expert e starts e*(N*K/2) bytes into Wq and e*(N*K/32) scales into sw
+ * (kernels/moe_fused.cuh:21-24), slot = token*topk + k, expert id idx[slot] read on the device — and
+ * applies the dense W4A8 product per slot.  Y[nslots,N].  x_per_slot = 0: activations are per token
+ * (row slot/topk; gate/up projection); 1: per slot (down projection). */
+int w4a8_moe_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, const int32_t *idx,
+                  float *Y, int nslots, int topk, int x_per_slot, int N, int K, int num_experts,
+                  int scale_dtype, void *stream);
+
+/* ---- a15: N-sharded weight upload --------------------------------------------------------------------
+ * Replaces QMat + load_dev()/mat() (runtime/weights_qwen.h:8, runtime/weights_qwen.cu:12-36,
+ * runtime/weights_gemma4.cu:12-41): `<name>_q4.bin` holds N*K/2 bytes, `<name>_scale.bin` holds
+ * N*K/32 scales of 4 (scale_dtype 0) or 2 (scale_dtype 1) bytes.  Rank r of `world` keeps rows
+ * [row0, row0+rows) — a contiguous byte range of each file, because rows are the outer dimension —
+ * on the current device.  world = 1 reproduces the reference's whole-file upload. */
+typedef struct w4a8_qmat {
+    uint8_t *wq;     /* device, rows*K/2 bytes */
+    void *sc;        /* device, rows*K/32 scales */
+    int64_t row0;    /* first row held */
+    int64_t rows;    /* number of rows held */
+    int64_t N, K;    /* full shape */
+    int scale_dtype; /* 0 fp32, 1 fp16 */
+} w4a8_qmat;
+
+/* Row range of `rank`: floor(N/world) rows each, the remainder spread one row each over the LAST
+ * ranks; ranges are contiguous and ordered by rank. */
+int w4a8_shard_rows(int64_t N, int rank, int world, int64_t *row0, int64_t *rows);
+int w4a8_load_qmat_shard(const char *q4_path, const char *scale_path, int64_t N, int64_t K,
+                         int scale_dtype, int rank, int world, w4a8_qmat *out);
+/* Same, from host memory holding the full [N] tensors (for callers that already read the files). */
+int w4a8_upload_qmat_shard(const uint8_t *host_wq, const void *host_sc, int64_t N, int64_t K,
+                           int scale_dtype, int rank, int world, w4a8_qmat *out);
+int w4a8_free_qmat(w4a8_qmat *m);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* W4A8_B200_H */

@@ -1,0 +1,181 @@
+"""numpy/ctypes front end of the CPU oracle (liboracle.so) plus the seeded synthetic-input generators.
+
+TEST INFRASTRUCTURE ONLY.  Imported by tests/, by __graft_entry__.smoke() and by bench.py's
+cpu_baseline / --impl reference legs; never by the shipped library or its Python binding.
+
+The arithmetic lives in w4a8_oracle.c (each function cites the reference file:line it restates).  The
+generators below produce the input distributions BASELINE.json's configs name: int4 weights uniform in
+[-8, 7] packed two per byte in the reference layout, group-32 fp32 scales |N(0, 0.02)|/7, activations
+N(0, 1) (optionally 1 % of entries scaled 20x), all from numpy's PCG64 with an explicit seed.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "liboracle.so")
+_REF_PATH = os.path.join(_HERE, "_ref", "libref_kernels.so")
+QBLK = 32
+_lib = None
+
+
+def build(force=False):
+    """Compiles liboracle.so (and, when the reference tree is present, _ref/libref_kernels.so)."""
+    src = os.path.join(_HERE, "w4a8_oracle.c")
+    stale = force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src)
+    if stale or (os.path.isdir("/root/reference/kernels") and not os.path.exists(_REF_PATH)):
+        if os.path.exists("/usr/bin/make") and os.path.exists("/usr/bin/gcc"):
+            subprocess.run(["make", "-C", _HERE] + (["-B"] if force else []), check=True, capture_output=True)
+    return _LIB_PATH
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build()
+        l = ctypes.CDLL(_LIB_PATH)
+        l.oracle_max_threads.restype = ctypes.c_int
+        l.oracle_lcg_frand.restype = ctypes.c_float
+        _lib = l
+    return _lib
+
+
+def ref_kernels_path():
+    """Path of the reference's own CUDA kernels rebuilt for sm_100a, or None if not built."""
+    return _REF_PATH if os.path.exists(_REF_PATH) else None
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def max_threads():
+    return int(lib().oracle_max_threads())
+
+
+def set_threads(n):
+    lib().oracle_set_threads(int(n))
+
+
+def lcg_fill(n, mul, seed):
+    """n floats from the reference tests' LCG (tests/test_w4a8.cu:16); returns (array, new_seed)."""
+    out = np.empty(n, dtype=np.float32)
+    s = ctypes.c_uint32(seed)
+    lib().oracle_lcg_fill(_p(out), ctypes.c_size_t(n), ctypes.c_float(mul), ctypes.byref(s))
+    return out, s.value
+
+
+def quantize_x_q8(X):
+    """X[S,IN] float32 -> (xq int8 [S,IN], xs float32 [S,IN/32], xsum int32 [S,IN/32])."""
+    X = np.ascontiguousarray(X, dtype=np.float32)
+    S, IN = X.shape
+    assert IN % QBLK == 0
+    xq = np.empty((S, IN), dtype=np.int8)
+    xs = np.empty((S, IN // QBLK), dtype=np.float32)
+    xsum = np.empty((S, IN // QBLK), dtype=np.int32)
+    lib().oracle_quantize_x_q8(_p(X), _p(xq), _p(xs), _p(xsum), IN, S)
+    return xq, xs, xsum
+
+
+def pack_q4(W, zero_scale=1.0):
+    """W[OUT,IN] float32 -> (Wq uint8 [OUT,IN/2], sc float32 [OUT,IN/32]); RTN, scale = max|w|/7."""
+    W = np.ascontiguousarray(W, dtype=np.float32)
+    OUT, IN = W.shape
+    Wq = np.empty((OUT, IN // 2), dtype=np.uint8)
+    sc = np.empty((OUT, IN // QBLK), dtype=np.float32)
+    lib().oracle_pack_q4(_p(W), OUT, IN, _p(Wq), _p(sc), ctypes.c_float(zero_scale))
+    return Wq, sc
+
+
+def _sd(sw):
+    assert sw.dtype in (np.float32, np.float16)
+    return 1 if sw.dtype == np.float16 else 0
+
+
+def group_dots(xq, Wq):
+    M, K = xq.shape
+    N = Wq.shape[0]
+    D = np.empty((M, N, K // QBLK), dtype=np.int32)
+    lib().oracle_group_dots(_p(np.ascontiguousarray(xq)), _p(np.ascontiguousarray(Wq)), _p(D), M, N, K)
+    return D
+
+
+def _run(fn, out_dtype, xq, xs, Wq, sw, extra=()):
+    M, K = xq.shape
+    N = Wq.shape[0]
+    Y = np.empty((M, N), dtype=out_dtype)
+    fn(_p(np.ascontiguousarray(xq)), _p(np.ascontiguousarray(xs)), _p(np.ascontiguousarray(Wq)),
+       _p(np.ascontiguousarray(sw)), _p(Y), M, N, K, _sd(sw), *extra)
+    return Y
+
+
+def w4a8_f64(xq, xs, Wq, sw):
+    """fp64 golden of tests/test_w4a8.cu:44-56."""
+    return _run(lib().oracle_w4a8_f64, np.float64, xq, xs, Wq, sw)
+
+
+def gemv_w4a8(xq, xs, Wq, sw):
+    """fp32 in the reference GEMV family's order (note the C signature is IN, OUT, S)."""
+    M, K = xq.shape
+    N = Wq.shape[0]
+    Y = np.empty((M, N), dtype=np.float32)
+    lib().oracle_gemv_w4a8(_p(np.ascontiguousarray(xq)), _p(np.ascontiguousarray(xs)), _p(np.ascontiguousarray(Wq)),
+                           _p(np.ascontiguousarray(sw)), _p(Y), K, N, M, _sd(sw))
+    return Y
+
+
+def gemm_mmq_w4a8(xq, xs, Wq, sw):
+    """fp32 in the reference MMQ / MMA family's order."""
+    return _run(lib().oracle_gemm_mmq_w4a8, np.float32, xq, xs, Wq, sw)
+
+
+def gemm_splitk_w4a8(xq, xs, Wq, sw, splitk):
+    return _run(lib().oracle_gemm_splitk_w4a8, np.float32, xq, xs, Wq, sw, (int(splitk),))
+
+
+def abs_terms(xq, xs, Wq, sw):
+    return _run(lib().oracle_abs_terms, np.float64, xq, xs, Wq, sw)
+
+
+def moe_w4a8(xq, xs, Wq, sw, idx, topk, x_per_slot, N, K):
+    nslots = idx.shape[0]
+    Y = np.empty((nslots, N), dtype=np.float32)
+    lib().oracle_moe_w4a8(_p(np.ascontiguousarray(xq)), _p(np.ascontiguousarray(xs)), _p(np.ascontiguousarray(Wq)),
+                          _p(np.ascontiguousarray(sw)), _p(np.ascontiguousarray(idx, dtype=np.int32)), _p(Y),
+                          nslots, topk, int(x_per_slot), N, K, _sd(sw))
+    return Y
+
+
+def gemv_b200_order(xq, xs, Wq, sw):
+    """fp32 in the B200 library's documented GEMV-family order (csrc/gemv_w4a8.cuh), for bit-exact checks."""
+    M, K = xq.shape
+    N = Wq.shape[0]
+    Y = np.empty((M, N), dtype=np.float32)
+    lib().oracle_gemv_b200_order(_p(np.ascontiguousarray(xq)), _p(np.ascontiguousarray(xs)),
+                                 _p(np.ascontiguousarray(Wq)), _p(np.ascontiguousarray(sw)), _p(Y), K, N, M, _sd(sw))
+    return Y
+
+
+# ---- seeded synthetic inputs of BASELINE.json's shapes ------------------------------------------------
+def make_weights(N, K, seed, scale_dtype=0):
+    """Packed int4 weights (every nibble uniform in 0..15, i.e. value uniform in [-8,7]) and group scales
+    |N(0, 0.02)|/7, fp32 or fp16."""
+    rng = np.random.default_rng(seed)
+    Wq = rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)
+    sw = (np.abs(rng.normal(0.0, 0.02, size=(N, K // QBLK))) / 7.0).astype(np.float32)
+    if scale_dtype == 1:
+        sw = sw.astype(np.float16)
+    return Wq, sw
+
+
+def make_activations(M, K, seed, outliers=False):
+    """x ~ N(0,1) float32; with outliers=True a random 1 % of the entries is multiplied by 20."""
+    rng = np.random.default_rng(seed)
+    X = rng.normal(0.0, 1.0, size=(M, K)).astype(np.float32)
+    if outliers:
+        mask = rng.random(size=(M, K)) < 0.01
+        X[mask] *= 20.0
+    return X

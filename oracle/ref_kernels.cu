@@ -1,0 +1,57 @@
+// Thin C-ABI wrapper around the reference's OWN kernel headers, compiled from where they lie
+// (-I<reference root>); no reference source is copied here.  TEST / BASELINE INFRASTRUCTURE ONLY:
+// the result (oracle/_ref/libref_kernels.so) is the reference's GPU code rebuilt for sm_100a, used
+// by the GPU parity tests as the bit-exact checker and by bench.py as the timed "reference kernels
+// on B200" baseline.  The shipped library never loads it.
+#include <cstdint>
+#include <cuda_runtime.h>
+#include "kernels/quantize_x.cuh"
+#include "kernels/gemv_w4a8.cuh"
+#include "kernels/gemm_batch.cuh"
+#include "kernels/gemm_mma.cuh"
+#include "kernels/gemm_mmq.cuh"
+#include "kernels/gemm_mmq_tmpl.cuh"
+#include "kernels/gemm_mmq_raster.cuh"
+
+#define REF_API extern "C" __attribute__((visibility("default")))
+static inline int ref_status() { return (int)cudaPeekAtLastError(); }
+
+REF_API int ref_quantize_x_q8(const float *X, int8_t *xq, float *xs, int32_t *xsum, int IN, int S, void *st) {
+    launch_quantize_x_q8(X, xq, xs, xsum, IN, S, (cudaStream_t)st); return ref_status();
+}
+REF_API int ref_gemv_w4a8(const int8_t *xq, const float *xs, const int32_t *xsum, const uint8_t *Wq, const void *sw,
+                          float *Y, int IN, int OUT, int S, int sd, void *st) {
+    launch_gemv_w4a8(xq, xs, xsum, Wq, sw, Y, IN, OUT, S, sd, (cudaStream_t)st); return ref_status();
+}
+REF_API int ref_gemv_w4a8_mlp2(const int8_t *xq, const float *xs, const int32_t *xsum, const uint8_t *Wq, const void *sw,
+                               float *Y, int IN, int OUT, int S, int sd, void *st) {
+    launch_gemv_w4a8_mlp<2>(xq, xs, xsum, Wq, sw, Y, IN, OUT, S, sd, (cudaStream_t)st); return ref_status();
+}
+REF_API int ref_gemv_w4a8_sb(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw,
+                             float *Y, int IN, int OUT, int S, int sd, void *st) {
+    launch_gemv_w4a8_sb(xq, xs, Wq, sw, Y, IN, OUT, S, sd, (cudaStream_t)st); return ref_status();
+}
+REF_API int ref_gemm_batch_w4a8(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw,
+                                float *Y, int IN, int OUT, int B, int sd, void *st) {
+    launch_gemm_batch_w4a8(xq, xs, Wq, sw, Y, IN, OUT, B, sd, (cudaStream_t)st); return ref_status();
+}
+REF_API int ref_gemm_mma_w4a8(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw,
+                              float *Y, int M, int N, int K, int sd, void *st) {
+    launch_gemm_mma_w4a8(X, xs, Wq, sw, Y, M, N, K, sd, (cudaStream_t)st); return ref_status();
+}
+REF_API int ref_gemm_mmq_w4a8(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw,
+                              float *Y, int M, int N, int K, int sd, void *st) {
+    launch_gemm_mmq_w4a8(X, xs, Wq, sw, Y, M, N, K, sd, (cudaStream_t)st); return ref_status();
+}
+REF_API int ref_gemm_mmq_256x64(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw,
+                                float *Y, int M, int N, int K, int sd, void *st) {
+    launch_gemm_mmq_tmpl<256, 64, 64, 4, 2>(X, xs, Wq, sw, Y, M, N, K, sd, (cudaStream_t)st); return ref_status();
+}
+REF_API int ref_gemm_mmq_raster_w4a8(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw,
+                                     float *Y, int M, int N, int K, int sd, int raster, int group, void *st) {
+    launch_gemm_mmq_raster_w4a8(X, xs, Wq, sw, Y, M, N, K, sd, raster, group, (cudaStream_t)st); return ref_status();
+}
+REF_API int ref_gemm_bm16_splitk(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw,
+                                 float *Y, int M, int N, int K, int sd, void *st) {
+    launch_gemm_bm16_splitk(X, xs, Wq, sw, Y, M, N, K, sd, (cudaStream_t)st); return ref_status();
+}
