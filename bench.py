@@ -1,0 +1,376 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A8 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Headline (BASELINE.json `metric`): HBM throughput of the W4A8 decode GEMV at M=1 on the
+Qwen3.5-27B-class MLP up/gate shape K=5120, N=17408 (BASELINE.json configs[1]); one step = one GEMV launch
+through the C ABI over the next of several distinct weight copies (more bytes than the 126 MB L2, so every
+step streams its weights from HBM).  `value` = algorithmic bytes / time with all inputs resident in HBM;
+`e2e` = the same product through w4a8_linear (quantize + GEMV) with HOST activations and outputs, the
+host<->device copies inside the timed region.  The M=2..16 sweep and the M=2048 prefill GEMM (quantize_x
+included) are reported in `extra`.  At N > 1 the weights are sharded along N (rows of Wq), every rank
+computes its slice and an NCCL all-gather reassembles Y (strong scaling: the total matrix is fixed).
+
+--impl reference times the CPU restatement of the reference path (oracle/, all host threads) on bounded
+samples of the same workload: the reference has no CPU build of its own and its CUDA kernels are reported,
+rebuilt for sm_100a, inside the default arm's `extra.reference_kernels_sm100a`.
+"""
+import argparse
+import ctypes
+import importlib
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+K_DIM, N_DIM = 5120, 17408
+L2_BYTES = 126 * 1024 * 1024
+NCU_TRAFFIC = {  # dram__bytes_read.sum + dram__bytes_write.sum per launch, from profiles/ (one ncu capture each)
+    "gemv_m1": 55.77e6,   # profiles/gemv_w4a8_m1_k5120_n17408.md
+}
+
+
+def load_package():
+    name = "dgx_serving_b200"
+    if name in sys.modules:
+        return sys.modules[name]
+    path = os.path.join(ROOT, "dgx-serving_b200", "__init__.py")
+    spec = importlib.util.spec_from_file_location(name, path, submodule_search_locations=[os.path.dirname(path)])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def load_oracle():
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle
+    oracle.lib()
+    return oracle
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops_sustained"]), "measured"
+    return 6650.0, 1400.0, "fallback"
+
+
+def gemv_bytes(M, N, K, scale_bytes=4):
+    """Algorithmic bytes of one GEMV launch: packed weights + scales + xq + xs + Y."""
+    nb = K // 32
+    return N * K // 2 + N * nb * scale_bytes + M * K + M * nb * 4 + M * N * 4
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.rows.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if r[1].replace(".", "").isdigit()]
+        reasons = []
+        for i, name in enumerate(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")):
+            if any(r[3 + i].lower().startswith("active") for r in self.rows):
+                reasons.append(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+# ---------------------------------------------------------------------------------------------------------
+def run_reference(args):
+    """CPU restatement of the reference path on all host threads; bounded samples of the same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    O = load_oracle()
+    cores = O.max_threads()
+    O.set_threads(cores)
+    Wq, sw = O.make_weights(N_DIM, K_DIM, seed=20260002)
+    X = O.make_activations(1, K_DIM, seed=20260102)
+    xq, xs, _ = O.quantize_x_q8(X)
+    per_step = max(1, int(os.environ.get("W4A8_REF_GEMVS_PER_STEP", "8")))
+    for _ in range(args.warmup):
+        O.gemm_mmq_w4a8(xq, xs, Wq, sw)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for _ in range(per_step):
+            O.gemm_mmq_w4a8(xq, xs, Wq, sw)
+    dt = time.perf_counter() - t0
+    launches = args.steps * per_step
+    gbps = gemv_bytes(1, N_DIM, K_DIM) * launches / dt / 1e9
+    line = {
+        "impl": "reference", "metric": "w4a8_gemv_m1_hbm_gbps", "value": gbps, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
+        "config": {"workload": "W4A8 decode GEMV M=1 K=5120 N=17408 (BASELINE configs[1])",
+                   "sample": "%d GEMVs per step" % per_step},
+        "cpu_baseline": {"value": gbps, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": "%d scalar-C GEMVs of the full shape (oracle/w4a8_oracle.c, OpenMP)" % launches},
+        "e2e": {"value": gbps, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the library has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    w = load_package()
+    w.lib()
+    sharded = importlib.import_module("dgx_serving_b200.sharded")
+    hbm_peak, bf16_peak, peak_kind = measured_peaks()
+
+    K, N = K_DIM, N_DIM
+    nb = K // 32
+    plan = sharded.shard_plan(N, world, w.shard_rows)
+    row0, rows = plan[rank]
+    shard_bytes = rows * (K // 2 + nb * 4)
+    nbuf = max(3, int(np.ceil(2.2 * L2_BYTES / shard_bytes)))
+    g = torch.Generator(device=dev)
+    g.manual_seed(20260002 + rank)
+    Wqs = [torch.randint(0, 256, (rows, K // 2), dtype=torch.uint8, device=dev, generator=g) for _ in range(nbuf)]
+    sws = [(torch.randn(rows, nb, device=dev, generator=g).abs() * (0.02 / 7.0)) for _ in range(nbuf)]
+    rng = np.random.default_rng(20260102)
+
+    def make_x(M, outliers=False):
+        X = rng.normal(0.0, 1.0, size=(M, K)).astype(np.float32)
+        if outliers:
+            X[rng.random(size=(M, K)) < 0.01] *= 20.0
+        Xh = torch.from_numpy(X).pin_memory()
+        Xd = Xh.to(dev)
+        xq = torch.empty((M, K), dtype=torch.int8, device=dev)
+        xs = torch.empty((M, nb), dtype=torch.float32, device=dev)
+        xsum = torch.empty((M, nb), dtype=torch.int32, device=dev)
+        w.launch_quantize_x_q8(Xd, xq, xs, xsum, K, M)
+        torch.cuda.synchronize()
+        return Xh, Xd, xq, xs, xsum
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    def time_steps(step_fn, steps, warmup, graph):
+        """step_fn(i, stream_handle) enqueues one step.  Returns ms for exactly `steps` steps (max over ranks)."""
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            for i in range(max(warmup, 3)):
+                step_fn(i, s.cuda_stream)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if graph:
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr, stream=s):
+                    for i in range(steps):
+                        step_fn(i, s.cuda_stream)
+                gr.replay()          # one untimed replay: graph upload
+                barrier()
+                e0.record(s)
+                gr.replay()
+                e1.record(s)
+            else:
+                barrier()
+                e0.record(s)
+                for i in range(steps):
+                    step_fn(i, s.cuda_stream)
+                e1.record(s)
+            torch.cuda.synchronize()
+            barrier()
+        return max_over_ranks(e0.elapsed_time(e1))
+
+    # ---- headline: GEMV M=1 (N-sharded + all-gather when world > 1) -------------------------------------
+    def gemv_case(M, steps, warmup):
+        Xh, Xd, xq, xs, xsum = make_x(M)
+        Yloc = torch.empty((M, rows), dtype=torch.float32, device=dev)
+
+        def step(i, st):
+            w.launch_gemv_w4a8_sb(xq, xs, Wqs[i % nbuf], sws[i % nbuf], Yloc, K, rows, M, 0, st)
+            if world > 1:
+                sharded.all_gather_columns(Yloc, plan)     # NCCL all-gather -> Y[M, N] on every rank
+        ms = time_steps(step, steps, warmup, graph=(world == 1))
+        total_bytes = gemv_bytes(M, N, K)          # all ranks together stream the whole matrix once per step
+        return ms, total_bytes * steps / (ms * 1e-3) / 1e9, (Xh, Xd, xq, xs, xsum)
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms, gbps, xin = gemv_case(1, args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+
+    # kernel-only time of this rank's GEMV (no collective), for the roofline of the dominant kernel
+    Xh, Xd, xq, xs, xsum = xin
+    Yloc = torch.empty((1, rows), dtype=torch.float32, device=dev)
+    ms_k = time_steps(lambda i, st: w.launch_gemv_w4a8_sb(xq, xs, Wqs[i % nbuf], sws[i % nbuf], Yloc, K, rows, 1, 0, st),
+                      args.steps, args.warmup, graph=True)
+    per_launch_us = ms_k * 1e3 / args.steps
+    achieved = gemv_bytes(1, rows, K) / (per_launch_us * 1e-6) / 1e9
+
+    # ---- e2e: host fp32 activations in, host fp32 outputs back, through w4a8_linear ------------------------
+    Yh = torch.empty((1, rows), dtype=torch.float32).pin_memory()
+    e2e_steps = max(10, min(args.steps, 200))
+
+    def e2e_step(i, st):
+        Xd.copy_(Xh, non_blocking=True)
+        w.linear(Xd, xq, xs, xsum, Wqs[i % nbuf], sws[i % nbuf], Yloc, 1, rows, K, 0, 0, st)
+        if world > 1:
+            pass  # the gathered row stays on the device; each rank returns its slice to its host
+        Yh.copy_(Yloc, non_blocking=True)
+        torch.cuda.current_stream().synchronize()     # the caller reads Y on the host every step
+    ms_e = time_steps(e2e_step, e2e_steps, 3, graph=False)
+    e2e_gbps = gemv_bytes(1, N, K) * e2e_steps / (ms_e * 1e-3) / 1e9
+
+    extra = {}
+    if world == 1:
+        # ---- sweep M = 2..16 on the same shape ------------------------------------------------------------
+        sweep = {"1": {"us": per_launch_us, "gbps": achieved, "frac_of_measured_hbm": achieved / hbm_peak,
+                       "frac_of_8tbs": achieved / 8000.0}}
+        for M in (2, 4, 8, 16):
+            ms_m, gb_m, _ = gemv_case(M, max(20, args.steps // 2), 3)
+            us = ms_m * 1e3 / max(20, args.steps // 2)
+            sweep[str(M)] = {"us": us, "gbps": gb_m, "frac_of_measured_hbm": gb_m / hbm_peak, "frac_of_8tbs": gb_m / 8000.0}
+        extra["gemv_sweep_k5120_n17408"] = sweep
+        # ---- prefill GEMM, quantize_x inside the timed region (BASELINE configs[3]) ------------------------
+        gemm = {}
+        for M in (512, 2048):
+            Xh2, Xd2, xq2, xs2, xsum2 = make_x(M, outliers=True)
+            Y2 = torch.empty((M, N), dtype=torch.float32, device=dev)
+            st_n = 5
+            ms_g = time_steps(lambda i, st: w.linear(Xd2, xq2, xs2, xsum2, Wqs[i % nbuf], sws[i % nbuf], Y2, M, N, K, 0, 0, st),
+                              st_n, 3, graph=False)
+            w.device_status()
+            us = ms_g * 1e3 / st_n
+            tops = 2.0 * M * N * K / (us * 1e-6) / 1e12
+            gemm[str(M)] = {"us": us, "int8_tops": tops, "frac_of_nominal_4500": tops / 4500.0,
+                            "frac_of_2x_measured_bf16": tops / (2.0 * bf16_peak)}
+            del Y2
+        extra["gemm_quantize_included_k5120_n17408"] = gemm
+        # ---- the reference's own kernels rebuilt for sm_100a, same buffers (not part of the library) -------
+        refp = os.path.join(ROOT, "oracle", "_ref", "libref_kernels.so")
+        if os.path.exists(refp):
+            ref = ctypes.CDLL(refp)
+            P = lambda t: ctypes.c_void_p(t.data_ptr())
+            ms_r = time_steps(lambda i, st: ref.ref_gemv_w4a8_mlp2(P(xq), P(xs), P(xsum), P(Wqs[i % nbuf]), P(sws[i % nbuf]), P(Yloc),
+                                                                  K, N, 1, 0, ctypes.c_void_p(st)), args.steps, 3, graph=True)
+            us_r = ms_r * 1e3 / args.steps
+            Xh2, Xd2, xq2, xs2, xsum2 = make_x(2048, outliers=True)
+            Y2 = torch.empty((2048, N), dtype=torch.float32, device=dev)
+
+            def ref_gemm(i, st):
+                ref.ref_quantize_x_q8(P(Xd2), P(xq2), P(xs2), P(xsum2), K, 2048, ctypes.c_void_p(st))
+                ref.ref_gemm_mmq_w4a8(P(xq2), P(xs2), P(Wqs[i % nbuf]), P(sws[i % nbuf]), P(Y2), 2048, N, K, 0, ctypes.c_void_p(st))
+            ms_rg = time_steps(ref_gemm, 3, 3, graph=False)
+            extra["reference_kernels_sm100a"] = {
+                "gemv_w4a8_mlp2_m1": {"us": us_r, "gbps": gemv_bytes(1, N, K) / (us_r * 1e-6) / 1e9},
+                "quantize+gemm_mmq_m2048": {"us": ms_rg * 1e3 / 3, "int8_tops": 2.0 * 2048 * N * K / (ms_rg / 3 * 1e-3) / 1e12}}
+            del Y2
+
+    cpu_baseline = None
+    if world == 1:
+        O = load_oracle()
+        cores = O.max_threads()
+        O.set_threads(cores)
+        Wq_h, sw_h = Wqs[0].cpu().numpy(), sws[0].cpu().numpy()
+        xq_h, xs_h = xq.cpu().numpy(), xs.cpu().numpy()
+        O.gemm_mmq_w4a8(xq_h, xs_h, Wq_h, sw_h)
+        n, t0 = 0, time.perf_counter()
+        while time.perf_counter() - t0 < 10.0:
+            O.gemm_mmq_w4a8(xq_h, xs_h, Wq_h, sw_h)
+            n += 1
+        dt = time.perf_counter() - t0
+        cpu_baseline = {"value": gemv_bytes(1, N, K) * n / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+                        "sample": "%d scalar-C GEMVs of the full M=1 shape in %.1f s (oracle/w4a8_oracle.c, OpenMP)" % (n, dt)}
+
+    if rank == 0:
+        line = {
+            "metric": "w4a8_gemv_m1_hbm_gbps", "value": gbps, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "i8", "data": "synthetic",
+            "config": {"workload": "W4A8 decode GEMV M=1 K=5120 N=17408, int4 group-32 weights + fp32 scales (BASELINE configs[1])",
+                       "parallelism": "n-shard x%d + nccl all-gather" % world if world > 1 else "single GPU",
+                       "l2": "rotating %d distinct weight copies per rank (%.0f MB > 126 MB L2)" % (nbuf, nbuf * shard_bytes / 1e6),
+                       "launch": "CUDA graph of %d launches" % args.steps if world == 1 else "stream launches + NCCL"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                         "traffic": NCU_TRAFFIC["gemv_m1"] if world == 1 else None, "peak_kind": "of " + peak_kind,
+                         "kernel": "gemv_w4a8 M=1, rank-local slice of %d rows" % rows, "us_per_launch": per_launch_us,
+                         "algorithmic_bytes_per_launch": gemv_bytes(1, rows, K), "frac_of_nominal_8tbs": achieved / 8000.0},
+            "cpu_baseline": cpu_baseline,
+            "e2e": {"value": e2e_gbps, "unit": "GB/s", "h2d_bytes_per_step": K * 4, "d2h_bytes_per_step": rows * 4,
+                    "ms_per_step": ms_e / e2e_steps, "path": "pinned host X -> w4a8_linear (quantize_x + gemv) -> pinned host Y"},
+            "gpu_launches": args.steps * (1 if world == 1 else 1),
+            "clocks": clocks,
+            "extra": extra,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

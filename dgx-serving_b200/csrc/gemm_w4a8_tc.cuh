@@ -12,10 +12,11 @@
 //               [128 x 64 B] per K-tile of 128 elements, each behind its own mbarrier ring
 //   warp 1      MMA issuer: one tcgen05.mma kind::i8 (128x128x32) per group into one of four 128-column
 //               accumulator buffers in tensor memory; tcgen05.commit signals operand release / result ready
-//   warps 2-5   expand int4 -> int8 (as 16*(w-8), see unpack8_x16) from the packed stage into the swizzled
+//   warps 2-3   expand int4 -> int8 (as 16*(w-8), see unpack8_x16) from the packed stage into the swizzled
 //               K-major operand stage the MMA reads (generic-proxy writes + fence.proxy.async), and stage
 //               the weight scales of the K-tile (pre-multiplied by the exact 1/16) transposed to [group][n]
-//   warps 6-13  epilogue: tcgen05.ld the int32 group dots (lane = row, 64 columns per warp), convert,
+//   warps 4-11  epilogue: tcgen05.ld the int32 group dots (lane = row, 64 columns per warp, loaded as two
+//               32-column chunks so that one chunk's load is in flight while the other is processed), convert,
 //               scale and accumulate in registers; store the fp32 tile at the end of the K loop
 // Ragged M, N and a last partial K-tile are handled by TMA zero fill plus guards on scales and stores.
 #pragma once
@@ -37,8 +38,10 @@ constexpr int A_STAGE = BM * KT;       // 16 KB
 constexpr int BP_STAGE = BN * KT / 2;  // 8 KB
 constexpr int B8_STAGE = BN * KT;      // 16 KB
 constexpr int SW_STAGE = GPK * BN * 4; // 2 KB
-constexpr int DEQ_WARPS = 4, EPI_WARPS = 8;
-constexpr int THREADS = (2 + DEQ_WARPS + EPI_WARPS) * 32;  // 448
+constexpr int DEQ_WARPS = 2, EPI_WARPS = 8;
+constexpr int EPI_COLS = BN / (EPI_WARPS / 4);  // accumulator columns per epilogue warp (64)
+constexpr int EPI_CH = EPI_COLS / 2;           // columns per tcgen05.ld chunk (32)
+constexpr int THREADS = (2 + DEQ_WARPS + EPI_WARPS) * 32;  // 384: up to 168 registers per thread
 constexpr int OFF_A = 0;
 constexpr int OFF_B8 = OFF_A + SA * A_STAGE;
 constexpr int OFF_BP = OFF_B8 + S8 * B8_STAGE;
@@ -61,6 +64,73 @@ struct Ring {
     }
 };
 
+// ---- epilogue arithmetic on one chunk of NC accumulator columns ------------------------------------
+// d[j] = 16 * D[m, n_j, b] (int32 from tensor memory), x = xs[m,b], sw16[j] = sw[n_j,b] / 16.
+// Evaluates t = (float)d * x (rounded), acc = fma(t, sw16, acc): bit-identical to the reference's
+// (float)c * xs * sw accumulation (kernels/gemm_mmq.cuh:104-105) because the two factors of 16 are exact.
+//   EPI bit 0: int -> float by adding the integer to the bit pattern of 1.5 * 2^23 and subtracting that
+//              constant as a float (exact for |d| < 2^22; here |d| <= 520,192) instead of cvt.rn.f32.s32
+//   EPI bit 1: packed two-wide fp32 multiply / fma (mul.rn.f32x2, fma.rn.f32x2): same IEEE results per lane
+__device__ __forceinline__ float cvt_exact(uint32_t d, bool magic) {
+    if (magic) return __int_as_float((int)d + 0x4B400000) - 12582912.0f;
+    return __int2float_rn((int)d);
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+template <int EPI, int NC>
+__device__ __forceinline__ void epi_chunk(const uint32_t (&d)[NC], float x, const float *__restrict__ sw16, float *__restrict__ acc) {
+    constexpr bool MAGIC = (EPI & 1) != 0, PACKED = (EPI & 2) != 0;
+    if (PACKED) {
+        const uint64_t xx = pack_f32x2(x, x);
+#pragma unroll
+        for (int j4 = 0; j4 < NC / 4; j4++) {
+            const float4 s4 = *reinterpret_cast<const float4 *>(sw16 + j4 * 4);
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int j = j4 * 4 + 2 * h;
+                const uint64_t f2 = pack_f32x2(cvt_exact(d[j], MAGIC), cvt_exact(d[j + 1], MAGIC));
+                const uint64_t s2 = h == 0 ? pack_f32x2(s4.x, s4.y) : pack_f32x2(s4.z, s4.w);
+                uint64_t a2 = pack_f32x2(acc[j], acc[j + 1]);
+                uint64_t t2;
+                asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(t2) : "l"(f2), "l"(xx));
+                asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(a2) : "l"(t2), "l"(s2));
+                unpack_f32x2(a2, acc[j], acc[j + 1]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j4 = 0; j4 < NC / 4; j4++) {
+            const float4 s4 = *reinterpret_cast<const float4 *>(sw16 + j4 * 4);
+            const int j = j4 * 4;
+            const float t0 = cvt_exact(d[j + 0], MAGIC) * x;
+            const float t1 = cvt_exact(d[j + 1], MAGIC) * x;
+            const float t2 = cvt_exact(d[j + 2], MAGIC) * x;
+            const float t3 = cvt_exact(d[j + 3], MAGIC) * x;
+            acc[j + 0] = fmaf(t0, s4.x, acc[j + 0]);
+            acc[j + 1] = fmaf(t1, s4.y, acc[j + 1]);
+            acc[j + 2] = fmaf(t2, s4.z, acc[j + 2]);
+            acc[j + 3] = fmaf(t3, s4.w, acc[j + 3]);
+        }
+    }
+}
+// Debug path: the exact group dots of one chunk to Dout[m][n][b] (undoing the factor 16).
+template <int NC>
+__device__ __forceinline__ void epi_dump(const uint32_t (&d)[NC], int32_t *__restrict__ Dout, int m, int M, int ncol0, int N,
+                                         int nb, int b) {
+    if (m >= M) return;
+#pragma unroll
+    for (int j = 0; j < NC; j++) {
+        const int n = ncol0 + j;
+        if (n < N) Dout[((size_t)m * N + n) * nb + b] = ((int)d[j]) >> 4;
+    }
+}
+
 // One unit of work = (output tile, K split).  Tiles are numbered M-fastest so that CTAs running at the
 // same time share weight tiles in L2; split s covers groups [s*gsplit, min(nb, (s+1)*gsplit)).
 struct Work {
@@ -79,7 +149,7 @@ __device__ __forceinline__ Work decode_work(int w, int m_tiles, int num_tiles, i
     return k;
 }
 
-template <typename ST, bool DUMP>
+template <typename ST, bool DUMP, int EPI>
 __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
     const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
     const float *__restrict__ xs, const ST *__restrict__ sw, float *__restrict__ Y, int32_t *__restrict__ Dout,
@@ -179,15 +249,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
         }
     } else if (warp < 2 + DEQ_WARPS) {
         // ---------------- int4 -> int8 expansion + weight-scale staging ----------------
-        const int dt = tid - 64;  // 0..127
+        const int dt = tid - 64;  // 0..DEQ_WARPS*32-1
         Ring rb(SB), r8(S8), rs(SS);
         bool ok = true;
         for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
             const Work wk = decode_work(wi, m_tiles, num_tiles, nb, gsplit);
             const int n0 = wk.n0;
             for (int kt = 0; kt < wk.nkt && ok; kt++) {
-                bool w = ptx::mbar_wait(BAR(BP_FULL + rb.stage), rb.phase) && ptx::mbar_wait(BAR(B8_EMPTY + r8.stage), r8.phase ^ 1u);
-                if (!__all_sync(0xffffffffu, w)) { dev_set_error(ERR_DEQUANT | 1); ok = false; break; }
+                bool w = ptx::mbar_wait_warp(BAR(BP_FULL + rb.stage), rb.phase) && ptx::mbar_wait_warp(BAR(B8_EMPTY + r8.stage), r8.phase ^ 1u);
+                if (!w) { dev_set_error(ERR_DEQUANT | 1); ok = false; break; }
                 const unsigned char *src = base_ptr + OFF_BP + rb.stage * BP_STAGE;
                 unsigned char *dst = base_ptr + OFF_B8 + r8.stage * B8_STAGE;
 #pragma unroll
@@ -206,16 +276,19 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
                 rb.advance();
                 r8.advance();
 
-                w = ptx::mbar_wait(BAR(SW_EMPTY + rs.stage), rs.phase ^ 1u);
-                if (!__all_sync(0xffffffffu, w)) { dev_set_error(ERR_DEQUANT | 2); ok = false; break; }
+                w = ptx::mbar_wait_warp(BAR(SW_EMPTY + rs.stage), rs.phase ^ 1u);
+                if (!w) { dev_set_error(ERR_DEQUANT | 2); ok = false; break; }
                 float *ssw = reinterpret_cast<float *>(base_ptr + OFF_SW + rs.stage * SW_STAGE);
-                const int n = n0 + dt;
 #pragma unroll
-                for (int g = 0; g < GPK; g++) {
-                    const int b = wk.g0 + kt * GPK + g;
-                    float v = 0.f;
-                    if (!DUMP && n < N && b < wk.g1) v = sval(sw[(size_t)n * nb + b]) * 0.0625f;  // exact: undoes the 16x of the expansion
-                    ssw[g * BN + dt] = v;
+                for (int r = 0; r < BN / (DEQ_WARPS * 32); r++) {
+                    const int nl = dt + r * DEQ_WARPS * 32, n = n0 + nl;
+#pragma unroll
+                    for (int g = 0; g < GPK; g++) {
+                        const int b = wk.g0 + kt * GPK + g;
+                        float v = 0.f;
+                        if (!DUMP && n < N && b < wk.g1) v = sval(sw[(size_t)n * nb + b]) * 0.0625f;  // exact: undoes the 16x of the expansion
+                        ssw[g * BN + nl] = v;
+                    }
                 }
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(BAR(SW_FULL + rs.stage));
@@ -224,9 +297,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
         }
     } else {
         // ---------------- epilogue ----------------
-        const int ew = warp - (2 + DEQ_WARPS);  // 0..7
+        const int ew = warp - (2 + DEQ_WARPS);  // 0..EPI_WARPS-1
         const int quad = warp & 3;              // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
-        const int half = ew >> 2;               // columns [64*half, 64*half+64)
+        const int col0 = (ew >> 2) * EPI_COLS;  // this warp's accumulator columns [col0, col0 + EPI_COLS)
         Ring rs(SS), rt(TB);
         bool ok = true;
         for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
@@ -236,9 +309,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
             // a warp whose 32 rows all lie beyond M only keeps the barriers moving
             const bool rows_live = (m0 + quad * 32) < M;
             const float *xsrow = xs + (size_t)(m < M ? m : 0) * nb;
-            float acc[64];
+            float acc[EPI_COLS];
 #pragma unroll
-            for (int j = 0; j < 64; j++) acc[j] = 0.f;
+            for (int j = 0; j < EPI_COLS; j++) acc[j] = 0.f;
             float xnext[GPK];
 #pragma unroll
             for (int g = 0; g < GPK; g++) xnext[g] = (!DUMP && m < M && wk.g0 + g < wk.g1) ? xsrow[wk.g0 + g] : 0.f;
@@ -250,60 +323,47 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
                     const int b = wk.g0 + (kt + 1) * GPK + g;
                     xnext[g] = (!DUMP && m < M && b < wk.g1) ? xsrow[b] : 0.f;
                 }
-                bool w = ptx::mbar_wait(BAR(SW_FULL + rs.stage), rs.phase);
-                if (!__all_sync(0xffffffffu, w)) { dev_set_error(ERR_EPILOGUE | 1); ok = false; break; }
-                const float *ssw = reinterpret_cast<const float *>(base_ptr + OFF_SW + rs.stage * SW_STAGE) + half * 64;
                 const int ng = min(GPK, wk.g1 - (wk.g0 + kt * GPK));
+                const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16) + col0;
+                // The 2*ng chunks (EPI_CH columns each) of this K-tile are software-pipelined: the tcgen05.ld of
+                // chunk i+1 is in flight while chunk i is converted and accumulated.  d0 holds the first half of
+                // this warp's columns of a group, d1 the second.
+                uint32_t d0[EPI_CH], d1[EPI_CH];
+                bool w = ptx::mbar_wait_warp(BAR(TM_FULL + rt.stage), rt.phase);
+                if (!w) { dev_set_error(ERR_EPILOGUE | 2); ok = false; break; }
+                ptx::tc_fence_after_sync();
+                if (rows_live) ptx::tmem_ld(tlane + rt.stage * BN, d0);
+                w = ptx::mbar_wait_warp(BAR(SW_FULL + rs.stage), rs.phase);
+                if (!w) { dev_set_error(ERR_EPILOGUE | 1); ok = false; break; }
+                const float *ssw = reinterpret_cast<const float *>(base_ptr + OFF_SW + rs.stage * SW_STAGE) + col0;
 #pragma unroll
                 for (int g = 0; g < GPK; g++) {
                     if (g < ng) {
-                        w = ptx::mbar_wait(BAR(TM_FULL + rt.stage), rt.phase);
-                        if (!__all_sync(0xffffffffu, w)) { dev_set_error(ERR_EPILOGUE | 2); ok = false; break; }
-                        ptx::tc_fence_after_sync();
-                        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + rt.stage * BN + half * 64;
-                        const float x = xcur[g];
-                        if (!rows_live) {
-                            ptx::tc_fence_before_sync();
-                            __syncwarp();
-                            if (lane == 0) ptx::mbar_arrive(BAR(TM_EMPTY + rt.stage));
-                        } else {
-#pragma unroll
-                        for (int c = 0; c < 2; c++) {
-                            uint32_t d[32];
-                            ptx::tmem_ld_32x32b_x32(taddr + c * 32, d);
-                            ptx::tmem_ld_wait();
-                            if (c == 1) {  // both halves are in registers: the buffer may be overwritten
-                                ptx::tc_fence_before_sync();
-                                __syncwarp();
-                                if (lane == 0) ptx::mbar_arrive(BAR(TM_EMPTY + rt.stage));
-                            }
-                            if (DUMP) {
-                                if (m < M) {
-                                    const int b = wk.g0 + kt * GPK + g;
-#pragma unroll
-                                    for (int j = 0; j < 32; j++) {
-                                        const int n = n0 + half * 64 + c * 32 + j;
-                                        if (n < N) Dout[((size_t)m * N + n) * nb + b] = ((int)d[j]) >> 4;
-                                    }
-                                }
-                            } else {
-#pragma unroll
-                                for (int j4 = 0; j4 < 8; j4++) {
-                                    const float4 s4 = *reinterpret_cast<const float4 *>(ssw + g * BN + c * 32 + j4 * 4);
-                                    const int j = c * 32 + j4 * 4;
-                                    float t0 = __int2float_rn((int)d[j4 * 4 + 0]) * x;
-                                    float t1 = __int2float_rn((int)d[j4 * 4 + 1]) * x;
-                                    float t2 = __int2float_rn((int)d[j4 * 4 + 2]) * x;
-                                    float t3 = __int2float_rn((int)d[j4 * 4 + 3]) * x;
-                                    acc[j + 0] = fmaf(t0, s4.x, acc[j + 0]);
-                                    acc[j + 1] = fmaf(t1, s4.y, acc[j + 1]);
-                                    acc[j + 2] = fmaf(t2, s4.z, acc[j + 2]);
-                                    acc[j + 3] = fmaf(t3, s4.w, acc[j + 3]);
-                                }
-                            }
+                        const int b = wk.g0 + kt * GPK + g;
+                        const uint32_t tcur = tlane + rt.stage * BN;
+                        // ---- first half: wait for it, start the second half's load, then compute
+                        ptx::tmem_ld_wait();
+                        if (rows_live) ptx::tmem_ld(tcur + EPI_CH, d1);
+                        if (rows_live) {
+                            if (DUMP) epi_dump<EPI_CH>(d0, Dout, m, M, n0 + col0, N, nb, b);
+                            else epi_chunk<EPI, EPI_CH>(d0, xcur[g], ssw + g * BN, acc);
                         }
-                        }
+                        // ---- second half: wait, release the accumulator buffer, start the next group's load
+                        ptx::tmem_ld_wait();
+                        ptx::tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(BAR(TM_EMPTY + rt.stage));
                         rt.advance();
+                        if (g + 1 < ng) {
+                            w = ptx::mbar_wait_warp(BAR(TM_FULL + rt.stage), rt.phase);
+                            if (!w) { dev_set_error(ERR_EPILOGUE | 3); ok = false; break; }
+                            ptx::tc_fence_after_sync();
+                            if (rows_live) ptx::tmem_ld(tlane + rt.stage * BN, d0);
+                        }
+                        if (rows_live) {
+                            if (DUMP) epi_dump<EPI_CH>(d1, Dout, m, M, n0 + col0 + EPI_CH, N, nb, b);
+                            else epi_chunk<EPI, EPI_CH>(d1, xcur[g], ssw + g * BN + EPI_CH, acc + EPI_CH);
+                        }
                     }
                 }
                 __syncwarp();
@@ -311,15 +371,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
                 rs.advance();
             }
             if (!DUMP && ok && m < M) {
-                float *yrow = Y + (size_t)wk.split * ((size_t)M * N) + (size_t)m * N + n0 + half * 64;
-                const int nleft = N - (n0 + half * 64);
-                if (nleft >= 64 && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0)) {
+                float *yrow = Y + (size_t)wk.split * ((size_t)M * N) + (size_t)m * N + n0 + col0;
+                const int nleft = N - (n0 + col0);
+                if (nleft >= EPI_COLS && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0)) {
 #pragma unroll
-                    for (int j = 0; j < 64; j += 4)
+                    for (int j = 0; j < EPI_COLS; j += 4)
                         *reinterpret_cast<float4 *>(yrow + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 64; j++)
+                    for (int j = 0; j < EPI_COLS; j++)
                         if (j < nleft) yrow[j] = acc[j];
                 }
             }
@@ -380,15 +440,15 @@ inline int make_tmap_u8(CUtensorMap *tm, const void *ptr, uint64_t row_bytes, ui
     return W4A8_OK;
 }
 
-template <typename ST, bool DUMP>
-inline int launch_tc_t(const int8_t *X, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int32_t *D,
+template <typename ST, bool DUMP, int EPI>
+inline int launch_tc_e(const int8_t *X, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int32_t *D,
                        int M, int N, int K, int nsplit, int gsplit, cudaStream_t st) {
     CUtensorMap tmA, tmB;
     int rc = make_tmap_u8(&tmA, X, (uint64_t)K, (uint64_t)M, KT, BM, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != W4A8_OK) return rc;
     rc = make_tmap_u8(&tmB, Wq, (uint64_t)K / 2, (uint64_t)N, KT / 2, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != W4A8_OK) return rc;
-    auto kern = gemm_w4a8_tc_kernel<ST, DUMP>;
+    auto kern = gemm_w4a8_tc_kernel<ST, DUMP, EPI>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -403,6 +463,27 @@ inline int launch_tc_t(const int8_t *X, const float *xs, const uint8_t *Wq, cons
 }
 
 // Needs X and Wq 16-byte aligned (TMA global address rule); the caller checks.
+// Epilogue arithmetic variant (see epi_chunk): all variants give identical bits.  W4A8_GEMM_EPI overrides the
+// default for measurements (0 cvt, 1 magic-number conversion, 2 cvt + f32x2, 3 magic + f32x2).
+inline int epi_variant() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("W4A8_GEMM_EPI");
+        v = e ? atoi(e) & 3 : 2;
+    }
+    return v;
+}
+template <typename ST, bool DUMP>
+inline int launch_tc_t(const int8_t *X, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int32_t *D,
+                       int M, int N, int K, int nsplit, int gsplit, cudaStream_t st) {
+    switch (DUMP ? 0 : epi_variant()) {
+        case 1: return launch_tc_e<ST, DUMP, 1>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
+        case 2: return launch_tc_e<ST, DUMP, 2>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
+        case 3: return launch_tc_e<ST, DUMP, 3>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
+        default: return launch_tc_e<ST, DUMP, 0>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
+    }
+}
+
 // nsplit = 1: Y is the output.  nsplit > 1: Y is the [nsplit][M][N] partial-sum workspace and gsplit the
 // number of groups per split.
 inline int launch_tc(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int M, int N, int K,

@@ -36,11 +36,61 @@ __device__ __forceinline__ uint4 ldg_w16(const uint8_t *p, bool a16) {
     return make_uint4(q[0], q[1], q[2], q[3]);
 }
 
-// MT  activation rows per pass (1..4), U = groups per lane loaded before any is consumed.
+// MT  activation rows per pass (1..4), U = groups per lane loaded as one batch.
+// Persistent CTAs: the grid is sized to the device (a few CTAs per SM) and every CTA owns a contiguous
+// range of output rows, so the activations are staged once per CTA, not once per 8 rows.  Warp w of the
+// CTA takes rows r0+w, r0+w+8, ...; the (row, batch) items of a warp form one flat sequence that is
+// software-pipelined: the 128-bit weight loads and scale loads of item i+1 are issued before item i is
+// unpacked and accumulated, so every lane keeps two batches of loads in flight.
 // Shared memory: the MT activation rows, re-ordered once per CTA so that every group is two 16-byte
 // pieces [e0 o0 e1 o1] and [e2 o2 e3 o3] (ew/ow = even/odd elements of the w-th 8-element chunk), the
 // order unpack8_x16 produces for the weights; the pieces live in two planes so that consecutive lanes
 // read consecutive 16-byte words (no bank conflicts).  Then xs[MT][nb].
+template <int U, typename ST>
+struct GemvBatch {
+    uint4 w[U];
+    float s[U];
+};
+
+template <int U, typename ST>
+__device__ __forceinline__ void gemv_load_batch(GemvBatch<U, ST> &bt, const uint8_t *__restrict__ wrow,
+                                                const ST *__restrict__ swrow, int slot0, int lane, int nb, bool a16) {
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        const int b = lane + 32 * (slot0 + u);
+        if (b < nb) { bt.w[u] = ldg_w16(wrow + 16 * b, a16); bt.s[u] = sval(swrow[b]); }
+        else { bt.w[u] = make_uint4(0, 0, 0, 0); bt.s[u] = 0.f; }
+    }
+}
+
+template <int MT, int U, typename ST>
+__device__ __forceinline__ void gemv_compute_batch(const GemvBatch<U, ST> &bt, float (&acc)[MT], const uint4 *plane0,
+                                                   const uint4 *plane1, const float *sxs, int slot0, int lane, int nb) {
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        const int b = lane + 32 * (slot0 + u);
+        if (b < nb) {
+            uint32_t e0, o0, e1, o1, e2, o2, e3, o3;
+            unpack8_x16(bt.w[u].x, e0, o0); unpack8_x16(bt.w[u].y, e1, o1);
+            unpack8_x16(bt.w[u].z, e2, o2); unpack8_x16(bt.w[u].w, e3, o3);
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                const uint4 xa = plane0[m * nb + b], xb = plane1[m * nb + b];
+                int d = __dp4a((int)xa.x, (int)e0, 0);
+                d = __dp4a((int)xa.y, (int)o0, d);
+                d = __dp4a((int)xa.z, (int)e1, d);
+                d = __dp4a((int)xa.w, (int)o1, d);
+                d = __dp4a((int)xb.x, (int)e2, d);
+                d = __dp4a((int)xb.y, (int)o2, d);
+                d = __dp4a((int)xb.z, (int)e3, d);
+                d = __dp4a((int)xb.w, (int)o3, d);      // d = 16 * D[m,o,b], exact
+                const float sc = (sxs[m * nb + b] * bt.s[u]) * 0.0625f;   // exact 1/16
+                acc[m] = fmaf(sc, (float)d, acc[m]);
+            }
+        }
+    }
+}
+
 template <int MT, int U, typename ST>
 __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_dp4a_kernel(
     const int8_t *__restrict__ xq, const float *__restrict__ xs, const uint8_t *__restrict__ Wq,
@@ -63,85 +113,67 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_dp4a_kernel(
     float *sxs = reinterpret_cast<float *>(plane1 + (size_t)MT * nb);  // [MT][nb]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int o = blockIdx.x * GEMV_WARPS + warp;
-    const bool row_ok = o < OUT;
-    const uint8_t *wrow = Wq + (size_t)(row_ok ? o : 0) * (IN / 2);
-    const ST *swrow = sw + (size_t)(row_ok ? o : 0) * nb;
+    // rows [r0, r1) of this CTA: a balanced contiguous partition of OUT over gridDim.x
+    const int r0 = (int)(((long)OUT * blockIdx.x) / gridDim.x), r1 = (int)(((long)OUT * (blockIdx.x + 1)) / gridDim.x);
+    const int nbatch = ((nb + 31) / 32 + U - 1) / U;                // batches per row
+    const int nrows_w = (r1 - r0 - warp + GEMV_WARPS - 1) / GEMV_WARPS;   // rows of this warp (may be <= 0)
+    const int nitems = nrows_w > 0 ? nrows_w * nbatch : 0;
+    const size_t wpitch = (size_t)(IN / 2);
 
-    // First batch of weight loads goes out before the activations are staged.
-    uint4 wv[U];
-    float sv[U];
-#pragma unroll
-    for (int u = 0; u < U; u++) {
-        const int b = lane + 32 * u;
-        if (row_ok && b < nb) { wv[u] = ldg_w16(wrow + 16 * b, w_a16); sv[u] = sval(swrow[b]); }
-        else { wv[u] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u); sv[u] = 0.f; }
-    }
+    // The first batch of weight loads goes out before the activations are staged.
+    GemvBatch<U, ST> ba, bb;
+    if (nitems > 0) gemv_load_batch<U, ST>(ba, Wq + (size_t)(r0 + warp) * wpitch, sw + (size_t)(r0 + warp) * nb, 0, lane, nb, w_a16);
 
     // Stage activations: one task = one 8-element chunk (two 4-byte loads, like the reference's x0/x1).
-    for (int t = tid; t < MT * (IN / 8); t += GEMV_WARPS * 32) {
-        const int m = t / (IN / 8), c = t % (IN / 8);   // chunk c of row m
-        uint32_t x0 = 0, x1 = 0;
-        if (m < S) {
-            const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + (size_t)m * IN + 8 * c);
-            x0 = src[0]; x1 = src[1];
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+        for (int c = tid; c < IN / 8; c += GEMV_WARPS * 32) {
+            uint32_t x0 = 0, x1 = 0;
+            if (m < S) {
+                const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + (size_t)m * IN + 8 * c);
+                x0 = src[0]; x1 = src[1];
+            }
+            uint32_t e, od;
+            split_even_odd(x0, x1, e, od);
+            const int b = c >> 2, w = c & 3;
+            uint2 *dst = reinterpret_cast<uint2 *>((w < 2 ? plane0 : plane1) + (size_t)m * nb + b) + (w & 1);
+            *dst = make_uint2(e, od);
         }
-        uint32_t e, od;
-        split_even_odd(x0, x1, e, od);
-        const int b = c >> 2, w = c & 3;
-        uint2 *dst = reinterpret_cast<uint2 *>((w < 2 ? plane0 : plane1) + (size_t)m * nb + b) + (w & 1);
-        *dst = make_uint2(e, od);
-    }
-    for (int t = tid; t < MT * nb; t += GEMV_WARPS * 32) {
-        const int m = t / nb, b = t % nb;
-        sxs[t] = (m < S) ? xs[(size_t)m * nb + b] : 0.f;
+        for (int b = tid; b < nb; b += GEMV_WARPS * 32) sxs[m * nb + b] = (m < S) ? xs[(size_t)m * nb + b] : 0.f;
     }
     __syncthreads();
-    if (!row_ok) return;
 
     float acc[MT];
 #pragma unroll
     for (int m = 0; m < MT; m++) acc[m] = 0.f;
 
-    for (int i0 = 0; i0 * 32 < nb; i0 += U) {
-        if (i0 > 0) {
+    // item i: row = r0 + warp + 8*(i / nbatch), batch = i % nbatch.  Two items per trip so that the two
+    // register buffers alternate without copies.
+    int row = r0 + warp, batch = 0;
+    auto advance = [&](int &r, int &bi) { if (++bi == nbatch) { bi = 0; r += GEMV_WARPS; } };
+    auto finish_row = [&](int r) {
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-                const int b = lane + 32 * (i0 + u);
-                if (b < nb) { wv[u] = ldg_w16(wrow + 16 * b, w_a16); sv[u] = sval(swrow[b]); }
-                else sv[u] = 0.f;
-            }
+        for (int m = 0; m < MT; m++) {
+            float v = acc[m];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
+            if (lane == 0 && m < S) Y[(size_t)m * OUT + r] = v;
+            acc[m] = 0.f;
         }
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int b = lane + 32 * (i0 + u);
-            if (b < nb) {
-                uint32_t e0, o0, e1, o1, e2, o2, e3, o3;
-                unpack8_x16(wv[u].x, e0, o0); unpack8_x16(wv[u].y, e1, o1);
-                unpack8_x16(wv[u].z, e2, o2); unpack8_x16(wv[u].w, e3, o3);
-#pragma unroll
-                for (int m = 0; m < MT; m++) {
-                    const uint4 xa = plane0[(size_t)m * nb + b], xb = plane1[(size_t)m * nb + b];
-                    int d = __dp4a((int)xa.x, (int)e0, 0);
-                    d = __dp4a((int)xa.y, (int)o0, d);
-                    d = __dp4a((int)xa.z, (int)e1, d);
-                    d = __dp4a((int)xa.w, (int)o1, d);
-                    d = __dp4a((int)xb.x, (int)e2, d);
-                    d = __dp4a((int)xb.y, (int)o2, d);
-                    d = __dp4a((int)xb.z, (int)e3, d);
-                    d = __dp4a((int)xb.w, (int)o3, d);      // d = 16 * D[m,o,b], exact
-                    const float sc = (sxs[m * nb + b] * sv[u]) * 0.0625f;   // exact 1/16
-                    acc[m] = fmaf(sc, (float)d, acc[m]);
-                }
-            }
-        }
-    }
-#pragma unroll
-    for (int m = 0; m < MT; m++) {
-        float v = acc[m];
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
-        if (lane == 0 && m < S) Y[(size_t)m * OUT + o] = v;
+    };
+    for (int i = 0; i < nitems; i += 2) {
+        int nrow = row, nbt = batch;
+        advance(nrow, nbt);
+        if (i + 1 < nitems) gemv_load_batch<U, ST>(bb, Wq + (size_t)nrow * wpitch, sw + (size_t)nrow * nb, nbt * U, lane, nb, w_a16);
+        gemv_compute_batch<MT, U, ST>(ba, acc, plane0, plane1, sxs, batch * U, lane, nb);
+        if (batch == nbatch - 1) finish_row(row);
+        if (i + 1 >= nitems) break;
+        row = nrow; batch = nbt;
+        advance(nrow, nbt);
+        if (i + 2 < nitems) gemv_load_batch<U, ST>(ba, Wq + (size_t)nrow * wpitch, sw + (size_t)nrow * nb, nbt * U, lane, nb, w_a16);
+        gemv_compute_batch<MT, U, ST>(bb, acc, plane0, plane1, sxs, batch * U, lane, nb);
+        if (batch == nbatch - 1) finish_row(row);
+        row = nrow; batch = nbt;
     }
 }
 
@@ -159,7 +191,21 @@ inline int launch_gemv_dp4a_t(const int8_t *xq, const float *xs, const uint8_t *
             configured = smem;
         }
     }
-    const dim3 grid((unsigned)((OUT + GEMV_WARPS - 1) / GEMV_WARPS), (unsigned)(ga.idx ? ga.nslots : 1));
+    // Persistent: as many CTAs as are resident at once (fewer when there are not enough rows, or when grouped
+    // slots already fill the GPU).  Residency is asked of the runtime once per kernel variant and smem size.
+    static size_t occ_smem = ~(size_t)0;
+    static int occ = 1;
+    if (occ_smem != smem) {
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, GEMV_WARPS * 32, smem);
+        if (e != cudaSuccess) return cuda_fail(e, "gemv occupancy query");
+        occ = n > 0 ? n : 1;
+        occ_smem = smem;
+    }
+    long want = (OUT + GEMV_WARPS - 1) / GEMV_WARPS;
+    long cap = (long)sm_count() * occ;
+    if (ga.idx) cap = cap / ga.nslots > 1 ? cap / ga.nslots : 1;
+    const dim3 grid((unsigned)(want < cap ? want : cap), (unsigned)(ga.idx ? ga.nslots : 1));
     // every expert's base stays 16-byte aligned when Wq is, because OUT*IN/2 is a multiple of 16
     kern<<<grid, GEMV_WARPS * 32, smem, st>>>(xq, xs, Wq, sw, Y, IN, OUT, S, aligned(Wq, 16), ga);
     return launch_status("gemv_w4a8");

@@ -45,6 +45,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long lo
     return true;
 }
 
+// Warp-wide bounded wait: ONE lane polls the barrier and the outcome is broadcast (the shuffle also
+// re-converges and orders the warp).  An mbarrier operation issued by 32 lanes is carried out lane by
+// lane, so letting every lane poll costs tens of cycles per wait; with one wait per 32-wide K group that
+// serialisation, not the arithmetic, would set the pace of the whole pipeline.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, long long limit_cycles = (1ll << 28)) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, limit_cycles) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 // ---- proxies / fences -------------------------------------------------------------------------
 // Makes generic-proxy shared-memory writes visible to the async proxy (TMA, tcgen05.mma operands).
 __device__ __forceinline__ void fence_proxy_async_smem() {
@@ -88,6 +98,18 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
         : "r"(taddr)
         : "memory");
 }
+// 16-column variant (16 registers per lane).
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld_32x32b_x32(taddr, r); }
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld_32x32b_x16(taddr, r); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ---- tcgen05.mma, kind::i8 (int8 x int8 -> int32 in TMEM), one CTA -----------------------------

@@ -1,0 +1,60 @@
+"""N-sharded (column tensor-parallel) W4A8 linear: host-side plumbing over torch.distributed.
+
+Every output column n of Y = X * W^T depends only on row n of Wq / sw, and rows are the outer dimension of
+the reference's weight files (runtime/weights_qwen.cu:28-36), so rank r of g keeps the contiguous row range
+w4a8_shard_rows gives it, computes Y[:, row0:row0+rows] with the ordinary single-GPU entry points and one
+all-gather reassembles the row-major Y[M, N].  The reference itself is single-GPU; nothing here replaces
+reference code.  The collective is NCCL on GPUs (gloo in the CPU tests); there is no other data-path exchange.
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_plan(N, world, shard_rows):
+    """[(row0, rows)] for every rank, from the library's w4a8_shard_rows (passed in as `shard_rows`)."""
+    plan = [shard_rows(N, r, world) for r in range(world)]
+    assert plan[0][0] == 0 and sum(r for _, r in plan) == N
+    for (a0, a), (b0, _) in zip(plan, plan[1:]):
+        assert a0 + a == b0, "shards must be contiguous and ordered by rank"
+    return plan
+
+
+def all_gather_columns(Y_local, plan, group=None):
+    """Y_local[M, rows_r] on every rank -> Y[M, N] on every rank (row-major).
+
+    Equal shards use one all_gather_into_tensor into [g][M][rows] followed, for M > 1, by the permutation to
+    [M][g*rows]; for M = 1 the gathered buffer already is Y.  Ragged shards (sizes differ by at most one row) are padded to the largest, gathered and trimmed.
+    """
+    M = Y_local.shape[0]
+    counts = [r for _, r in plan]
+    N = sum(counts)
+    world = len(plan)
+    if world == 1:
+        return Y_local
+    if len(set(counts)) == 1:
+        buf = torch.empty((world * M, counts[0]), dtype=Y_local.dtype, device=Y_local.device)   # rank-major concat
+        dist.all_gather_into_tensor(buf, Y_local.contiguous(), group=group)
+        if M == 1:
+            return buf.view(1, N)
+        return buf.view(world, M, counts[0]).permute(1, 0, 2).reshape(M, N)
+    cmax = max(counts)                      # ragged shards (differ by at most one row): pad, gather, trim
+    padded = torch.zeros((M, cmax), dtype=Y_local.dtype, device=Y_local.device)
+    padded[:, : Y_local.shape[1]] = Y_local
+    buf = torch.empty((world * M, cmax), dtype=Y_local.dtype, device=Y_local.device)
+    dist.all_gather_into_tensor(buf, padded, group=group)
+    buf = buf.view(world, M, cmax)
+    return torch.cat([buf[r, :, : counts[r]] for r in range(world)], dim=1)
+
+
+class NShardedLinear:
+    """One (Wq, sw) pair sharded along N.  `compute(X, row0, rows) -> Y_local[M, rows]` is the rank-local
+    product: on a GPU it calls w4a8_linear on the rank's shard; the CPU tests inject a host function."""
+
+    def __init__(self, N, K, rank, world, shard_rows, compute, group=None):
+        self.N, self.K, self.rank, self.world, self.group = N, K, rank, world, group
+        self.plan = shard_plan(N, world, shard_rows)
+        self.row0, self.rows = self.plan[rank]
+        self.compute = compute
+
+    def __call__(self, X):
+        return all_gather_columns(self.compute(X, self.row0, self.rows), self.plan, self.group)
