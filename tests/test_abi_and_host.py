@@ -131,3 +131,53 @@ def test_n_sharded_all_gather_two_gloo_ranks(tmp_path):
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, o[-2000:]
         assert "rank %d ok" % r in o
+
+
+_SHIM_TU = r'''
+#include "kernels/quantize_x.cuh"
+#include "kernels/gemv_w4a8.cuh"
+#include "kernels/gemm_batch.cuh"
+#include "kernels/gemm_mma.cuh"
+#include "kernels/gemm_mmq.cuh"
+#include "kernels/gemm_mmq_tmpl.cuh"
+#include "kernels/gemm_mmq_raster.cuh"
+#include "kernels/gemm_mmq_ms.cuh"
+#include "runtime/weights_shard.h"
+// every launcher of the reference's W4A8 path, called with the reference's argument lists and defaults
+void all(const float *X, int8_t *xq, float *xs, int32_t *xsum, const uint8_t *Wq, const void *sw, float *Y, cudaStream_t st) {
+    launch_quantize_x_q8(X, xq, xs, xsum, 64, 1);
+    launch_gemv_w4a8(xq, xs, xsum, Wq, sw, Y, 64, 8, 1);
+    launch_gemv_w4a8_mlp<2>(xq, xs, xsum, Wq, sw, Y, 64, 8, 1, 0, st);
+    launch_gemv_w4a8_mlp_auto(xq, xs, xsum, Wq, sw, Y, 64, 8, 1, 1, st);
+    launch_gemv_w4a8_g4(xq, xs, xsum, Wq, sw, Y, 64, 8, 1, 0, st);
+    launch_gemv_w4a8_sb(xq, xs, Wq, sw, Y, 64, 8, 5);
+    launch_gemv_w4a8_sb_g4(xq, xs, Wq, sw, Y, 64, 8, 5, 0, st);
+    launch_gemm_batch_w4a8(xq, xs, Wq, sw, Y, 64, 8, 16);
+    launch_gemm_mma_w4a8(xq, xs, Wq, sw, Y, 128, 8, 64);
+    launch_gemm_mma_w4a8_bm<128>(xq, xs, Wq, sw, Y, 128, 8, 64, 0, st);
+    launch_gemm_mmq_w4a8(xq, xs, Wq, sw, Y, 128, 8, 64);
+    launch_gemm_mmq_w4a8_kt<128>(xq, xs, Wq, sw, Y, 128, 8, 64, 0, st);
+    launch_gemm_mmq_w4a8_auto(xq, xs, Wq, sw, Y, 128, 8, 64);
+    launch_gemm_mmq_tmpl<256, 64, 64, 4, 2>(xq, xs, Wq, sw, Y, 128, 8, 64, 0, st);
+    launch_gemm_mmq_raster_w4a8(xq, xs, Wq, sw, Y, 128, 8, 64, 0, 1, 1);
+    launch_gemm_mmq_ms<128, 128, 64, 2, 4, 3>(xq, xs, Wq, sw, Y, 128, 8, 64);
+    launch_gemm_bm16_splitk(xq, xs, Wq, sw, Y, 16, 8, 64);
+    QMatShard m = mat_shard("dir", "L0_mlp.gate_proj", 8, 64, 0, 0, 1);
+    (void)m;
+}
+int main() { return QBLK == 32 ? 0 : 1; }
+'''
+
+
+def test_shim_headers_compile_and_link_with_reference_signatures(w4a8, tmp_path):
+    nvcc = "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not available")
+    src = tmp_path / "shim_tu.cu"
+    src.write_text(_SHIM_TU)
+    pkg = os.path.join(ROOT, "dgx-serving_b200")
+    exe = tmp_path / "shim_tu"
+    r = subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-I" + pkg, "-o", str(exe), str(src),
+                        "-L" + pkg, "-lw4a8_b200", "-Xlinker", "-rpath", "-Xlinker", pkg], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert subprocess.run([str(exe)]).returncode == 0

@@ -125,3 +125,17 @@ def test_reference_splitk(ref, w4a8, oracle, cuda):
     nsplit = max(1, nbytes // (M * N * 4))
     assert np.array_equal(Yr.cpu().numpy().view(np.uint32), oracle.gemm_splitk_w4a8(xq, xs, Wq, sw, nsplit).view(np.uint32))
     assert np.array_equal(Y.cpu().numpy().view(np.uint32), Yr.cpu().numpy().view(np.uint32))
+
+
+def test_reference_unit_test_runs_against_the_dropin_library(oracle):
+    """The reference's own tests/test_w4a8.cu, compiled unmodified against this repository's shim launchers
+    (oracle/reftest_w4a8_dropin.cu): its gates are xq and xsum mismatches == 0 and |Y - fp64 golden| < 1e-2."""
+    import os
+    import subprocess
+    exe = os.path.join(os.path.dirname(oracle.__file__), "_ref", "reftest_w4a8_dropin")
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/reftest_w4a8_dropin not built (needs the reference tree at build time)")
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "[test_w4a8] PASS" in r.stdout and "FAIL" not in r.stdout
+    assert r.stdout.count("xq_mis=0 xsum_mis=0") == 4
