@@ -45,6 +45,7 @@ _SIGNATURES = {
     "w4a8_gemm": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "w4a8_gemm_splitk_workspace_bytes": (_Z, [_I, _I, _I, _I]),
     "w4a8_gemm_splitk": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _Z, _P]),
+    "w4a8_gemm_splitk_static": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "w4a8_group_dots": (_I, [_P, _P, _P, _I, _I, _I, _I, _P]),
     "w4a8_linear": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "w4a8_moe_gemv": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P]),
@@ -140,6 +141,16 @@ def launch_gemm_bm16_splitk(X, xs, Wq, sw, Y, M, N, K, scale_dtype=0, splitk=0, 
     nbytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     _check(lib().w4a8_gemm_splitk(_ptr(X), _ptr(xs), _ptr(Wq), _ptr(sw), _ptr(Y), M, N, K, scale_dtype, splitk,
                                   _ptr(workspace), nbytes, _stream(stream)))
+
+
+SPLITK_STATIC_BYTES = 16 * 1024 * 1024
+
+
+def launch_gemm_splitk_static(X, xs, Wq, sw, Y, M, N, K, scale_dtype=0, splitk=0, stream=None):
+    """Split-K GEMM whose partial sums live in a buffer built into the library: no workspace, no allocation.
+    For callers that cannot allocate at the point of the call; at most SPLITK_STATIC_BYTES of partial sums."""
+    _check(lib().w4a8_gemm_splitk_static(_ptr(X), _ptr(xs), _ptr(Wq), _ptr(sw), _ptr(Y), M, N, K, scale_dtype, splitk,
+                                         _stream(stream)))
 
 
 def group_dots(xq, Wq, D, M, N, K, path=0, stream=None):

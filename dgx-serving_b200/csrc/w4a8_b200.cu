@@ -197,6 +197,62 @@ W4A8_API int w4a8_gemm_splitk(const int8_t *X, const float *xs, const uint8_t *W
     return launch_status("splitk_reduce");
 }
 
+// ---- split-K without an allocator ---------------------------------------------------------------------
+// Partial-sum buffer for w4a8_gemm_splitk_static: lives in the library image, so no call ever allocates.
+// In host code this name is only a handle for cudaGetSymbolAddress, never a usable pointer.
+static __device__ __align__(256) float g_splitk_static_scratch[W4A8_SPLITK_STATIC_BYTES / sizeof(float)];
+
+// Device address of the buffer on the current device; queried once per device and cached.
+static int splitk_static_ptr(float **out) {
+    constexpr int MAX_DEV = 64;
+    static float *cached[MAX_DEV] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "gemm_splitk_static: cudaGetDevice");
+    if (dev < 0 || dev >= MAX_DEV) return fail(W4A8_ERR_UNSUPPORTED, "gemm_splitk_static: device index %d out of range", dev);
+    if (!cached[dev]) {
+        float *p = nullptr;
+        e = cudaGetSymbolAddress((void **)&p, g_splitk_static_scratch);
+        if (e != cudaSuccess || !p) return cuda_fail(e, "gemm_splitk_static: cudaGetSymbolAddress");
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return W4A8_OK;
+}
+
+W4A8_API int w4a8_gemm_splitk_static(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int M, int N,
+                                     int K, int scale_dtype, int splitk, void *stream) {
+    if (M < 0 || N < 0) return fail(W4A8_ERR_ARG, "gemm_splitk_static: negative size M=%d N=%d", M, N);
+    if (M == 0 || N == 0) return W4A8_OK;
+    int rc = check_common(X, xs, Wq, sw, Y, K, scale_dtype, "gemm_splitk_static");
+    if (rc != W4A8_OK) return rc;
+    if (!aligned(X, 16) || !aligned(Wq, 16)) return fail(W4A8_ERR_ALIGN, "gemm_splitk_static: X and Wq must be 16-byte aligned (TMA)");
+    if (K == 0) return w4a8_gemm(X, xs, Wq, sw, Y, M, N, K, scale_dtype, stream);
+    int ns, gs;
+    splitk_plan(N, K, splitk, &ns, &gs);
+    const size_t need = (size_t)ns * M * N * sizeof(float);
+    if (ns > 1 && need > (size_t)W4A8_SPLITK_STATIC_BYTES)
+        return fail(W4A8_ERR_UNSUPPORTED,
+                    "gemm_splitk_static: %d splits x M=%d x N=%d need %zu bytes of partial sums, the built-in buffer holds %u; "
+                    "use w4a8_gemm_splitk with a caller-owned workspace",
+                    ns, M, N, need, (unsigned)W4A8_SPLITK_STATIC_BYTES);
+    rc = require_sm100();
+    if (rc != W4A8_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (ns == 1) return gemm::launch_tc(X, xs, Wq, sw, Y, M, N, K, scale_dtype, 1, K / QBLK, st);
+    float *scratch = nullptr;
+    rc = splitk_static_ptr(&scratch);
+    if (rc != W4A8_OK) return rc;
+    // kernel 1 writes every partial sum [split][m][n], m < M, n < N (an empty K range writes zeros), kernel 2 reads
+    // exactly those: nothing left over from an earlier call is ever read, so nothing needs clearing.
+    rc = gemm::launch_tc(X, xs, Wq, sw, scratch, M, N, K, scale_dtype, ns, gs, st);
+    if (rc != W4A8_OK) return rc;
+    const long MN = (long)M * N;
+    long want = (MN + 255) / 256, cap = (long)sm_count() * 8;
+    gemm::splitk_reduce_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(scratch, Y, MN, ns);
+    return launch_status("splitk_reduce (static)");
+}
+
 W4A8_API int w4a8_group_dots(const int8_t *xq, const uint8_t *Wq, int32_t *D, int M, int N, int K, int path, void *stream) {
     if (M < 0 || N < 0 || K < 0 || K % QBLK != 0) return fail(W4A8_ERR_ARG, "group_dots: bad shape M=%d N=%d K=%d", M, N, K);
     if (M == 0 || N == 0 || K == 0) return W4A8_OK;

@@ -95,6 +95,29 @@ int w4a8_gemm_splitk(const int8_t *X, const float *xs, const uint8_t *Wq, const 
                      int M, int N, int K, int scale_dtype, int splitk,
                      void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---- split-K GEMM for callers that cannot allocate device memory ------------------------------------
+ * No counterpart in the reference (its split-K launcher allocates its own workspace with cudaMalloc,
+ * kernels/gemm_mmq.cuh:206,215).
+ * Same product and same bits as w4a8_gemm_splitk, but the partial sums live in a fixed buffer that is part
+ * of the library image (W4A8_SPLITK_STATIC_BYTES of device memory, held by every GPU that loads the library
+ * until the process exits), so the call needs no workspace argument and performs no cudaMalloc / cudaFree
+ * or any other allocation.  It is meant for callers that have no way to obtain device scratch at the point
+ * of the call: a serving loop that must not touch the device allocator once it is running (an allocation
+ * can synchronise the device or fail under memory pressure in the middle of a request), or a host plugin
+ * that another runtime handed only its input and output buffers and that owns no allocator of its own.
+ *  - Limit: nsplit * M * N * 4 bytes must fit in W4A8_SPLITK_STATIC_BYTES (nsplit as chosen by `splitk`,
+ *    see w4a8_gemm_splitk); larger problems are rejected with W4A8_ERR_UNSUPPORTED and a message that names
+ *    both sizes.  Use w4a8_gemm_splitk with your own workspace for those.
+ *  - The first call on each device looks up the buffer's device address (one host-side query, result
+ *    cached per device).  Make that first call outside any stream capture.
+ *  - All calls share the one buffer and it keeps whatever the previous call left.  Nothing in it has to be
+ *    cleared: the first kernel of a call rewrites every partial sum that the second kernel of the same
+ *    call reads.  Because the buffer is shared, two calls whose kernels may overlap on the GPU (different
+ *    streams, or concurrent host threads) race on it; issue calls on one stream, or order them yourself. */
+#define W4A8_SPLITK_STATIC_BYTES (16u * 1024u * 1024u)
+int w4a8_gemm_splitk_static(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y,
+                            int M, int N, int K, int scale_dtype, int splitk, void *stream);
+
 /* ---- exact integer group dots (debug / parity) ------------------------------------------------------
  * D[m,n,b] = sum_{k in b} xq[m,k]*(Wq[n,k]-8) as int32, D laid out [M][N][K/32].  `path` selects the
  * producer: 0 = the GEMV kernels' dp4a path, 1 = the GEMM kernel's tcgen05 path (accumulators read
