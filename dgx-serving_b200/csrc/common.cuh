@@ -38,6 +38,29 @@ int sm_count();
 // W4A8_OK if the current device is compute capability 10.x, else W4A8_ERR_UNSUPPORTED.
 int require_sm100();
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// Kernels that only READ data no earlier kernel of the stream writes (the weights) before they touch anything
+// else are launched with the programmatic-stream-serialization attribute: their CTAs may become resident while
+// the previous kernel of the stream is still draining, issue their first weight loads, and then block in
+// pdl_wait() until that kernel has completed and its writes are visible.  That hides the launch gap and the
+// ramp-up of a 10-microsecond kernel behind the tail of its predecessor.  Without the attribute both
+// instructions do nothing.  W4A8_PDL=0 in the environment disables the attribute (plain stream order).
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+bool pdl_enabled();   // w4a8_b200.cu
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 // ---- device-side error word (set when a bounded wait runs out) ---------------------------------
 __device__ unsigned int g_dev_error = 0u;  // one translation unit: w4a8_b200.cu includes every kernel file
 __device__ __forceinline__ void dev_set_error(unsigned int code) { atomicCAS(&g_dev_error, 0u, code); }

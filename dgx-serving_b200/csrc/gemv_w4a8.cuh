@@ -122,7 +122,11 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_dp4a_kernel(
 
     // The first batch of weight loads goes out before the activations are staged.
     GemvBatch<U, ST> ba, bb;
+    pdl_launch_dependents();
     if (nitems > 0) gemv_load_batch<U, ST>(ba, Wq + (size_t)(r0 + warp) * wpitch, sw + (size_t)(r0 + warp) * nb, 0, lane, nb, w_a16);
+    // Everything above read only the weights and their scales.  The activations (written by the quantize kernel
+    // that precedes this launch in the stream) and Y may only be touched once the previous kernel is complete.
+    pdl_wait();
 
     // Stage activations: one task = one 8-element chunk (two 4-byte loads, like the reference's x0/x1).
 #pragma unroll
@@ -207,7 +211,8 @@ inline int launch_gemv_dp4a_t(const int8_t *xq, const float *xs, const uint8_t *
     if (ga.idx) cap = cap / ga.nslots > 1 ? cap / ga.nslots : 1;
     const dim3 grid((unsigned)(want < cap ? want : cap), (unsigned)(ga.idx ? ga.nslots : 1));
     // every expert's base stays 16-byte aligned when Wq is, because OUT*IN/2 is a multiple of 16
-    kern<<<grid, GEMV_WARPS * 32, smem, st>>>(xq, xs, Wq, sw, Y, IN, OUT, S, aligned(Wq, 16), ga);
+    cudaError_t le = launch_pdl(kern, grid, dim3(GEMV_WARPS * 32), smem, st, xq, xs, Wq, sw, Y, IN, OUT, S, aligned(Wq, 16), ga);
+    if (le != cudaSuccess) return cuda_fail(le, "gemv_w4a8 launch");
     return launch_status("gemv_w4a8");
 }
 

@@ -16,6 +16,10 @@ __global__ void __launch_bounds__(256) quantize_x_q8_vec_kernel(const float4 *__
                                                                 long nvec /* = S*IN/4, a multiple of 8 */) {
     const long stride = (long)gridDim.x * blockDim.x;
     long i0 = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    // Lets a following kernel that was launched for programmatic dependent launch (the GEMV) become resident and
+    // start streaming its weights while this kernel runs; it still waits for this kernel's completion before it
+    // reads xq / xs.
+    pdl_launch_dependents();
     // nvec is a multiple of 8 and i0 - lane is a multiple of 32, so the 8-lane groups are either fully
     // inside or fully outside; shuffles use the full mask with out-of-range lanes carrying zeros.
     for (; i0 - (threadIdx.x & 31) < nvec; i0 += stride * UNROLL) {

@@ -20,6 +20,15 @@ char *err_buf() {
     return buf;
 }
 
+bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("W4A8_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
 int sm_count() {
     static int cached_dev = -1, cached = 0;
     int dev = 0;
