@@ -14,7 +14,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libw4a8_b200.so")
+LIB_PATH = os.environ.get("W4A8_LIB") or os.path.join(_HERE, "libw4a8_b200.so")   # W4A8_LIB: another build, for A/B timing
 QBLK = 32
 
 OK, ERR_ARG, ERR_ALIGN, ERR_CUDA, ERR_IO, ERR_DEVICE, ERR_UNSUPPORTED, ERR_WORKSPACE = range(8)
@@ -40,6 +40,7 @@ _SIGNATURES = {
     "w4a8_version": (_I, []),
     "w4a8_last_error": (ctypes.c_char_p, []),
     "w4a8_device_status": (_I, [ctypes.POINTER(ctypes.c_uint32)]),
+    "w4a8_config": (_I, [ctypes.c_char_p, _I]),
     "w4a8_quantize_x_q8": (_I, [_P, _P, _P, _P, _I, _I, _P]),
     "w4a8_gemv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "w4a8_gemm": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
@@ -92,6 +93,11 @@ def _stream(stream):
     if isinstance(stream, int):
         return stream
     return stream.cuda_stream
+
+
+def config(key, value):
+    """Run-time policy switch, e.g. config("gemv_kernel", 2): tensor-path GEMV for every S (see include/w4a8_b200.h)."""
+    _check(lib().w4a8_config(key.encode(), int(value)))
 
 
 def device_status():

@@ -11,6 +11,7 @@
 #include "common.cuh"
 #include "quantize_x.cuh"
 #include "gemv_w4a8.cuh"
+#include "gemv_w4a8_mma.cuh"
 #include "gemm_w4a8_tc.cuh"
 
 namespace w4a8 {
@@ -124,6 +125,32 @@ W4A8_API int w4a8_quantize_x_q8(const float *X, int8_t *xq, float *xs, int32_t *
     return launch_quantize_x(X, xq, xs, xsum, IN, S, (cudaStream_t)stream);
 }
 
+// GEMV kernel policy: 0 auto (one activation row -> dp4a kernel, more -> tensor-path kernel), 1 always dp4a,
+// 2 tensor path for every S it supports.  Initialised from the environment (W4A8_GEMV = dp4a | mma), changed at
+// run time with w4a8_config("gemv_kernel", v).
+static int g_gemv_policy = -1;
+static int gemv_policy() {
+    if (g_gemv_policy < 0) {
+        const char *e = getenv("W4A8_GEMV");
+        g_gemv_policy = !e ? 0 : (e[0] == 'm' ? 2 : (e[0] == 'd' ? 1 : 0));
+    }
+    return g_gemv_policy;
+}
+static bool gemv_use_mma(int S) {
+    const int p = gemv_policy();
+    return p == 2 || (p == 0 && S >= 2);
+}
+
+W4A8_API int w4a8_config(const char *key, int value) {
+    if (!key) return fail(W4A8_ERR_ARG, "config: null key");
+    if (!strcmp(key, "gemv_kernel")) {
+        if (value < 0 || value > 2) return fail(W4A8_ERR_ARG, "config: gemv_kernel = 0 (auto), 1 (dp4a), 2 (tensor path); got %d", value);
+        g_gemv_policy = value;
+        return W4A8_OK;
+    }
+    return fail(W4A8_ERR_ARG, "config: unknown key '%s'", key);
+}
+
 W4A8_API int w4a8_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int IN, int OUT,
                        int S, int scale_dtype, void *stream) {
     if (S < 0 || OUT < 0) return fail(W4A8_ERR_ARG, "gemv: negative size S=%d OUT=%d", S, OUT);
@@ -136,6 +163,25 @@ W4A8_API int w4a8_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, con
     if (IN == 0) {
         cudaError_t e = cudaMemsetAsync(Y, 0, (size_t)S * OUT * sizeof(float), (cudaStream_t)stream);
         return e == cudaSuccess ? W4A8_OK : cuda_fail(e, "gemv: memset");
+    }
+    // Kernel choice.  W4A8_GEMV=dp4a / mma forces one formulation (measurements); default: see gemv_kernel_choice.
+    if (gemv_use_mma(S)) {
+        // rows go in passes of up to 16 (8 when 16 rows of activations do not fit in shared memory next to the ring)
+        gemv_mma::Plan plan;
+        int per = S < 16 ? S : 16;
+        bool ok = gemv_mma::plan_for(Wq, sw, IN, per, &plan);
+        if (!ok && per > 8) { per = 8; ok = gemv_mma::plan_for(Wq, sw, IN, per, &plan); }
+        if (ok) {
+            for (int s0 = 0; s0 < S; s0 += per) {
+                const int s = S - s0 < per ? S - s0 : per;
+                gemv_mma::Plan pl = plan;
+                if (s <= 8 && pl.MH == 2) gemv_mma::plan_for(Wq, sw, IN, s, &pl);
+                rc = gemv_mma::launch(xq + (size_t)s0 * IN, xs + (size_t)s0 * (IN / QBLK), Wq, sw, Y + (size_t)s0 * OUT, IN, OUT, s,
+                                      scale_dtype, pl, (cudaStream_t)stream);
+                if (rc != W4A8_OK) return rc;
+            }
+            return W4A8_OK;
+        }
     }
     return launch_gemv(xq, xs, Wq, sw, Y, IN, OUT, S, scale_dtype, (cudaStream_t)stream);
 }

@@ -55,6 +55,16 @@ const char *w4a8_last_error(void);
  * out.  Synchronises the device.  Returns W4A8_OK or W4A8_ERR_DEVICE (detail in *detail if given). */
 int w4a8_device_status(uint32_t *detail);
 
+/* Run-time policy switches (the reference keeps such switches in runtime/knobs.h, read from the environment;
+ * the same names are read here once: W4A8_GEMV = dp4a | mma, W4A8_PDL = 0 | 1).
+ *   "gemv_kernel": 0 = auto (default): one activation row uses the dp4a streaming kernel, 2..16 rows the
+ *                  tensor-path kernel; 1 = dp4a kernel for every S; 2 = tensor-path kernel for every S it
+ *                  supports (K % 256 == 0, 16-byte aligned Wq and sw).  The tensor-path kernel evaluates fp32 in
+ *                  the MMQ order (bit-identical to w4a8_gemm and to the reference's MMQ kernels); the dp4a kernel
+ *                  in its own fixed order (within 1e-5).  Policy 2 therefore makes a row's bits independent of S
+ *                  for all S >= 1 (the reference's batch == single invariant), policy 0 for all S >= 2. */
+int w4a8_config(const char *key, int value);
+
 /* ---- a1: activation quantization ------------------------------------------------------------------
  * Replaces launch_quantize_x_q8 (kernels/quantize_x.cuh:41-47).
  * X[S,IN] fp32 -> xq[S,IN] int8, xs[S,IN/32] fp32 (= amax/127), xsum[S,IN/32] int32 (= sum of xq over

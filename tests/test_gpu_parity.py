@@ -3,7 +3,8 @@
 Bars (BASELINE north_star): quantized activations and int32 group dots bit-exact; fp32 outputs within
 1e-5 relative.  The library's fp32 orders are fixed and restated in the oracle, so most fp32 checks here
 are in fact bit-exact too: the GEMM family reproduces the reference MMQ order
-(kernels/gemm_mmq.cuh:104-105), the GEMV family its own documented order; against the *other* order the
+(kernels/gemm_mmq.cuh:104-105) and so does the GEMV family's tensor-path kernel (S >= 2), the single-row dp4a GEMV
+kernel has its own documented order; against the *other* order the
 reference's own gate max|d|/rms < 1e-5 (tests/test_gemm_mmq.cu:28) applies.
 Shapes follow the reference tests: tests/test_w4a8.cu:95-98, tests/test_gemm_mmq.cu:38,
 tests/test_gemm_mma.cu:40, plus BASELINE.json config 1 and ragged / partial-K-tile cases.
@@ -84,31 +85,62 @@ GEMV_SHAPES = [(1024, 256, 1), (1024, 2048, 1), (3584, 1024, 1), (1024, 4096, 5)
                (160, 37, 3), (96, 9, 2), (5120, 1000, 16), (15360, 384, 8), (2048, 768, 7), (768, 2048, 12)]
 
 
+def gemv_expected(oracle, xq, xs, Wq, sw, policy=0):
+    """The documented fp32 order of w4a8_gemv: the tensor-path kernel (MMQ order) serves S >= 2 (every S under
+    policy 2) when K % 256 == 0, the dp4a kernel (its own chain order) everything else."""
+    S, K = xq.shape
+    mma = K % 256 == 0 and (policy == 2 or (policy == 0 and S >= 2))
+    return oracle.gemm_mmq_w4a8(xq, xs, Wq, sw) if mma else oracle.gemv_b200_order(xq, xs, Wq, sw)
+
+
+@pytest.mark.parametrize("policy", [0, 1, 2])
 @pytest.mark.parametrize("scale_dtype", [0, 1])
 @pytest.mark.parametrize("IN,OUT,S", GEMV_SHAPES)
-def test_gemv_parity(w4a8, oracle, cuda, IN, OUT, S, scale_dtype):
+def test_gemv_parity(w4a8, oracle, cuda, IN, OUT, S, scale_dtype, policy):
+    if policy != 0 and scale_dtype == 1 and IN not in (1024, 5120, 768):
+        pytest.skip("forced-kernel policies are covered on a subset of the fp16-scale shapes")
     xq, xs, Wq, sw = make_case(oracle, S, OUT, IN, seed=500 + IN + OUT + S, scale_dtype=scale_dtype)
-    Y = torch.full((S, OUT), float("nan"), dtype=torch.float32, device=cuda)
-    w4a8.launch_gemv_w4a8_sb(to_dev(xq, cuda), to_dev(xs, cuda), to_dev(Wq, cuda), to_dev(sw, cuda), Y, IN, OUT, S, scale_dtype)
-    torch.cuda.synchronize()
+    Y = torch.full((S + 1, OUT), float("nan"), dtype=torch.float32, device=cuda)          # last row: canary
+    w4a8.config("gemv_kernel", policy)
+    try:
+        w4a8.launch_gemv_w4a8_sb(to_dev(xq, cuda), to_dev(xs, cuda), to_dev(Wq, cuda), to_dev(sw, cuda), Y, IN, OUT, S, scale_dtype)
+        torch.cuda.synchronize()
+    finally:
+        w4a8.config("gemv_kernel", 0)
     y = Y.cpu().numpy()
-    assert np.array_equal(y.view(np.uint32), oracle.gemv_b200_order(xq, xs, Wq, sw).view(np.uint32))   # documented order
+    assert np.all(np.isnan(y[S])) and not np.any(np.isnan(y[:S]))
+    y = y[:S]
+    assert np.array_equal(y.view(np.uint32), gemv_expected(oracle, xq, xs, Wq, sw, policy).view(np.uint32))   # documented order
     assert rel_err(y, oracle.gemv_w4a8(xq, xs, Wq, sw)) < REL_TOL                                        # reference GEMV order
     assert np.max(np.abs(y - oracle.w4a8_f64(xq, xs, Wq, sw))) < 1e-2                                    # tests/test_w4a8.cu:83
 
 
 def test_gemv_rows_independent_of_batch(w4a8, oracle, cuda):
-    """A row's result does not depend on S or on its position (models/qwen35_batch.cu:270-273)."""
+    """A row's result does not depend on S or on its position (models/qwen35_batch.cu:270-273): for every S >= 2
+    under the default policy, for every S >= 1 with the tensor-path kernel forced, and equal to the GEMM family."""
     IN, OUT, S = 2048, 520, 13
     xq, xs, Wq, sw = make_case(oracle, S, OUT, IN, seed=77)
     d = [to_dev(a, cuda) for a in (xq, xs, Wq, sw)]
     Y = torch.empty((S, OUT), dtype=torch.float32, device=cuda)
     w4a8.launch_gemv_w4a8_sb(d[0], d[1], d[2], d[3], Y, IN, OUT, S)
-    for s in (0, 6, 12):
-        y1 = torch.empty((1, OUT), dtype=torch.float32, device=cuda)
-        w4a8.launch_gemv_w4a8(d[0][s:s + 1].contiguous(), d[1][s:s + 1].contiguous(), None, d[2], d[3], y1, IN, OUT, 1)
+    for s in (0, 6, 11):                                   # pairs of rows, default policy
+        y2 = torch.empty((2, OUT), dtype=torch.float32, device=cuda)
+        w4a8.launch_gemm_batch_w4a8(d[0][s:s + 2].contiguous(), d[1][s:s + 2].contiguous(), d[2], d[3], y2, IN, OUT, 2)
         torch.cuda.synchronize()
-        assert torch.equal(y1[0], Y[s])
+        assert torch.equal(y2, Y[s:s + 2])
+    w4a8.config("gemv_kernel", 2)
+    try:
+        for s in (0, 6, 12):                               # single rows, tensor-path kernel for every S
+            y1 = torch.empty((1, OUT), dtype=torch.float32, device=cuda)
+            w4a8.launch_gemv_w4a8(d[0][s:s + 1].contiguous(), d[1][s:s + 1].contiguous(), None, d[2], d[3], y1, IN, OUT, 1)
+            torch.cuda.synchronize()
+            assert torch.equal(y1[0], Y[s])
+    finally:
+        w4a8.config("gemv_kernel", 0)
+    Yg = torch.empty((S, OUT), dtype=torch.float32, device=cuda)      # the GEMM family gives the same bits
+    w4a8.launch_gemm_mmq_w4a8(d[0], d[1], d[2], d[3], Yg, S, OUT, IN)
+    w4a8.device_status()
+    assert torch.equal(Yg, Y)
 
 
 GEMM_SHAPES = [(128, 128, 512), (256, 512, 1024), (200, 300, 256), (129, 140, 160),     # tests/test_gemm_mmq.cu:38
@@ -208,7 +240,7 @@ def test_linear_dispatch_and_loader(w4a8, oracle, cuda, tmp_path):
         Y = torch.empty((S, N), dtype=torch.float32, device=cuda)
         w4a8.linear(to_dev(X, cuda), xq, xs, xsum, whole.wq, whole.sc, Y, S, N, K)
         w4a8.device_status()
-        ref = oracle.gemv_b200_order(xq_o, xs_o, Wq, sw) if S <= 16 else oracle.gemm_mmq_w4a8(xq_o, xs_o, Wq, sw)
+        ref = gemv_expected(oracle, xq_o, xs_o, Wq, sw) if S <= 16 else oracle.gemm_mmq_w4a8(xq_o, xs_o, Wq, sw)
         assert np.array_equal(Y.cpu().numpy().view(np.uint32), ref.view(np.uint32))
         # the same product assembled from three row shards
         parts = []
