@@ -54,6 +54,15 @@ _SIGNATURES = {
     "w4a8_load_qmat_shard": (_I, [ctypes.c_char_p, ctypes.c_char_p, _L, _L, _I, _I, _I, ctypes.POINTER(QMat)]),
     "w4a8_upload_qmat_shard": (_I, [_P, _P, _L, _L, _I, _I, _I, ctypes.POINTER(QMat)]),
     "w4a8_free_qmat": (_I, [ctypes.POINTER(QMat)]),
+    "w4a8_arena_create": (_I, [_Z, _I, _I, ctypes.POINTER(_P)]),
+    "w4a8_arena_base": (_P, [_P]),
+    "w4a8_arena_connect": (_I, [_P, ctypes.POINTER(_P)]),
+    "w4a8_arena_destroy": (_I, [_P]),
+    "w4a8_ipc_export": (_I, [_P, ctypes.c_char_p]),
+    "w4a8_ipc_open": (_I, [ctypes.c_char_p, ctypes.POINTER(_P)]),
+    "w4a8_ipc_close": (_I, [_P]),
+    "w4a8_gemv_allgather": (_I, [_P, _P, _P, _P, _P, _Z, _I, _I, _I, _I, _I, _I, ctypes.c_uint32, _P]),
+    "w4a8_allgather_wait": (_I, [_P, ctypes.c_uint32, _I, _P]),
 }
 EXPORTS = tuple(_SIGNATURES)
 
@@ -197,3 +206,71 @@ def upload_qmat_shard(host_wq, host_sc, N, K, scale_dtype, rank, world):
 
 def free_qmat(m):
     _check(lib().w4a8_free_qmat(ctypes.byref(m)))
+
+
+class Arena:
+    """Peer-visible device memory for the fused GEMV + all-gather (w4a8_arena in include/w4a8_b200.h)."""
+
+    def __init__(self, nbytes, rank, world):
+        h = _P()
+        _check(lib().w4a8_arena_create(nbytes, rank, world, ctypes.byref(h)))
+        self.handle, self.rank, self.world, self.nbytes = h, rank, world, nbytes
+        self.base = lib().w4a8_arena_base(h)
+        self._opened = []
+
+    def export_handle(self):
+        buf = ctypes.create_string_buffer(64)
+        _check(lib().w4a8_ipc_export(self.base, buf))
+        return buf.raw
+
+    def connect_handles(self, handles):
+        """handles[r] = 64-byte CUDA IPC handle of rank r's arena (this rank's own entry is ignored)."""
+        bases = (_P * self.world)()
+        for r, hd in enumerate(handles):
+            if r == self.rank:
+                bases[r] = self.base
+            else:
+                p = _P()
+                _check(lib().w4a8_ipc_open(hd, ctypes.byref(p)))
+                self._opened.append(p)
+                bases[r] = p.value
+        _check(lib().w4a8_arena_connect(self.handle, bases))
+
+    def connect_pointers(self, pointers):
+        """pointers[r] = arena base of rank r already mapped into this process (same-process emulation, or another
+        peer-mapping mechanism)."""
+        bases = (_P * self.world)(*[int(p) for p in pointers])
+        _check(lib().w4a8_arena_connect(self.handle, bases))
+
+    def tensor(self, offset, shape, dtype=None):
+        """A torch view of the local arena (no copy)."""
+        import torch
+        dtype = dtype or torch.float32
+        return _as_tensor(self.base + offset, shape, dtype)
+
+    def gemv_allgather(self, xq, xs, Wq, sw, y_offset, IN, rows, row0, ldY, S, scale_dtype, epoch, stream=None):
+        _check(lib().w4a8_gemv_allgather(_ptr(xq), _ptr(xs), _ptr(Wq), _ptr(sw), self.handle, y_offset, IN, rows, row0, ldY, S,
+                                         scale_dtype, epoch, _stream(stream)))
+
+    def wait(self, epoch, timeout_us=1000000, stream=None):
+        _check(lib().w4a8_allgather_wait(self.handle, epoch, timeout_us, _stream(stream)))
+
+    def close(self):
+        for p in self._opened:
+            lib().w4a8_ipc_close(p)
+        self._opened = []
+        if self.handle:
+            lib().w4a8_arena_destroy(self.handle)
+            self.handle = None
+
+
+def _as_tensor(ptr, shape, dtype):
+    """Wraps raw device memory as a torch tensor through the CUDA array interface (no copy, no ownership)."""
+    import torch
+    typestr = {torch.float32: "<f4", torch.int32: "<i4", torch.uint8: "|u1", torch.int8: "|i1"}[dtype]
+
+    class _Holder:
+        pass
+    h = _Holder()
+    h.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 3, "strides": None}
+    return torch.as_tensor(h, device="cuda")

@@ -16,6 +16,7 @@
 // tests compare families with max|d|/rms < 1e-5, tests/test_gemm_mmq.cu:28.)
 #pragma once
 #include "common.cuh"
+#include "peer_allgather.cuh"
 
 namespace w4a8 {
 
@@ -94,7 +95,7 @@ __device__ __forceinline__ void gemv_compute_batch(const GemvBatch<U, ST> &bt, f
 template <int MT, int U, typename ST>
 __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_dp4a_kernel(
     const int8_t *__restrict__ xq, const float *__restrict__ xs, const uint8_t *__restrict__ Wq,
-    const ST *__restrict__ sw, float *__restrict__ Y, int IN, int OUT, int S, bool w_a16, GroupedArgs ga) {
+    const ST *__restrict__ sw, float *__restrict__ Y, int IN, int OUT, int S, bool w_a16, GroupedArgs ga, OutArgs oa) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int nb = IN / QBLK;
     if (ga.idx) {  // grouped experts: blockIdx.y = slot, one activation row against that slot's expert
@@ -161,7 +162,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_dp4a_kernel(
             float v = acc[m];
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
-            if (lane == 0 && m < S) Y[(size_t)m * OUT + r] = v;
+            if (lane == 0 && m < S) store_out(Y, oa, OUT, m, r, v);
             acc[m] = 0.f;
         }
     };
@@ -179,6 +180,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_dp4a_kernel(
         if (batch == nbatch - 1) finish_row(row);
         row = nrow; batch = nbt;
     }
+    publish_out(oa);
 }
 
 template <int MT, int U, typename ST>
@@ -211,7 +213,7 @@ inline int launch_gemv_dp4a_t(const int8_t *xq, const float *xs, const uint8_t *
     if (ga.idx) cap = cap / ga.nslots > 1 ? cap / ga.nslots : 1;
     const dim3 grid((unsigned)(want < cap ? want : cap), (unsigned)(ga.idx ? ga.nslots : 1));
     // every expert's base stays 16-byte aligned when Wq is, because OUT*IN/2 is a multiple of 16
-    cudaError_t le = launch_pdl(kern, grid, dim3(GEMV_WARPS * 32), smem, st, xq, xs, Wq, sw, Y, IN, OUT, S, aligned(Wq, 16), ga);
+    cudaError_t le = launch_pdl(kern, grid, dim3(GEMV_WARPS * 32), smem, st, xq, xs, Wq, sw, Y, IN, OUT, S, aligned(Wq, 16), ga, current_out());
     if (le != cudaSuccess) return cuda_fail(le, "gemv_w4a8 launch");
     return launch_status("gemv_w4a8");
 }
@@ -237,8 +239,11 @@ inline int launch_gemv_st(const int8_t *xq, const float *xs, const uint8_t *Wq, 
                           int IN, int OUT, int S, cudaStream_t st) {
     const int nb = IN / QBLK;
     // Rows beyond GEMV_MT_MAX go in further passes over the weights (which then come from L2).
+    OutArgs &oa = current_out();
+    const size_t y_off0 = oa.y_off;
     for (int s0 = 0; s0 < S; s0 += GEMV_MT_MAX) {
         const int s = S - s0 < GEMV_MT_MAX ? S - s0 : GEMV_MT_MAX;
+        if (oa.peers) oa.y_off = y_off0 + (size_t)s0 * oa.ld * sizeof(float);
         const int8_t *xq_p = xq + (size_t)s0 * IN;
         const float *xs_p = xs + (size_t)s0 * nb;
         float *y_p = Y + (size_t)s0 * OUT;
@@ -249,8 +254,9 @@ inline int launch_gemv_st(const int8_t *xq, const float *xs, const uint8_t *Wq, 
             case 3: rc = launch_gemv_dp4a_u<3, ST>(xq_p, xs_p, Wq, sw, y_p, IN, OUT, s, st); break;
             default: rc = launch_gemv_dp4a_u<4, ST>(xq_p, xs_p, Wq, sw, y_p, IN, OUT, s, st); break;
         }
-        if (rc != W4A8_OK) return rc;
+        if (rc != W4A8_OK) { oa.y_off = y_off0; return rc; }
     }
+    oa.y_off = y_off0;
     return W4A8_OK;
 }
 

@@ -72,7 +72,7 @@ __device__ __forceinline__ int swz(int r, int GS) { return GS >= 8 ? (r & 7) : (
 template <int MH, int GS, int STAGES, typename ST>
 __global__ void __launch_bounds__(WARPS * 32, 1) gemv_w4a8_mma_kernel(
     const int8_t *__restrict__ xq, const float *__restrict__ xs, const uint8_t *__restrict__ Wq,
-    const ST *__restrict__ sw, float *__restrict__ Y, int IN, int OUT, int S) {
+    const ST *__restrict__ sw, float *__restrict__ Y, int IN, int OUT, int S, OutArgs oa) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int STEP_W = step_w(GS), STEP_BYTES = step_bytes(GS);
     const int nb = IN / QBLK, nsteps = nb / GS;       // nb % GS == 0 is a launch precondition
@@ -223,16 +223,17 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_w4a8_mma_kernel(
         for (int h = 0; h < MH; h++) {
             const int m0 = 8 * h + 2 * t, rA = base + g, rB = base + 8 + g;
             if (rA < lim) {
-                if (m0 < S) Y[(size_t)m0 * OUT + rA] = acc[h][0];
-                if (m0 + 1 < S) Y[(size_t)(m0 + 1) * OUT + rA] = acc[h][1];
+                if (m0 < S) store_out(Y, oa, OUT, m0, rA, acc[h][0]);
+                if (m0 + 1 < S) store_out(Y, oa, OUT, m0 + 1, rA, acc[h][1]);
             }
             if (rB < lim) {
-                if (m0 < S) Y[(size_t)m0 * OUT + rB] = acc[h][2];
-                if (m0 + 1 < S) Y[(size_t)(m0 + 1) * OUT + rB] = acc[h][3];
+                if (m0 < S) store_out(Y, oa, OUT, m0, rB, acc[h][2]);
+                if (m0 + 1 < S) store_out(Y, oa, OUT, m0 + 1, rB, acc[h][3]);
             }
         }
     }
     cp_async_wait<0>();
+    publish_out(oa);
 }
 
 // Launch plan: groups per step (the largest of 16, 8 that divides the group count), ring depth and rows per pass
@@ -276,7 +277,7 @@ inline int launch_t(const int8_t *xq, const float *xs, const uint8_t *Wq, const 
     long want = (units + 1) / 2;                         // at least one 16-row tile per CTA
     long cap = sm_count();                               // one persistent CTA per SM
     const dim3 grid((unsigned)(want < cap ? want : cap));
-    cudaError_t le = launch_pdl(kern, grid, dim3(WARPS * 32), smem, st, xq, xs, Wq, sw, Y, IN, OUT, S);
+    cudaError_t le = launch_pdl(kern, grid, dim3(WARPS * 32), smem, st, xq, xs, Wq, sw, Y, IN, OUT, S, current_out());
     if (le != cudaSuccess) return cuda_fail(le, "gemv_w4a8_mma launch");
     return launch_status("gemv_w4a8_mma");
 }

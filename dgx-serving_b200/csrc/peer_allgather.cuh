@@ -1,0 +1,89 @@
+// Fused GEMV + all-gather for N-sharded weights (no counterpart in the reference, which is single-GPU).
+// Every rank holds rows [row0, row0+rows) of Wq / sw and computes Y[:, row0:row0+rows].  Instead of a collective
+// after the kernel, the GEMV epilogue stores each output straight into EVERY rank's Y at its final address
+// (plain st.global through peer-mapped pointers over NVLink: 4 bytes x world per output, 8.7 KB per peer at M=1),
+// and the last CTA to finish publishes a per-rank flag on every peer.  A consumer waits (bounded) until all `world`
+// flags of its own arena have reached the step's epoch.  No TMA, no multicast: peer memory is only ever the target
+// of ordinary stores and the flags are ordinary release stores / acquire loads.
+//
+// Arena layout (one per rank, same size everywhere): [ user bytes ... | 256-byte tail: flags[8] u32, counter u32 ].
+#pragma once
+#include "common.cuh"
+
+namespace w4a8 {
+
+constexpr int PEER_MAX = 8;
+constexpr size_t PEER_TAIL = 256;
+
+struct PeerDesc {                   // lives in device memory of the owning rank
+    unsigned char *base[PEER_MAX];  // arena base of every rank as mapped into this process (base[rank] = local)
+    unsigned int *counter;          // local: CTAs of the running kernel that have finished their stores
+    size_t flag_off;                // byte offset of flags[] inside every arena
+    int world, rank;
+};
+
+struct OutArgs {                    // passed by value to the GEMV kernels; peers == nullptr: ordinary Y[m*OUT + r]
+    const PeerDesc *peers = nullptr;
+    size_t y_off = 0;               // byte offset of Y[M, ld] inside every arena
+    long ld = 0, col0 = 0;          // row pitch of the gathered Y (= total N) and this rank's first column (= row0)
+    unsigned int epoch = 0;         // value published in the flags when this launch's stores are complete
+    int publish = 0;                // 1: the last CTA of this launch publishes; 0: a later launch of the same call does
+};
+
+// Set by w4a8_gemv_allgather around its call into the ordinary launch path (single host thread per device).
+inline OutArgs &current_out() { static OutArgs o; return o; }
+
+__device__ __forceinline__ void store_out(float *Y, const OutArgs &oa, int OUT, int m, int r, float v) {
+    if (!oa.peers) { Y[(size_t)m * OUT + r] = v; return; }
+    const PeerDesc *p = oa.peers;
+    const int world = p->world;
+    for (int k = 0; k < world; k++)
+        reinterpret_cast<float *>(p->base[k] + oa.y_off)[(size_t)m * oa.ld + oa.col0 + r] = v;
+}
+
+// Called by every thread of every CTA after its last store.
+__device__ __forceinline__ void publish_out(const OutArgs &oa) {
+    if (!oa.peers || !oa.publish) return;
+    __threadfence_system();                        // this thread's peer stores are visible system-wide
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const PeerDesc *p = oa.peers;
+        const unsigned total = gridDim.x * gridDim.y;
+        const unsigned prev = atomicAdd(p->counter, 1u);
+        if (prev == total - 1) {                   // last CTA: all CTAs' stores are fenced
+            *p->counter = 0u;
+            __threadfence_system();
+            for (int k = 0; k < p->world; k++) {
+                unsigned int *f = reinterpret_cast<unsigned int *>(p->base[k] + p->flag_off) + p->rank;
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(oa.epoch) : "memory");
+            }
+        }
+    }
+}
+
+// Publishes `epoch` after earlier launches of the same stream (which stored without publishing) have completed.
+__global__ void allgather_publish_kernel(const PeerDesc *p, unsigned int epoch) {
+    if (threadIdx.x != 0) return;
+    __threadfence_system();
+    for (int k = 0; k < p->world; k++) {
+        unsigned int *f = reinterpret_cast<unsigned int *>(p->base[k] + p->flag_off) + p->rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
+    }
+}
+
+// One warp; lane r < world waits until rank r's flag in THIS rank's arena has reached `epoch`.  Bounded: after
+// `limit_cycles` SM clocks the lane gives up and records an error (w4a8_device_status) instead of spinning on.
+__global__ void allgather_wait_kernel(const PeerDesc *p, unsigned int epoch, long long limit_cycles) {
+    const int r = threadIdx.x;
+    if (r >= p->world) return;
+    const unsigned int *f = reinterpret_cast<const unsigned int *>(p->base[p->rank] + p->flag_off) + r;
+    const long long t0 = clock64();
+    for (;;) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+        if ((int)(v - epoch) >= 0) return;
+        if (clock64() - t0 > limit_cycles) { dev_set_error(0x200u | (unsigned)r); return; }
+    }
+}
+
+}  // namespace w4a8

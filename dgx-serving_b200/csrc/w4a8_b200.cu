@@ -141,6 +141,37 @@ static bool gemv_use_mma(int S) {
     return p == 2 || (p == 0 && S >= 2);
 }
 
+// The one place that decides which GEMV kernel runs and in how many launches.  count_only != nullptr: nothing is
+// launched, *count_only receives the number of kernel launches the call would make.
+static int gemv_dispatch(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int IN, int OUT, int S,
+                         int scale_dtype, cudaStream_t st, int *count_only) {
+    if (gemv_use_mma(S)) {
+        // rows go in passes of up to 16 (8 when 16 rows of activations do not fit in shared memory next to the ring)
+        gemv_mma::Plan plan;
+        int per = S < 16 ? S : 16;
+        bool ok = gemv_mma::plan_for(Wq, sw, IN, per, &plan);
+        if (!ok && per > 8) { per = 8; ok = gemv_mma::plan_for(Wq, sw, IN, per, &plan); }
+        if (ok) {
+            if (count_only) { *count_only = (S + per - 1) / per; return W4A8_OK; }
+            OutArgs &oa = current_out();
+            for (int s0 = 0; s0 < S; s0 += per) {
+                const int s = S - s0 < per ? S - s0 : per;
+                gemv_mma::Plan pl = plan;
+                if (s <= 8 && pl.MH == 2) gemv_mma::plan_for(Wq, sw, IN, s, &pl);
+                const size_t y_off0 = oa.y_off;
+                if (oa.peers) oa.y_off = y_off0 + (size_t)s0 * oa.ld * sizeof(float);
+                int rc = gemv_mma::launch(xq + (size_t)s0 * IN, xs + (size_t)s0 * (IN / QBLK), Wq, sw, Y + (size_t)s0 * OUT, IN, OUT, s,
+                                          scale_dtype, pl, st);
+                oa.y_off = y_off0;
+                if (rc != W4A8_OK) return rc;
+            }
+            return W4A8_OK;
+        }
+    }
+    if (count_only) { *count_only = (S + GEMV_MT_MAX - 1) / GEMV_MT_MAX; return W4A8_OK; }
+    return launch_gemv(xq, xs, Wq, sw, Y, IN, OUT, S, scale_dtype, st);
+}
+
 W4A8_API int w4a8_config(const char *key, int value) {
     if (!key) return fail(W4A8_ERR_ARG, "config: null key");
     if (!strcmp(key, "gemv_kernel")) {
@@ -164,26 +195,7 @@ W4A8_API int w4a8_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, con
         cudaError_t e = cudaMemsetAsync(Y, 0, (size_t)S * OUT * sizeof(float), (cudaStream_t)stream);
         return e == cudaSuccess ? W4A8_OK : cuda_fail(e, "gemv: memset");
     }
-    // Kernel choice.  W4A8_GEMV=dp4a / mma forces one formulation (measurements); default: see gemv_kernel_choice.
-    if (gemv_use_mma(S)) {
-        // rows go in passes of up to 16 (8 when 16 rows of activations do not fit in shared memory next to the ring)
-        gemv_mma::Plan plan;
-        int per = S < 16 ? S : 16;
-        bool ok = gemv_mma::plan_for(Wq, sw, IN, per, &plan);
-        if (!ok && per > 8) { per = 8; ok = gemv_mma::plan_for(Wq, sw, IN, per, &plan); }
-        if (ok) {
-            for (int s0 = 0; s0 < S; s0 += per) {
-                const int s = S - s0 < per ? S - s0 : per;
-                gemv_mma::Plan pl = plan;
-                if (s <= 8 && pl.MH == 2) gemv_mma::plan_for(Wq, sw, IN, s, &pl);
-                rc = gemv_mma::launch(xq + (size_t)s0 * IN, xs + (size_t)s0 * (IN / QBLK), Wq, sw, Y + (size_t)s0 * OUT, IN, OUT, s,
-                                      scale_dtype, pl, (cudaStream_t)stream);
-                if (rc != W4A8_OK) return rc;
-            }
-            return W4A8_OK;
-        }
-    }
-    return launch_gemv(xq, xs, Wq, sw, Y, IN, OUT, S, scale_dtype, (cudaStream_t)stream);
+    return gemv_dispatch(xq, xs, Wq, sw, Y, IN, OUT, S, scale_dtype, (cudaStream_t)stream, nullptr);
 }
 
 W4A8_API int w4a8_gemm(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int M, int N, int K,
@@ -446,4 +458,117 @@ W4A8_API int w4a8_free_qmat(w4a8_qmat *m) {
     m->wq = nullptr;
     m->sc = nullptr;
     return W4A8_OK;
+}
+
+// ---- arenas, IPC, fused GEMV + all-gather ---------------------------------------------------------------------
+struct w4a8_arena {
+    unsigned char *base = nullptr;      // local allocation: user bytes + PEER_TAIL
+    size_t bytes = 0;                   // user bytes
+    int rank = 0, world = 1;
+    PeerDesc *desc_dev = nullptr;       // device copy of the descriptor (valid after connect)
+    bool connected = false;
+};
+
+W4A8_API int w4a8_arena_create(size_t bytes, int rank, int world, w4a8_arena **out) {
+    if (!out || world < 1 || world > PEER_MAX || rank < 0 || rank >= world)
+        return fail(W4A8_ERR_ARG, "arena_create: rank=%d world=%d (1..%d ranks)", rank, world, PEER_MAX);
+    int rc = require_sm100();
+    if (rc != W4A8_OK) return rc;
+    w4a8_arena *a = new w4a8_arena();
+    a->bytes = (bytes + 255) & ~(size_t)255;
+    a->rank = rank; a->world = world;
+    cudaError_t e = cudaMalloc((void **)&a->base, a->bytes + PEER_TAIL);
+    if (e == cudaSuccess) e = cudaMemset(a->base, 0, a->bytes + PEER_TAIL);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&a->desc_dev, sizeof(PeerDesc));
+    if (e != cudaSuccess) { if (a->base) cudaFree(a->base); delete a; return cuda_fail(e, "arena_create"); }
+    *out = a;
+    return W4A8_OK;
+}
+W4A8_API void *w4a8_arena_base(w4a8_arena *a) { return a ? a->base : nullptr; }
+
+W4A8_API int w4a8_arena_connect(w4a8_arena *a, void *const *bases) {
+    if (!a || !bases) return fail(W4A8_ERR_ARG, "arena_connect: null argument");
+    PeerDesc d = {};
+    for (int r = 0; r < a->world; r++) {
+        d.base[r] = (r == a->rank) ? a->base : (unsigned char *)bases[r];
+        if (!d.base[r]) return fail(W4A8_ERR_ARG, "arena_connect: no mapping for rank %d", r);
+    }
+    d.flag_off = a->bytes;
+    d.counter = reinterpret_cast<unsigned int *>(a->base + a->bytes + PEER_MAX * sizeof(unsigned int));
+    d.world = a->world; d.rank = a->rank;
+    cudaError_t e = cudaMemcpy(a->desc_dev, &d, sizeof(d), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return cuda_fail(e, "arena_connect");
+    a->connected = true;
+    return W4A8_OK;
+}
+
+W4A8_API int w4a8_arena_destroy(w4a8_arena *a) {
+    if (!a) return W4A8_OK;
+    if (a->desc_dev) cudaFree(a->desc_dev);
+    if (a->base) cudaFree(a->base);
+    delete a;
+    return W4A8_OK;
+}
+
+W4A8_API int w4a8_ipc_export(void *dev_ptr, unsigned char handle[64]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handle size");
+    if (!dev_ptr || !handle) return fail(W4A8_ERR_ARG, "ipc_export: null argument");
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, dev_ptr);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaIpcGetMemHandle");
+    memcpy(handle, &h, 64);
+    return W4A8_OK;
+}
+W4A8_API int w4a8_ipc_open(const unsigned char handle[64], void **dev_ptr) {
+    if (!dev_ptr || !handle) return fail(W4A8_ERR_ARG, "ipc_open: null argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    cudaError_t e = cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaIpcOpenMemHandle");
+    return W4A8_OK;
+}
+W4A8_API int w4a8_ipc_close(void *dev_ptr) {
+    if (!dev_ptr) return W4A8_OK;
+    cudaError_t e = cudaIpcCloseMemHandle(dev_ptr);
+    return e == cudaSuccess ? W4A8_OK : cuda_fail(e, "cudaIpcCloseMemHandle");
+}
+
+W4A8_API int w4a8_gemv_allgather(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a, size_t y_offset,
+                                 int IN, int rows, int row0, int ldY, int S, int scale_dtype, uint32_t epoch, void *stream) {
+    if (!a || !a->connected) return fail(W4A8_ERR_ARG, "gemv_allgather: arena not connected");
+    if (S < 0 || rows < 0 || row0 < 0 || ldY < row0 + rows) return fail(W4A8_ERR_ARG, "gemv_allgather: bad shape S=%d rows=%d row0=%d ldY=%d", S, rows, row0, ldY);
+    if (y_offset % 16 != 0 || y_offset + (size_t)S * ldY * sizeof(float) > a->bytes)
+        return fail(W4A8_ERR_ARG, "gemv_allgather: Y[%d x %d] at offset %zu does not fit the %zu-byte arena", S, ldY, y_offset, a->bytes);
+    if (IN <= 0) return fail(W4A8_ERR_ARG, "gemv_allgather: IN must be positive");
+    cudaStream_t st = (cudaStream_t)stream;
+    float *Ylocal = reinterpret_cast<float *>(a->base + y_offset);   // unused by the peer path; keeps the argument checks happy
+    int launches = 1;
+    if (S > 0 && rows > 0) {
+        int rc = check_common(xq, xs, Wq, sw, Ylocal, IN, scale_dtype, "gemv_allgather");
+        if (rc != W4A8_OK) return rc;
+        rc = gemv_dispatch(xq, xs, Wq, sw, Ylocal, IN, rows, S, scale_dtype, st, &launches);
+        if (rc != W4A8_OK) return rc;
+    } else {
+        launches = 0;
+    }
+    OutArgs &oa = current_out();
+    oa.peers = a->desc_dev; oa.y_off = y_offset; oa.ld = ldY; oa.col0 = row0; oa.epoch = epoch;
+    oa.publish = launches == 1 ? 1 : 0;
+    int rc = W4A8_OK;
+    if (launches > 0) rc = w4a8_gemv(xq, xs, Wq, sw, Ylocal, IN, rows, S, scale_dtype, stream);
+    oa = OutArgs();
+    if (rc != W4A8_OK) return rc;
+    if (launches != 1) {   // several passes (or nothing to compute): publish once they are all complete
+        allgather_publish_kernel<<<1, 32, 0, st>>>(a->desc_dev, epoch);
+        return launch_status("allgather_publish");
+    }
+    return W4A8_OK;
+}
+
+W4A8_API int w4a8_allgather_wait(w4a8_arena *a, uint32_t epoch, int timeout_us, void *stream) {
+    if (!a || !a->connected) return fail(W4A8_ERR_ARG, "allgather_wait: arena not connected");
+    if (timeout_us <= 0) timeout_us = 1000000;
+    const long long limit = (long long)timeout_us * 2000;            // SM clock <= 2 GHz: at least timeout_us
+    allgather_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(a->desc_dev, epoch, limit);
+    return launch_status("allgather_wait");
 }

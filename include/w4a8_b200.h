@@ -179,6 +179,36 @@ int w4a8_upload_qmat_shard(const uint8_t *host_wq, const void *host_sc, int64_t 
                            int scale_dtype, int rank, int world, w4a8_qmat *out);
 int w4a8_free_qmat(w4a8_qmat *m);
 
+/* ---- N-sharded GEMV with the all-gather fused into the epilogue ------------------------------------------
+ * New for multi-GPU; the reference is single-GPU and has nothing to replace here.  One process per GPU.
+ * Every rank owns an ARENA: device memory that all ranks of the box map (CUDA IPC, or any other peer mapping the
+ * caller has), holding the gathered outputs plus a small tail of flags.  w4a8_gemv_allgather runs the ordinary
+ * GEMV on the rank's row shard, but its epilogue stores each result into EVERY rank's arena at the final address
+ * of Y[M, ldY] (plain peer stores over NVLink; no collective, no TMA), and publishes `epoch` in a flag on every
+ * rank when its stores are complete.  w4a8_allgather_wait enqueues a kernel that waits until all ranks' flags in
+ * the local arena have reached `epoch`; work enqueued after it on the same stream sees the complete Y.
+ * The wait is bounded: after timeout_us it records a device error (w4a8_device_status returns W4A8_ERR_DEVICE)
+ * and returns, leaving the context usable.
+ * Rules: epochs of successive steps must increase; a rank may start step e+1 only after its own wait for step e
+ * (stream order does that), and Y buffers of consecutive steps must alternate between two offsets, because a
+ * fast rank's step e+1 stores may land while a slow rank still reads step e.  At most 8 ranks. */
+typedef struct w4a8_arena w4a8_arena;
+int w4a8_arena_create(size_t bytes, int rank, int world, w4a8_arena **out);   /* cudaMalloc'd, zeroed */
+void *w4a8_arena_base(w4a8_arena *a);                                          /* local device pointer */
+/* bases[r] = arena base of rank r as mapped into THIS process (bases[rank] is ignored and taken as local). */
+int w4a8_arena_connect(w4a8_arena *a, void *const *bases);
+int w4a8_arena_destroy(w4a8_arena *a);
+/* CUDA IPC helpers for the mapping: export the local arena's 64-byte handle, open / close a peer's. */
+int w4a8_ipc_export(void *dev_ptr, unsigned char handle[64]);
+int w4a8_ipc_open(const unsigned char handle[64], void **dev_ptr);
+int w4a8_ipc_close(void *dev_ptr);
+/* Y lives at byte offset y_offset in every arena, row pitch ldY floats; this rank writes columns
+ * [row0, row0+rows).  Other arguments as w4a8_gemv with OUT = rows. */
+int w4a8_gemv_allgather(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a,
+                        size_t y_offset, int IN, int rows, int row0, int ldY, int S, int scale_dtype,
+                        uint32_t epoch, void *stream);
+int w4a8_allgather_wait(w4a8_arena *a, uint32_t epoch, int timeout_us, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
