@@ -206,12 +206,17 @@ def run_ours(args):
             return float(t.item())
         return ms
 
-    def time_steps(step_fn, steps, warmup, graph):
-        """step_fn(i, stream_handle) enqueues one step.  Returns ms for exactly `steps` steps (max over ranks)."""
+    def time_steps(step_fn, steps, warmup, graph, after_fn=None):
+        """step_fn(i, stream_handle) enqueues one step; after_fn(n, stream_handle), if given, is enqueued after every
+        block of n steps (eager warm-up block, and as the last node of the captured graph).  Returns ms for exactly
+        `steps` steps (max over ranks)."""
         s = torch.cuda.Stream()
         with torch.cuda.stream(s):
-            for i in range(max(warmup, 3)):
+            nw = max(warmup, 3)
+            for i in range(nw):
                 step_fn(i, s.cuda_stream)
+            if after_fn:
+                after_fn(nw, s.cuda_stream)
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             if graph:
@@ -219,6 +224,8 @@ def run_ours(args):
                 with torch.cuda.graph(gr, stream=s):
                     for i in range(steps):
                         step_fn(i, s.cuda_stream)
+                    if after_fn:
+                        after_fn(steps, s.cuda_stream)
                 gr.replay()          # one untimed replay: graph upload
                 barrier()
                 e0.record(s)
@@ -229,21 +236,45 @@ def run_ours(args):
                 e0.record(s)
                 for i in range(steps):
                     step_fn(i, s.cuda_stream)
+                if after_fn:
+                    after_fn(steps, s.cuda_stream)
                 e1.record(s)
             torch.cuda.synchronize()
             barrier()
         return max_over_ranks(e0.elapsed_time(e1))
 
     # ---- headline: GEMV M=1 (N-sharded + all-gather when world > 1) -------------------------------------
-    def gemv_case(M, steps, warmup):
+    def gemv_case(M, steps, warmup, mode="fused"):
+        """One step = the rank-local GEMV plus (world > 1) the exchange that leaves the whole Y[M, N] on every rank:
+        mode "fused": peer stores from the GEMV epilogue + flag wait (w4a8_gemv_allgather / w4a8_allgather_wait);
+        mode "nccl":  GEMV into a local slice, then an NCCL all-gather."""
         Xh, Xd, xq, xs, xsum = make_x(M)
         Yloc = torch.empty((M, rows), dtype=torch.float32, device=dev)
+        after = None
+        if world > 1 and mode == "fused":
+            ystride = (M * N * 4 + 255) // 256 * 256
+            arena = w.Arena(2 * ystride, rank, world)
+            handles = [None] * world
+            dist.all_gather_object(handles, arena.export_handle())
+            arena.connect_handles(handles)
+            dist.barrier()
 
-        def step(i, st):
-            w.launch_gemv_w4a8_sb(xq, xs, Wqs[i % nbuf], sws[i % nbuf], Yloc, K, rows, M, 0, st)
-            if world > 1:
-                sharded.all_gather_columns(Yloc, plan)     # NCCL all-gather -> Y[M, N] on every rank
-        ms = time_steps(step, steps, warmup, graph=(world == 1))
+            def step(i, st):
+                arena.gemv_allgather(xq, xs, Wqs[i % nbuf], sws[i % nbuf], (i % 2) * ystride, K, rows, row0, N, M, 0, i + 1, st)
+                arena.wait(i + 1, 2000000, st)
+
+            def after(n, st):
+                arena.advance_epoch(n, st)
+        else:
+            def step(i, st):
+                w.launch_gemv_w4a8_sb(xq, xs, Wqs[i % nbuf], sws[i % nbuf], Yloc, K, rows, M, 0, st)
+                if world > 1:
+                    sharded.all_gather_columns(Yloc, plan)     # NCCL all-gather -> Y[M, N] on every rank
+        ms = time_steps(step, steps, warmup, graph=(world == 1 or mode == "fused"), after_fn=after)
+        if world > 1 and mode == "fused":
+            w.device_status()
+            barrier()
+            arena.close()
         total_bytes = gemv_bytes(M, N, K)          # all ranks together stream the whole matrix once per step
         return ms, total_bytes * steps / (ms * 1e-3) / 1e9, (Xh, Xd, xq, xs, xsum)
 
@@ -274,6 +305,14 @@ def run_ours(args):
     e2e_gbps = gemv_bytes(1, N, K) * e2e_steps / (ms_e * 1e-3) / 1e9
 
     extra = {}
+    if world > 1:
+        ms_n, gb_n, _ = gemv_case(1, args.steps, args.warmup, mode="nccl")
+        extra["nccl_allgather_path"] = {"ms_per_step": ms_n / args.steps, "gbps": gb_n}
+        sw_ = {}
+        for M in (8, 16):
+            ms_m, gb_m, _ = gemv_case(M, max(20, args.steps // 2), 3)
+            sw_[str(M)] = {"us": ms_m * 1e3 / max(20, args.steps // 2), "gbps": gb_m}
+        extra["gemv_sweep_fused_allgather"] = sw_
     if world == 1:
         # ---- sweep M = 2..16 on the same shape ------------------------------------------------------------
         sweep = {"1": {"us": per_launch_us, "gbps": achieved, "frac_of_measured_hbm": achieved / hbm_peak,
@@ -340,9 +379,10 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "i8", "data": "synthetic",
             "config": {"workload": "W4A8 decode GEMV M=1 K=5120 N=17408, int4 group-32 weights + fp32 scales (BASELINE configs[1])",
-                       "parallelism": "n-shard x%d + nccl all-gather" % world if world > 1 else "single GPU",
+                       "parallelism": ("n-shard x%d, all-gather fused into the GEMV epilogue (peer stores over NVLink + flag wait)" % world)
+                       if world > 1 else "single GPU",
                        "l2": "rotating %d distinct weight copies per rank (%.0f MB > 126 MB L2)" % (nbuf, nbuf * shard_bytes / 1e6),
-                       "launch": "CUDA graph of %d launches" % args.steps if world == 1 else "stream launches + NCCL"},
+                       "launch": "CUDA graph of %d steps" % args.steps},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": NCU_TRAFFIC["gemv_m1"] if world == 1 else None, "peak_kind": "of " + peak_kind,
                          "kernel": "gemv_w4a8 M=1, rank-local slice of %d rows" % rows, "us_per_launch": per_launch_us,
@@ -350,7 +390,7 @@ def run_ours(args):
             "cpu_baseline": cpu_baseline,
             "e2e": {"value": e2e_gbps, "unit": "GB/s", "h2d_bytes_per_step": K * 4, "d2h_bytes_per_step": rows * 4,
                     "ms_per_step": ms_e / e2e_steps, "path": "pinned host X -> w4a8_linear (quantize_x + gemv) -> pinned host Y"},
-            "gpu_launches": args.steps * (1 if world == 1 else 1),
+            "gpu_launches": args.steps * (1 if world == 1 else 2),
             "clocks": clocks,
             "extra": extra,
         }

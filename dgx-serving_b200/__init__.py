@@ -63,6 +63,7 @@ _SIGNATURES = {
     "w4a8_ipc_close": (_I, [_P]),
     "w4a8_gemv_allgather": (_I, [_P, _P, _P, _P, _P, _Z, _I, _I, _I, _I, _I, _I, ctypes.c_uint32, _P]),
     "w4a8_allgather_wait": (_I, [_P, ctypes.c_uint32, _I, _P]),
+    "w4a8_arena_advance_epoch": (_I, [_P, ctypes.c_uint32, _P]),
 }
 EXPORTS = tuple(_SIGNATURES)
 
@@ -254,6 +255,9 @@ class Arena:
 
     def wait(self, epoch, timeout_us=1000000, stream=None):
         _check(lib().w4a8_allgather_wait(self.handle, epoch, timeout_us, _stream(stream)))
+
+    def advance_epoch(self, delta, stream=None):
+        _check(lib().w4a8_arena_advance_epoch(self.handle, delta, _stream(stream)))
 
     def close(self):
         for p in self._opened:

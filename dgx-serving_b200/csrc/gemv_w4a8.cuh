@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_dp4a_kernel(
         if (batch == nbatch - 1) finish_row(row);
         row = nrow; batch = nbt;
     }
-    publish_out(oa);
+    publish_out(oa, lane == 0);
 }
 
 template <int MT, int U, typename ST>

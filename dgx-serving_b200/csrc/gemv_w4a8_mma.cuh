@@ -233,7 +233,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_w4a8_mma_kernel(
         }
     }
     cp_async_wait<0>();
-    publish_out(oa);
+    publish_out(oa, 2 * t < S || MH == 2);          // lanes whose columns m = 8h + 2t (+1) exist
 }
 
 // Launch plan: groups per step (the largest of 16, 8 that divides the group count), ring depth and rows per pass

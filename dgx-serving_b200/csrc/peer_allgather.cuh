@@ -6,7 +6,7 @@
 // flags of its own arena have reached the step's epoch.  No TMA, no multicast: peer memory is only ever the target
 // of ordinary stores and the flags are ordinary release stores / acquire loads.
 //
-// Arena layout (one per rank, same size everywhere): [ user bytes ... | 256-byte tail: flags[8] u32, counter u32 ].
+// Arena layout (one per rank, same size everywhere): [ user bytes ... | 256-byte tail: flags[8], counter, epoch base ].
 #pragma once
 #include "common.cuh"
 
@@ -18,6 +18,7 @@ constexpr size_t PEER_TAIL = 256;
 struct PeerDesc {                   // lives in device memory of the owning rank
     unsigned char *base[PEER_MAX];  // arena base of every rank as mapped into this process (base[rank] = local)
     unsigned int *counter;          // local: CTAs of the running kernel that have finished their stores
+    unsigned int *epoch_base;       // local: added to every epoch argument (lets a captured graph be replayed)
     size_t flag_off;                // byte offset of flags[] inside every arena
     int world, rank;
 };
@@ -41,10 +42,11 @@ __device__ __forceinline__ void store_out(float *Y, const OutArgs &oa, int OUT, 
         reinterpret_cast<float *>(p->base[k] + oa.y_off)[(size_t)m * oa.ld + oa.col0 + r] = v;
 }
 
-// Called by every thread of every CTA after its last store.
-__device__ __forceinline__ void publish_out(const OutArgs &oa) {
+// Called by every thread of every CTA after its last store; `stored` = this thread wrote outputs (only those
+// threads pay for the system-scope fence).
+__device__ __forceinline__ void publish_out(const OutArgs &oa, bool stored = true) {
     if (!oa.peers || !oa.publish) return;
-    __threadfence_system();                        // this thread's peer stores are visible system-wide
+    if (stored) __threadfence_system();            // this thread's peer stores are visible system-wide
     __syncthreads();
     if (threadIdx.x == 0) {
         const PeerDesc *p = oa.peers;
@@ -53,9 +55,10 @@ __device__ __forceinline__ void publish_out(const OutArgs &oa) {
         if (prev == total - 1) {                   // last CTA: all CTAs' stores are fenced
             *p->counter = 0u;
             __threadfence_system();
+            const unsigned int e = *p->epoch_base + oa.epoch;
             for (int k = 0; k < p->world; k++) {
                 unsigned int *f = reinterpret_cast<unsigned int *>(p->base[k] + p->flag_off) + p->rank;
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(oa.epoch) : "memory");
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(e) : "memory");
             }
         }
     }
@@ -65,6 +68,7 @@ __device__ __forceinline__ void publish_out(const OutArgs &oa) {
 __global__ void allgather_publish_kernel(const PeerDesc *p, unsigned int epoch) {
     if (threadIdx.x != 0) return;
     __threadfence_system();
+    epoch += *p->epoch_base;
     for (int k = 0; k < p->world; k++) {
         unsigned int *f = reinterpret_cast<unsigned int *>(p->base[k] + p->flag_off) + p->rank;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
@@ -75,8 +79,14 @@ __global__ void allgather_publish_kernel(const PeerDesc *p, unsigned int epoch) 
 // `limit_cycles` SM clocks the lane gives up and records an error (w4a8_device_status) instead of spinning on.
 __global__ void allgather_wait_kernel(const PeerDesc *p, unsigned int epoch, long long limit_cycles) {
     const int r = threadIdx.x;
+    // Launched for programmatic dependent launch: resident early, and the kernel after it (typically the next GEMV,
+    // which may prefetch weights) may become resident too; polling starts only once this rank's own producer kernel
+    // has completed, so the only flags still outstanding are the ones other GPUs write.
+    pdl_launch_dependents();
+    pdl_wait();
     if (r >= p->world) return;
     const unsigned int *f = reinterpret_cast<const unsigned int *>(p->base[p->rank] + p->flag_off) + r;
+    epoch += *p->epoch_base;
     const long long t0 = clock64();
     for (;;) {
         unsigned int v;
@@ -84,6 +94,12 @@ __global__ void allgather_wait_kernel(const PeerDesc *p, unsigned int epoch, lon
         if ((int)(v - epoch) >= 0) return;
         if (clock64() - t0 > limit_cycles) { dev_set_error(0x200u | (unsigned)r); return; }
     }
+}
+
+// epoch_base += delta: the last node of a captured graph of `delta` steps, so that the next replay of the same graph
+// publishes and waits for fresh epochs.
+__global__ void allgather_advance_kernel(const PeerDesc *p, unsigned int delta) {
+    if (threadIdx.x == 0) *p->epoch_base += delta;
 }
 
 }  // namespace w4a8

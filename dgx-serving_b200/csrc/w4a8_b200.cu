@@ -495,6 +495,7 @@ W4A8_API int w4a8_arena_connect(w4a8_arena *a, void *const *bases) {
     }
     d.flag_off = a->bytes;
     d.counter = reinterpret_cast<unsigned int *>(a->base + a->bytes + PEER_MAX * sizeof(unsigned int));
+    d.epoch_base = d.counter + 1;
     d.world = a->world; d.rank = a->rank;
     cudaError_t e = cudaMemcpy(a->desc_dev, &d, sizeof(d), cudaMemcpyHostToDevice);
     if (e != cudaSuccess) return cuda_fail(e, "arena_connect");
@@ -569,6 +570,13 @@ W4A8_API int w4a8_allgather_wait(w4a8_arena *a, uint32_t epoch, int timeout_us, 
     if (!a || !a->connected) return fail(W4A8_ERR_ARG, "allgather_wait: arena not connected");
     if (timeout_us <= 0) timeout_us = 1000000;
     const long long limit = (long long)timeout_us * 2000;            // SM clock <= 2 GHz: at least timeout_us
-    allgather_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(a->desc_dev, epoch, limit);
+    cudaError_t le = launch_pdl(allgather_wait_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, (const PeerDesc *)a->desc_dev, (unsigned int)epoch, limit);
+    if (le != cudaSuccess) return cuda_fail(le, "allgather_wait launch");
     return launch_status("allgather_wait");
+}
+
+W4A8_API int w4a8_arena_advance_epoch(w4a8_arena *a, uint32_t delta, void *stream) {
+    if (!a || !a->connected) return fail(W4A8_ERR_ARG, "arena_advance_epoch: arena not connected");
+    allgather_advance_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(a->desc_dev, delta);
+    return launch_status("allgather_advance");
 }

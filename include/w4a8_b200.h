@@ -208,6 +208,10 @@ int w4a8_gemv_allgather(const int8_t *xq, const float *xs, const uint8_t *Wq, co
                         size_t y_offset, int IN, int rows, int row0, int ldY, int S, int scale_dtype,
                         uint32_t epoch, void *stream);
 int w4a8_allgather_wait(w4a8_arena *a, uint32_t epoch, int timeout_us, void *stream);
+/* The epoch a kernel publishes / waits for is `epoch` plus a per-arena base kept in device memory (initially 0).
+ * This enqueues base += delta.  A CUDA graph that captured steps with epochs 1..n ends with
+ * w4a8_arena_advance_epoch(a, n, stream), so that every replay (on all ranks alike) uses fresh epochs. */
+int w4a8_arena_advance_epoch(w4a8_arena *a, uint32_t delta, void *stream);
 
 #ifdef __cplusplus
 }
