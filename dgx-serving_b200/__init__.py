@@ -49,6 +49,7 @@ _SIGNATURES = {
     "w4a8_gemm_splitk_static": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "w4a8_group_dots": (_I, [_P, _P, _P, _I, _I, _I, _I, _P]),
     "w4a8_linear": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "w4a8_linear_host": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "w4a8_moe_gemv": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P]),
     "w4a8_shard_rows": (_I, [_L, _I, _I, ctypes.POINTER(_L), ctypes.POINTER(_L)]),
     "w4a8_load_qmat_shard": (_I, [ctypes.c_char_p, ctypes.c_char_p, _L, _L, _I, _I, _I, ctypes.POINTER(QMat)]),
@@ -177,6 +178,12 @@ def linear(X, xq, xs, xsum, Wq, sw, Y, S, N, K, scale_dtype=0, skip_quantize=0, 
     """The mm() dispatcher of the model graphs (models/qwen35_decode.cu:51-62)."""
     _check(lib().w4a8_linear(_ptr(X), _ptr(xq), _ptr(xs), _ptr(xsum), _ptr(Wq), _ptr(sw), _ptr(Y), S, N, K,
                              scale_dtype, skip_quantize, _stream(stream)))
+
+
+def linear_host(X_host, Y_host, X_dev, xq, xs, xsum, Y_dev, Wq, sw, S, N, K, scale_dtype=0, stream=None):
+    """mm() with host activations in and host results out (pinned torch tensors or raw host pointers); synchronous."""
+    _check(lib().w4a8_linear_host(_ptr(X_host), _ptr(Y_host), _ptr(X_dev), _ptr(xq), _ptr(xs), _ptr(xsum), _ptr(Y_dev), _ptr(Wq),
+                                  _ptr(sw), S, N, K, scale_dtype, _stream(stream)))
 
 
 def moe_gemv(xq, xs, Wq, sw, idx, Y, nslots, topk, x_per_slot, N, K, num_experts, scale_dtype=0, stream=None):

@@ -53,13 +53,24 @@ struct GemvBatch {
     float s[U];
 };
 
+// Scale of group b of a row.  fp16 scales are fetched as the aligned 32-bit word that holds the pair (b & ~1, b | 1)
+// when the row start is 4-byte aligned (two-byte loads cost the same requests for half the bytes).
+__device__ __forceinline__ float load_scale(const float *swrow, int b) { return swrow[b]; }
+__device__ __forceinline__ float load_scale(const __half *swrow, int b) {
+    if ((reinterpret_cast<uintptr_t>(swrow) & 3) == 0) {
+        const uint32_t w = reinterpret_cast<const uint32_t *>(swrow)[b >> 1];
+        return __half2float(__ushort_as_half((unsigned short)((b & 1) ? (w >> 16) : (w & 0xFFFFu))));
+    }
+    return __half2float(swrow[b]);
+}
+
 template <int U, typename ST>
 __device__ __forceinline__ void gemv_load_batch(GemvBatch<U, ST> &bt, const uint8_t *__restrict__ wrow,
                                                 const ST *__restrict__ swrow, int slot0, int lane, int nb, bool a16) {
 #pragma unroll
     for (int u = 0; u < U; u++) {
         const int b = lane + 32 * (slot0 + u);
-        if (b < nb) { bt.w[u] = ldg_w16(wrow + 16 * b, a16); bt.s[u] = sval(swrow[b]); }
+        if (b < nb) { bt.w[u] = ldg_w16(wrow + 16 * b, a16); bt.s[u] = load_scale(swrow, b); }
         else { bt.w[u] = make_uint4(0, 0, 0, 0); bt.s[u] = 0.f; }
     }
 }
@@ -92,7 +103,7 @@ __device__ __forceinline__ void gemv_compute_batch(const GemvBatch<U, ST> &bt, f
     }
 }
 
-template <int MT, int U, typename ST>
+template <int MT, int U, typename ST, bool PEER>
 __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_dp4a_kernel(
     const int8_t *__restrict__ xq, const float *__restrict__ xs, const uint8_t *__restrict__ Wq,
     const ST *__restrict__ sw, float *__restrict__ Y, int IN, int OUT, int S, bool w_a16, GroupedArgs ga, OutArgs oa) {
@@ -162,7 +173,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_dp4a_kernel(
             float v = acc[m];
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
-            if (lane == 0 && m < S) store_out(Y, oa, OUT, m, r, v);
+            if (lane == 0 && m < S) store_out<PEER>(Y, oa, OUT, m, r, v);
             acc[m] = 0.f;
         }
     };
@@ -180,15 +191,15 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_dp4a_kernel(
         if (batch == nbatch - 1) finish_row(row);
         row = nrow; batch = nbt;
     }
-    publish_out(oa, lane == 0);
+    publish_out<PEER>(oa, lane == 0);
 }
 
-template <int MT, int U, typename ST>
-inline int launch_gemv_dp4a_t(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y,
+template <int MT, int U, typename ST, bool PEER>
+inline int launch_gemv_dp4a_p(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y,
                               int IN, int OUT, int S, cudaStream_t st, const GroupedArgs &ga) {
     const int nb = IN / QBLK;
     const size_t smem = (size_t)MT * IN + (size_t)MT * nb * sizeof(float);
-    auto kern = gemv_w4a8_dp4a_kernel<MT, U, ST>;
+    auto kern = gemv_w4a8_dp4a_kernel<MT, U, ST, PEER>;
     if (smem > 48 * 1024) {
         static size_t configured = 0;   // grow-only; single host thread per device (library convention)
         if (smem > configured) {
@@ -216,6 +227,13 @@ inline int launch_gemv_dp4a_t(const int8_t *xq, const float *xs, const uint8_t *
     cudaError_t le = launch_pdl(kern, grid, dim3(GEMV_WARPS * 32), smem, st, xq, xs, Wq, sw, Y, IN, OUT, S, aligned(Wq, 16), ga, current_out());
     if (le != cudaSuccess) return cuda_fail(le, "gemv_w4a8 launch");
     return launch_status("gemv_w4a8");
+}
+
+template <int MT, int U, typename ST>
+inline int launch_gemv_dp4a_t(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y,
+                              int IN, int OUT, int S, cudaStream_t st, const GroupedArgs &ga) {
+    if (current_out().peers) return launch_gemv_dp4a_p<MT, U, ST, true>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga);
+    return launch_gemv_dp4a_p<MT, U, ST, false>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga);
 }
 
 template <int MT, typename ST>

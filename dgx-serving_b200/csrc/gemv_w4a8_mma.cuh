@@ -69,7 +69,7 @@ __host__ __device__ inline size_t smem_bytes(int MH, int S, int nb, int GS, int 
 // matrix hit eight different 16-byte bank groups (row pitch GS*16 B is a multiple of 128 B for GS >= 8).
 __device__ __forceinline__ int swz(int r, int GS) { return GS >= 8 ? (r & 7) : ((r >> 1) & 3); }
 
-template <int MH, int GS, int STAGES, typename ST>
+template <int MH, int GS, int STAGES, typename ST, bool PEER>
 __global__ void __launch_bounds__(WARPS * 32, 1) gemv_w4a8_mma_kernel(
     const int8_t *__restrict__ xq, const float *__restrict__ xs, const uint8_t *__restrict__ Wq,
     const ST *__restrict__ sw, float *__restrict__ Y, int IN, int OUT, int S, OutArgs oa) {
@@ -87,7 +87,12 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_w4a8_mma_kernel(
     const int u0 = (int)(((long)units * blockIdx.x) / gridDim.x), u1 = (int)(((long)units * (blockIdx.x + 1)) / gridDim.x);
     const int ntiles_cta = (u1 - u0 + 1) / 2;
     const int my_tiles = ntiles_cta > warp ? (ntiles_cta - warp + WARPS - 1) / WARPS : 0;
-    unsigned char *ring = ring0 + (size_t)warp * STAGES * STEP_BYTES;
+    // When the CTA has fewer tiles than warps (narrow matrices), the idle warps' ring slots are lent to the working
+    // ones: a warp that is alone with a long row range needs more bytes in flight to stream at full speed.
+    int mult = 1;
+    while (mult < 4 && ntiles_cta * mult * 2 <= WARPS) mult *= 2;
+    const int depth = STAGES * mult;
+    unsigned char *ring = ring0 + (size_t)warp * mult * STAGES * STEP_BYTES;   // only warps < ntiles_cta use theirs when mult > 1
     const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring);
     const size_t wpitch = (size_t)(IN / 2);
 
@@ -122,12 +127,12 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_w4a8_mma_kernel(
         }
         cp_async_commit();                                        // one group per step, also when empty
         if (++iq == nsteps) { iq = 0; it++; }
-        if (++isl == STAGES) isl = 0;
+        if (++isl == depth) isl = 0;
     };
 
     pdl_launch_dependents();
 #pragma unroll 1
-    for (int s = 0; s < STAGES - 1; s++) issue();                 // weights only: allowed before the dependency wait
+    for (int s = 0; s < depth - 1; s++) issue();                  // weights only: allowed before the dependency wait
     pdl_wait();
 
     // ---- stage the activations once per CTA -----------------------------------------------------------------
@@ -169,7 +174,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_w4a8_mma_kernel(
         for (int h = 0; h < MH; h++) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;
         for (int q = 0; q < nsteps; q++) {
             issue();
-            cp_async_wait<STAGES - 1>();
+            if (mult == 1) cp_async_wait<STAGES - 1>();
+            else if (mult == 2) cp_async_wait<2 * STAGES - 1>();
+            else cp_async_wait<4 * STAGES - 1>();
             __syncwarp();
             const uint32_t slot = ring_u32 + (uint32_t)csl * STEP_BYTES;
             const unsigned char *slot_p = ring + (size_t)csl * STEP_BYTES;
@@ -215,7 +222,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_w4a8_mma_kernel(
                 }
             }
             __syncwarp();                                  // the slot is refilled by the next iteration's copies
-            if (++csl == STAGES) csl = 0;
+            if (++csl == depth) csl = 0;
         }
         const int base = (u0 + 2 * (warp + ti * WARPS)) * 8;
         const int lim = min(OUT, u1 * 8);
@@ -223,17 +230,17 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_w4a8_mma_kernel(
         for (int h = 0; h < MH; h++) {
             const int m0 = 8 * h + 2 * t, rA = base + g, rB = base + 8 + g;
             if (rA < lim) {
-                if (m0 < S) store_out(Y, oa, OUT, m0, rA, acc[h][0]);
-                if (m0 + 1 < S) store_out(Y, oa, OUT, m0 + 1, rA, acc[h][1]);
+                if (m0 < S) store_out<PEER>(Y, oa, OUT, m0, rA, acc[h][0]);
+                if (m0 + 1 < S) store_out<PEER>(Y, oa, OUT, m0 + 1, rA, acc[h][1]);
             }
             if (rB < lim) {
-                if (m0 < S) store_out(Y, oa, OUT, m0, rB, acc[h][2]);
-                if (m0 + 1 < S) store_out(Y, oa, OUT, m0 + 1, rB, acc[h][3]);
+                if (m0 < S) store_out<PEER>(Y, oa, OUT, m0, rB, acc[h][2]);
+                if (m0 + 1 < S) store_out<PEER>(Y, oa, OUT, m0 + 1, rB, acc[h][3]);
             }
         }
     }
     cp_async_wait<0>();
-    publish_out(oa, 2 * t < S || MH == 2);          // lanes whose columns m = 8h + 2t (+1) exist
+    publish_out<PEER>(oa, 2 * t < S || MH == 2);          // lanes whose columns m = 8h + 2t (+1) exist
 }
 
 // Launch plan: groups per step (the largest of 16, 8 that divides the group count), ring depth and rows per pass
@@ -261,12 +268,12 @@ inline bool plan_for(const void *Wq, const void *sw, int IN, int S, Plan *p) {
     return false;
 }
 
-template <int MH, int GS, int STAGES, typename ST>
-inline int launch_t(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int IN, int OUT, int S,
+template <int MH, int GS, int STAGES, typename ST, bool PEER>
+inline int launch_p(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int IN, int OUT, int S,
                     cudaStream_t st) {
     const int nb = IN / QBLK;
     const size_t smem = smem_bytes(MH, S, nb, GS, STAGES);
-    auto kern = gemv_w4a8_mma_kernel<MH, GS, STAGES, ST>;
+    auto kern = gemv_w4a8_mma_kernel<MH, GS, STAGES, ST, PEER>;
     static size_t configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -280,6 +287,13 @@ inline int launch_t(const int8_t *xq, const float *xs, const uint8_t *Wq, const 
     cudaError_t le = launch_pdl(kern, grid, dim3(WARPS * 32), smem, st, xq, xs, Wq, sw, Y, IN, OUT, S, current_out());
     if (le != cudaSuccess) return cuda_fail(le, "gemv_w4a8_mma launch");
     return launch_status("gemv_w4a8_mma");
+}
+
+template <int MH, int GS, int STAGES, typename ST>
+inline int launch_t(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int IN, int OUT, int S,
+                    cudaStream_t st) {
+    if (current_out().peers) return launch_p<MH, GS, STAGES, ST, true>(xq, xs, Wq, sw, Y, IN, OUT, S, st);
+    return launch_p<MH, GS, STAGES, ST, false>(xq, xs, Wq, sw, Y, IN, OUT, S, st);
 }
 
 template <typename ST>

@@ -34,8 +34,10 @@ struct OutArgs {                    // passed by value to the GEMV kernels; peer
 // Set by w4a8_gemv_allgather around its call into the ordinary launch path (single host thread per device).
 inline OutArgs &current_out() { static OutArgs o; return o; }
 
+// PEER is a template parameter of the GEMV kernels: the single-GPU instantiation carries none of this code.
+template <bool PEER>
 __device__ __forceinline__ void store_out(float *Y, const OutArgs &oa, int OUT, int m, int r, float v) {
-    if (!oa.peers) { Y[(size_t)m * OUT + r] = v; return; }
+    if (!PEER) { Y[(size_t)m * OUT + r] = v; return; }
     const PeerDesc *p = oa.peers;
     const int world = p->world;
     for (int k = 0; k < world; k++)
@@ -44,8 +46,9 @@ __device__ __forceinline__ void store_out(float *Y, const OutArgs &oa, int OUT, 
 
 // Called by every thread of every CTA after its last store; `stored` = this thread wrote outputs (only those
 // threads pay for the system-scope fence).
+template <bool PEER>
 __device__ __forceinline__ void publish_out(const OutArgs &oa, bool stored = true) {
-    if (!oa.peers || !oa.publish) return;
+    if (!PEER || !oa.publish) return;
     if (stored) __threadfence_system();            // this thread's peer stores are visible system-wide
     __syncthreads();
     if (threadIdx.x == 0) {

@@ -125,7 +125,7 @@ W4A8_API int w4a8_quantize_x_q8(const float *X, int8_t *xq, float *xs, int32_t *
     return launch_quantize_x(X, xq, xs, xsum, IN, S, (cudaStream_t)stream);
 }
 
-// GEMV kernel policy: 0 auto (one activation row -> dp4a kernel, more -> tensor-path kernel), 1 always dp4a,
+// GEMV kernel policy: 0 auto (one activation row with fp32 scales -> dp4a kernel, else tensor-path kernel), 1 always dp4a,
 // 2 tensor path for every S it supports.  Initialised from the environment (W4A8_GEMV = dp4a | mma), changed at
 // run time with w4a8_config("gemv_kernel", v).
 static int g_gemv_policy = -1;
@@ -136,16 +136,18 @@ static int gemv_policy() {
     }
     return g_gemv_policy;
 }
-static bool gemv_use_mma(int S) {
+static bool gemv_use_mma(int S, int scale_dtype) {
     const int p = gemv_policy();
-    return p == 2 || (p == 0 && S >= 2);
+    // auto: the dp4a streaming kernel only for a single row with fp32 scales, where it is the fastest; its two-byte
+    // scale loads make it slower than the tensor-path kernel with fp16 scales
+    return p == 2 || (p == 0 && (S >= 2 || scale_dtype == 1));
 }
 
 // The one place that decides which GEMV kernel runs and in how many launches.  count_only != nullptr: nothing is
 // launched, *count_only receives the number of kernel launches the call would make.
 static int gemv_dispatch(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int IN, int OUT, int S,
                          int scale_dtype, cudaStream_t st, int *count_only) {
-    if (gemv_use_mma(S)) {
+    if (gemv_use_mma(S, scale_dtype)) {
         // rows go in passes of up to 16 (8 when 16 rows of activations do not fit in shared memory next to the ring)
         gemv_mma::Plan plan;
         int per = S < 16 ? S : 16;
@@ -347,6 +349,21 @@ W4A8_API int w4a8_linear(const float *X, int8_t *xq, float *xs, int32_t *xsum, c
     }
     if (S <= 16 || !aligned(xq, 16) || !aligned(Wq, 16)) return w4a8_gemv(xq, xs, Wq, sw, Y, K, N, S, scale_dtype, stream);
     return w4a8_gemm(xq, xs, Wq, sw, Y, S, N, K, scale_dtype, stream);
+}
+
+W4A8_API int w4a8_linear_host(const float *X_host, float *Y_host, float *X_dev, int8_t *xq, float *xs, int32_t *xsum, float *Y_dev,
+                              const uint8_t *Wq, const void *sw, int S, int N, int K, int scale_dtype, void *stream) {
+    if (S < 0 || N < 0 || K < 0) return fail(W4A8_ERR_ARG, "linear_host: negative size");
+    if (S == 0 || N == 0) return W4A8_OK;
+    if (!X_host || !Y_host || !X_dev || !Y_dev) return fail(W4A8_ERR_ARG, "linear_host: null buffer");
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemcpyAsync(X_dev, X_host, (size_t)S * K * sizeof(float), cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return cuda_fail(e, "linear_host: H2D");
+    int rc = w4a8_linear(X_dev, xq, xs, xsum, Wq, sw, Y_dev, S, N, K, scale_dtype, 0, stream);
+    if (rc != W4A8_OK) return rc;
+    e = cudaMemcpyAsync(Y_host, Y_dev, (size_t)S * N * sizeof(float), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    return e == cudaSuccess ? W4A8_OK : cuda_fail(e, "linear_host: D2H");
 }
 
 W4A8_API int w4a8_moe_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, const int32_t *idx, float *Y,

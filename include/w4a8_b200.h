@@ -57,8 +57,8 @@ int w4a8_device_status(uint32_t *detail);
 
 /* Run-time policy switches (the reference keeps such switches in runtime/knobs.h, read from the environment;
  * the same names are read here once: W4A8_GEMV = dp4a | mma, W4A8_PDL = 0 | 1).
- *   "gemv_kernel": 0 = auto (default): one activation row uses the dp4a streaming kernel, 2..16 rows the
- *                  tensor-path kernel; 1 = dp4a kernel for every S; 2 = tensor-path kernel for every S it
+ *   "gemv_kernel": 0 = auto (default): one activation row with fp32 scales uses the dp4a streaming kernel,
+ *                  2..16 rows (and one row with fp16 scales) the tensor-path kernel; 1 = dp4a kernel for every S; 2 = tensor-path kernel for every S it
  *                  supports (K % 256 == 0, 16-byte aligned Wq and sw).  The tensor-path kernel evaluates fp32 in
  *                  the MMQ order (bit-identical to w4a8_gemm and to the reference's MMQ kernels); the dp4a kernel
  *                  in its own fixed order (within 1e-5).  Policy 2 therefore makes a row's bits independent of S
@@ -143,6 +143,14 @@ int w4a8_group_dots(const int8_t *xq, const uint8_t *Wq, int32_t *D, int M, int 
  * models/gemma4_decode.cu:115), then S <= 16 -> w4a8_gemv, else -> w4a8_gemm. */
 int w4a8_linear(const float *X, int8_t *xq, float *xs, int32_t *xsum, const uint8_t *Wq, const void *sw,
                 float *Y, int S, int N, int K, int scale_dtype, int skip_quantize, void *stream);
+
+/* mm() for a caller whose activations and results live in HOST memory (the daemon side of the reference's pipe
+ * protocol, runtime/serving_online.h): copies X_host[S,K] to X_dev, runs w4a8_linear into Y_dev, copies Y_dev[S,N]
+ * to Y_host and synchronises the stream, so Y_host is complete on return.  All device buffers are the caller's
+ * (same scratch as w4a8_linear plus X_dev and Y_dev); pinned host memory makes the copies asynchronous. */
+int w4a8_linear_host(const float *X_host, float *Y_host, float *X_dev, int8_t *xq, float *xs, int32_t *xsum,
+                     float *Y_dev, const uint8_t *Wq, const void *sw, int S, int N, int K, int scale_dtype,
+                     void *stream);
 
 /* ---- grouped experts (W4A8 semantics per expert) ----------------------------------------------------
  * The reference's expert kernels take fp32 activations (kernels/moe_fused.cuh:14-33); this keeps their

@@ -87,9 +87,9 @@ GEMV_SHAPES = [(1024, 256, 1), (1024, 2048, 1), (3584, 1024, 1), (1024, 4096, 5)
 
 def gemv_expected(oracle, xq, xs, Wq, sw, policy=0):
     """The documented fp32 order of w4a8_gemv: the tensor-path kernel (MMQ order) serves S >= 2 (every S under
-    policy 2) when K % 256 == 0, the dp4a kernel (its own chain order) everything else."""
+    policy 2; also S = 1 with fp16 scales) when K % 256 == 0, the dp4a kernel (its own chain order) everything else."""
     S, K = xq.shape
-    mma = K % 256 == 0 and (policy == 2 or (policy == 0 and S >= 2))
+    mma = K % 256 == 0 and (policy == 2 or (policy == 0 and (S >= 2 or sw.dtype == np.float16)))
     return oracle.gemm_mmq_w4a8(xq, xs, Wq, sw) if mma else oracle.gemv_b200_order(xq, xs, Wq, sw)
 
 
@@ -256,3 +256,83 @@ def test_linear_dispatch_and_loader(w4a8, oracle, cuda, tmp_path):
     with pytest.raises(w4a8.W4A8Error) as ei:
         w4a8.load_qmat_shard(str(q4), str(sc), N + 1, K, 0, 0, 1)      # file shorter than the shape: size mismatch
     assert ei.value.code == w4a8.ERR_IO
+
+
+def test_linear_host_entry(w4a8, oracle, cuda):
+    """mm() with host buffers: H2D, quantize + product, D2H, synchronous."""
+    S, N, K = 3, 200, 512
+    X = oracle.make_activations(S, K, seed=8)
+    Wq, sw = oracle.make_weights(N, K, seed=9)
+    Xh = torch.from_numpy(X).pin_memory()
+    Yh = torch.empty((S, N), dtype=torch.float32).pin_memory()
+    Xd = torch.empty((S, K), dtype=torch.float32, device=cuda)
+    xq = torch.empty((S, K), dtype=torch.int8, device=cuda)
+    xs = torch.empty((S, K // 32), dtype=torch.float32, device=cuda)
+    xsum = torch.empty((S, K // 32), dtype=torch.int32, device=cuda)
+    Yd = torch.empty((S, N), dtype=torch.float32, device=cuda)
+    w4a8.linear_host(Xh, Yh, Xd, xq, xs, xsum, Yd, to_dev(Wq, cuda), to_dev(sw, cuda), S, N, K)
+    xq_o, xs_o, _ = oracle.quantize_x_q8(X)
+    assert np.array_equal(Yh.numpy().view(np.uint32), gemv_expected(oracle, xq_o, xs_o, Wq, sw).view(np.uint32))
+
+
+# ---- BASELINE.json configs at their full shapes -----------------------------------------------------------------
+@pytest.mark.parametrize("K,N", [(3840, 4096), (3840, 3840), (3840, 15360), (15360, 3840)])
+def test_config3_gemma_layer_shapes_m8(w4a8, oracle, cuda, K, N):
+    xq, xs, Wq, sw = make_case(oracle, 8, N, K, seed=K + N)
+    Y = torch.empty((8, N), dtype=torch.float32, device=cuda)
+    w4a8.launch_gemv_w4a8_sb(to_dev(xq, cuda), to_dev(xs, cuda), to_dev(Wq, cuda), to_dev(sw, cuda), Y, K, N, 8)
+    torch.cuda.synchronize()
+    assert np.array_equal(Y.cpu().numpy().view(np.uint32), gemv_expected(oracle, xq, xs, Wq, sw).view(np.uint32))
+
+
+@pytest.mark.parametrize("M", [1, 16])
+def test_config2_decode_sweep_full_shape(w4a8, oracle, cuda, M):
+    K, N = 5120, 17408
+    xq, xs, Wq, sw = make_case(oracle, M, N, K, seed=20260002 + M)
+    Y = torch.empty((M, N), dtype=torch.float32, device=cuda)
+    w4a8.launch_gemv_w4a8_sb(to_dev(xq, cuda), to_dev(xs, cuda), to_dev(Wq, cuda), to_dev(sw, cuda), Y, K, N, M)
+    torch.cuda.synchronize()
+    y = Y.cpu().numpy()
+    assert np.array_equal(y.view(np.uint32), gemv_expected(oracle, xq, xs, Wq, sw).view(np.uint32))
+    assert rel_err(y, oracle.w4a8_f64(xq, xs, Wq, sw)) < REL_TOL
+
+
+def test_config4_prefill_gemm_full_shape_sampled_rows(w4a8, oracle, cuda):
+    """M=2048, K=5120, N=17408 with 1 % outliers x20, quantize_x on the device.  The oracle cannot do the whole product
+    in seconds, so: xq/xs/xsum of all rows exact; a sample of output rows bit-exact (rows are independent of M in the
+    reference, tools/probe_mmq_rowdep.cu, so a row equals the M=1 product of that row); a second run bitwise equal."""
+    M, K, N = 2048, 5120, 17408
+    X = oracle.make_activations(M, K, seed=20260004, outliers=True)
+    Wq, sw = oracle.make_weights(N, K, seed=20260005)
+    xq_o, xs_o, xsum_o = oracle.quantize_x_q8(X)
+    xq, xs, xsum = quantize_dev(w4a8, to_dev(X, cuda))
+    torch.cuda.synchronize()
+    assert np.array_equal(xq.cpu().numpy(), xq_o) and np.array_equal(xs.cpu().numpy(), xs_o) and np.array_equal(xsum.cpu().numpy(), xsum_o)
+    Wq_d, sw_d = to_dev(Wq, cuda), to_dev(sw, cuda)
+    Y = torch.empty((M, N), dtype=torch.float32, device=cuda)
+    w4a8.launch_gemm_mmq_w4a8(xq, xs, Wq_d, sw_d, Y, M, N, K)
+    w4a8.device_status()
+    rows = np.array([0, 1, 127, 128, 777, 1023, 1024, 2046, 2047])
+    ref = oracle.gemm_mmq_w4a8(xq_o[rows], xs_o[rows], Wq, sw)
+    assert np.array_equal(Y[torch.from_numpy(rows).to(cuda)].cpu().numpy().view(np.uint32), ref.view(np.uint32))
+    Y2 = torch.empty((M, N), dtype=torch.float32, device=cuda)
+    w4a8.launch_gemm_mmq_w4a8(xq, xs, Wq_d, sw_d, Y2, M, N, K)
+    w4a8.device_status()
+    assert torch.equal(Y, Y2)
+
+
+def test_config5_moe_shapes(w4a8, oracle, cuda):
+    """128 experts, top-8, gate/up K=2048 -> N=768 and down K=768 -> N=2048, 32 tokens (256 slots)."""
+    E, topk, tokens = 128, 8, 32
+    rng = np.random.default_rng(5)
+    idx = np.stack([rng.permutation(E)[:topk] for _ in range(tokens)]).astype(np.int32).reshape(-1)
+    for (K, N, per_slot) in [(2048, 768, 0), (768, 2048, 1)]:
+        rows = tokens * topk if per_slot else tokens
+        X = oracle.make_activations(rows, K, seed=K)
+        Wq, sw = oracle.make_weights(E * N, K, seed=N)
+        xq, xs, _ = oracle.quantize_x_q8(X)
+        Y = torch.empty((tokens * topk, N), dtype=torch.float32, device=cuda)
+        w4a8.moe_gemv(to_dev(xq, cuda), to_dev(xs, cuda), to_dev(Wq, cuda), to_dev(sw, cuda), to_dev(idx, cuda), Y,
+                      tokens * topk, topk, per_slot, N, K, E)
+        torch.cuda.synchronize()
+        assert rel_err(Y.cpu().numpy(), oracle.moe_w4a8(xq, xs, Wq, sw, idx, topk, per_slot, N, K)) < REL_TOL
