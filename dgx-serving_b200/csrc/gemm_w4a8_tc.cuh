@@ -37,8 +37,15 @@ constexpr int TB = 4;           // TMEM accumulator buffers (TB * BN = 512 colum
 constexpr int A_STAGE = BM * KT;       // 16 KB
 constexpr int BP_STAGE = BN * KT / 2;  // 8 KB
 constexpr int B8_STAGE = BN * KT;      // 16 KB
-constexpr int SW_STAGE = GPK * BN * 4; // 2 KB
-constexpr int DEQ_WARPS = 2, EPI_WARPS = 8;
+constexpr int SW_STAGE = GPK * (BN + BM) * 4; // 4 KB: weight scales [group][n], then activation scales [group][m]
+#ifndef W4A8_DEQ_WARPS
+#define W4A8_DEQ_WARPS 2
+#endif
+#ifndef W4A8_EPI_UNROLL
+#define W4A8_EPI_UNROLL 4
+#endif
+constexpr int DEQ_WARPS = W4A8_DEQ_WARPS, EPI_WARPS = 8;
+constexpr int EPI_UNROLL = W4A8_EPI_UNROLL;
 constexpr int EPI_COLS = BN / (EPI_WARPS / 4);  // accumulator columns per epilogue warp (64)
 constexpr int EPI_CH = EPI_COLS / 2;           // columns per tcgen05.ld chunk (32)
 constexpr int THREADS = (2 + DEQ_WARPS + EPI_WARPS) * 32;  // 384: up to 168 registers per thread
@@ -119,6 +126,18 @@ __device__ __forceinline__ void epi_chunk(const uint32_t (&d)[NC], float x, cons
         }
     }
 }
+// Four consecutive scales of one row (one K-tile's worth) with one load; the address must be aligned to the
+// size of the load.
+__device__ __forceinline__ void load_scales4(const float *p, float (&v)[4]) {
+    const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load_scales4(const __half *p, float (&v)[4]) {
+    const uint2 t = __ldg(reinterpret_cast<const uint2 *>(p));
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&t.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&t.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
 // Debug path: the exact group dots of one chunk to Dout[m][n][b] (undoing the factor 16).
 template <int NC>
 __device__ __forceinline__ void epi_dump(const uint32_t (&d)[NC], int32_t *__restrict__ Dout, int m, int M, int ncol0, int N,
@@ -169,6 +188,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nb = K / QBLK;
+    const bool scales_aligned = ((reinterpret_cast<uintptr_t>(xs) & 15) == 0) && ((reinterpret_cast<uintptr_t>(sw) & (4 * sizeof(ST) - 1)) == 0);
     const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
     const int num_tiles = m_tiles * n_tiles;
     const int num_work = num_tiles * nsplit;
@@ -256,18 +276,64 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
             const Work wk = decode_work(wi, m_tiles, num_tiles, nb, gsplit);
             const int n0 = wk.n0;
             for (int kt = 0; kt < wk.nkt && ok; kt++) {
+                // ---- this K-tile's scales: issue the loads first, they complete behind the expansion below.
+                // A row's GPK scales are contiguous in memory: one 16-byte (fp32) or 8-byte (fp16) load per row
+                // when the K-tile is complete and the addresses line up, else element by element.
+                constexpr int RW = BN / (DEQ_WARPS * 32), RX = BM / (DEQ_WARPS * 32);
+                const int b0 = wk.g0 + kt * GPK;   // first group of this K-tile
+                const bool vec = !DUMP && (b0 + GPK <= wk.g1) && (nb % GPK == 0) && (b0 % GPK == 0) && scales_aligned;
+                float vw[RW][GPK], vx[RX][GPK];
+#pragma unroll
+                for (int r = 0; r < RW; r++) {
+                    const int n = n0 + dt + r * DEQ_WARPS * 32;
+#pragma unroll
+                    for (int g = 0; g < GPK; g++) vw[r][g] = 0.f;
+                    if (!DUMP && n < N) {
+                        if (vec) load_scales4(sw + (size_t)n * nb + b0, vw[r]);
+                        else {
+#pragma unroll
+                            for (int g = 0; g < GPK; g++)
+                                if (b0 + g < wk.g1) vw[r][g] = sval(sw[(size_t)n * nb + b0 + g]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < RX; r++) {
+                    const int m = wk.m0 + dt + r * DEQ_WARPS * 32;
+#pragma unroll
+                    for (int g = 0; g < GPK; g++) vx[r][g] = 0.f;
+                    if (!DUMP && m < M) {
+                        if (vec) load_scales4(xs + (size_t)m * nb + b0, vx[r]);
+                        else {
+#pragma unroll
+                            for (int g = 0; g < GPK; g++)
+                                if (b0 + g < wk.g1) vx[r][g] = xs[(size_t)m * nb + b0 + g];
+                        }
+                    }
+                }
+
+                // ---- expansion of the packed stage into the operand stage
                 bool w = ptx::mbar_wait_warp(BAR(BP_FULL + rb.stage), rb.phase) && ptx::mbar_wait_warp(BAR(B8_EMPTY + r8.stage), r8.phase ^ 1u);
                 if (!w) { dev_set_error(ERR_DEQUANT | 1); ok = false; break; }
                 const unsigned char *src = base_ptr + OFF_BP + rb.stage * BP_STAGE;
                 unsigned char *dst = base_ptr + OFF_B8 + r8.stage * B8_STAGE;
+                // All loads first, then expansion and stores: the compiler cannot tell that the two stages do not
+                // overlap, so in one loop every load would wait for the previous store.
+                constexpr int NT = (BN * 8) / (DEQ_WARPS * 32);
+                uint2 pk[NT];
 #pragma unroll
-                for (int i = 0; i < (BN * 8) / (DEQ_WARPS * 32); i++) {
+                for (int i = 0; i < NT; i++) {
                     const int j = dt + i * DEQ_WARPS * 32;
                     const int n = j >> 3, c = j & 7;  // row n, 8 packed bytes = 16 weights = one 16-byte chunk
-                    const uint2 p = *reinterpret_cast<const uint2 *>(src + n * (KT / 2) + c * 8);
+                    pk[i] = *reinterpret_cast<const uint2 *>(src + n * (KT / 2) + c * 8);
+                }
+#pragma unroll
+                for (int i = 0; i < NT; i++) {
+                    const int j = dt + i * DEQ_WARPS * 32;
+                    const int n = j >> 3, c = j & 7;
                     uint4 o;
-                    unpack8_x16_seq(p.x, o.x, o.y);
-                    unpack8_x16_seq(p.y, o.z, o.w);
+                    unpack8_x16_seq(pk[i].x, o.x, o.y);
+                    unpack8_x16_seq(pk[i].y, o.z, o.w);
                     *reinterpret_cast<uint4 *>(dst + n * KT + ((c ^ (n & 7)) << 4)) = o;
                 }
                 ptx::fence_proxy_async_smem();
@@ -276,20 +342,20 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
                 rb.advance();
                 r8.advance();
 
+                // ---- store the scales: weight scales transposed to [group][n] and pre-multiplied by the exact
+                // 1/16 that undoes the 16x of the expansion, activation scales transposed to [group][m]
                 w = ptx::mbar_wait_warp(BAR(SW_EMPTY + rs.stage), rs.phase ^ 1u);
                 if (!w) { dev_set_error(ERR_DEQUANT | 2); ok = false; break; }
                 float *ssw = reinterpret_cast<float *>(base_ptr + OFF_SW + rs.stage * SW_STAGE);
+                float *ssx = ssw + GPK * BN;
 #pragma unroll
-                for (int r = 0; r < BN / (DEQ_WARPS * 32); r++) {
-                    const int nl = dt + r * DEQ_WARPS * 32, n = n0 + nl;
+                for (int r = 0; r < RW; r++)
 #pragma unroll
-                    for (int g = 0; g < GPK; g++) {
-                        const int b = wk.g0 + kt * GPK + g;
-                        float v = 0.f;
-                        if (!DUMP && n < N && b < wk.g1) v = sval(sw[(size_t)n * nb + b]) * 0.0625f;  // exact: undoes the 16x of the expansion
-                        ssw[g * BN + nl] = v;
-                    }
-                }
+                    for (int g = 0; g < GPK; g++) ssw[g * BN + dt + r * DEQ_WARPS * 32] = vw[r][g] * 0.0625f;
+#pragma unroll
+                for (int r = 0; r < RX; r++)
+#pragma unroll
+                    for (int g = 0; g < GPK; g++) ssx[g * BM + dt + r * DEQ_WARPS * 32] = vx[r][g];
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(BAR(SW_FULL + rs.stage));
                 rs.advance();
@@ -308,68 +374,66 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
             const int m = m0 + quad * 32 + lane;
             // a warp whose 32 rows all lie beyond M only keeps the barriers moving
             const bool rows_live = (m0 + quad * 32) < M;
-            const float *xsrow = xs + (size_t)(m < M ? m : 0) * nb;
             float acc[EPI_COLS];
 #pragma unroll
             for (int j = 0; j < EPI_COLS; j++) acc[j] = 0.f;
-            float xnext[GPK];
-#pragma unroll
-            for (int g = 0; g < GPK; g++) xnext[g] = (!DUMP && m < M && wk.g0 + g < wk.g1) ? xsrow[wk.g0 + g] : 0.f;
-            for (int kt = 0; kt < wk.nkt && ok; kt++) {
-                float xcur[GPK];
-#pragma unroll
-                for (int g = 0; g < GPK; g++) {
-                    xcur[g] = xnext[g];
-                    const int b = wk.g0 + (kt + 1) * GPK + g;
-                    xnext[g] = (!DUMP && m < M && b < wk.g1) ? xsrow[b] : 0.f;
-                }
-                const int ng = min(GPK, wk.g1 - (wk.g0 + kt * GPK));
-                const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16) + col0;
-                // The 2*ng chunks (EPI_CH columns each) of this K-tile are software-pipelined: the tcgen05.ld of
-                // chunk i+1 is in flight while chunk i is converted and accumulated.  d0 holds the first half of
-                // this warp's columns of a group, d1 the second.
-                uint32_t d0[EPI_CH], d1[EPI_CH];
-                bool w = ptx::mbar_wait_warp(BAR(TM_FULL + rt.stage), rt.phase);
+            const int ngroups = wk.g1 - wk.g0;
+            const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16) + col0;
+            // One flat loop over the groups of this unit of work.  The 2 chunks (EPI_CH columns each) of a group
+            // are software-pipelined with the next group's: the tcgen05.ld of the next chunk is in flight while
+            // the current one is converted and accumulated.  d0 holds the first half of this warp's columns of
+            // a group, d1 the second.  Both scales come from the staged K-tile slice in shared memory, so the
+            // loop issues no global loads.
+            uint32_t d0[EPI_CH], d1[EPI_CH];
+            const float *ssw = nullptr, *ssx = nullptr;
+            bool w = true;
+            if (ngroups > 0) {   // a split beyond the last group has no work: its partial sums are zeros
+                w = ptx::mbar_wait_warp(BAR(TM_FULL + rt.stage), rt.phase);
                 if (!w) { dev_set_error(ERR_EPILOGUE | 2); ok = false; break; }
                 ptx::tc_fence_after_sync();
                 if (rows_live) ptx::tmem_ld(tlane + rt.stage * BN, d0);
-                w = ptx::mbar_wait_warp(BAR(SW_FULL + rs.stage), rs.phase);
-                if (!w) { dev_set_error(ERR_EPILOGUE | 1); ok = false; break; }
-                const float *ssw = reinterpret_cast<const float *>(base_ptr + OFF_SW + rs.stage * SW_STAGE) + col0;
-#pragma unroll
-                for (int g = 0; g < GPK; g++) {
-                    if (g < ng) {
-                        const int b = wk.g0 + kt * GPK + g;
-                        const uint32_t tcur = tlane + rt.stage * BN;
-                        // ---- first half: wait for it, start the second half's load, then compute
-                        ptx::tmem_ld_wait();
-                        if (rows_live) ptx::tmem_ld(tcur + EPI_CH, d1);
-                        if (rows_live) {
-                            if (DUMP) epi_dump<EPI_CH>(d0, Dout, m, M, n0 + col0, N, nb, b);
-                            else epi_chunk<EPI, EPI_CH>(d0, xcur[g], ssw + g * BN, acc);
-                        }
-                        // ---- second half: wait, release the accumulator buffer, start the next group's load
-                        ptx::tmem_ld_wait();
-                        ptx::tc_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(BAR(TM_EMPTY + rt.stage));
-                        rt.advance();
-                        if (g + 1 < ng) {
-                            w = ptx::mbar_wait_warp(BAR(TM_FULL + rt.stage), rt.phase);
-                            if (!w) { dev_set_error(ERR_EPILOGUE | 3); ok = false; break; }
-                            ptx::tc_fence_after_sync();
-                            if (rows_live) ptx::tmem_ld(tlane + rt.stage * BN, d0);
-                        }
-                        if (rows_live) {
-                            if (DUMP) epi_dump<EPI_CH>(d1, Dout, m, M, n0 + col0 + EPI_CH, N, nb, b);
-                            else epi_chunk<EPI, EPI_CH>(d1, xcur[g], ssw + g * BN + EPI_CH, acc + EPI_CH);
-                        }
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(BAR(SW_EMPTY + rs.stage));
-                rs.advance();
             }
+#pragma unroll EPI_UNROLL
+            for (int gi = 0; gi < ngroups; gi++) {
+                const int g = gi & (GPK - 1);
+                if (g == 0) {
+                    w = ptx::mbar_wait_warp(BAR(SW_FULL + rs.stage), rs.phase);
+                    if (!w) { dev_set_error(ERR_EPILOGUE | 1); ok = false; break; }
+                    ssw = reinterpret_cast<const float *>(base_ptr + OFF_SW + rs.stage * SW_STAGE) + col0;
+                    ssx = reinterpret_cast<const float *>(base_ptr + OFF_SW + rs.stage * SW_STAGE) + GPK * BN + quad * 32 + lane;
+                }
+                const float x = ssx[g * BM];
+                const uint32_t tcur = tlane + rt.stage * BN;
+                // ---- first half: wait for it, start the second half's load, then compute
+                ptx::tmem_ld_wait();
+                if (rows_live) ptx::tmem_ld(tcur + EPI_CH, d1);
+                if (rows_live) {
+                    if (DUMP) epi_dump<EPI_CH>(d0, Dout, m, M, n0 + col0, N, nb, wk.g0 + gi);
+                    else epi_chunk<EPI, EPI_CH>(d0, x, ssw + g * BN, acc);
+                }
+                // ---- second half: wait, release the accumulator buffer, start the next group's load
+                ptx::tmem_ld_wait();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(BAR(TM_EMPTY + rt.stage));
+                rt.advance();
+                if (gi + 1 < ngroups) {
+                    w = ptx::mbar_wait_warp(BAR(TM_FULL + rt.stage), rt.phase);
+                    if (!w) { dev_set_error(ERR_EPILOGUE | 3); ok = false; break; }
+                    ptx::tc_fence_after_sync();
+                    if (rows_live) ptx::tmem_ld(tlane + rt.stage * BN, d0);
+                }
+                if (rows_live) {
+                    if (DUMP) epi_dump<EPI_CH>(d1, Dout, m, M, n0 + col0 + EPI_CH, N, nb, wk.g0 + gi);
+                    else epi_chunk<EPI, EPI_CH>(d1, x, ssw + g * BN + EPI_CH, acc + EPI_CH);
+                }
+                if (g == GPK - 1 || gi + 1 == ngroups) {   // done with this K-tile's scales
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(BAR(SW_EMPTY + rs.stage));
+                    rs.advance();
+                }
+            }
+            if (!ok) break;
             if (!DUMP && ok && m < M) {
                 float *yrow = Y + (size_t)wk.split * ((size_t)M * N) + (size_t)m * N + n0 + col0;
                 const int nleft = N - (n0 + col0);

@@ -23,6 +23,8 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One attempt; comes back after a short system-chosen time if the phase has not completed (about 34 cycles
+// when it has).
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -34,25 +36,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after `limit_cycles` SM clocks (default 2^28, about 0.15 s), far beyond any
-// legitimate pipeline wait (microseconds).  Returns false on timeout.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long long limit_cycles = (1ll << 28)) {
-    if (mbar_try_wait(bar, parity)) return true;
+// Polling loop behind the first attempt.  Kept out of line on purpose: inlined, the 64-bit clock read that
+// bounds the loop was scheduled ahead of the first attempt and a wait on a barrier that had ALREADY completed
+// cost about 180 cycles instead of 34, on every hand-off of the pipeline.  The clock is read once per 64
+// attempts so that it does not delay the wake-up either.  Gives up after `limit_cycles` SM clocks.
+__device__ __noinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, long long limit_cycles) {
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait(bar, parity)) return true;
         if (clock64() - t0 > limit_cycles) return false;
     }
-    return true;
+}
+// Bounded wait of one thread: the default limit of 2^28 cycles (about 0.15 s) is far beyond any legitimate
+// pipeline wait (microseconds).  Returns false on timeout.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long long limit_cycles = (1ll << 28)) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_poll(bar, parity, limit_cycles);
 }
 
-// Warp-wide bounded wait: ONE lane polls the barrier and the outcome is broadcast (the shuffle also
-// re-converges and orders the warp).  An mbarrier operation issued by 32 lanes is carried out lane by
-// lane, so letting every lane poll costs tens of cycles per wait; with one wait per 32-wide K group that
-// serialisation, not the arithmetic, would set the pace of the whole pipeline.
+// Warp-wide bounded wait: every lane makes the attempt (uniform control flow, about 47 cycles with the vote
+// when the phase has completed; letting one lane wait and broadcasting the outcome by shuffle cost more) and
+// the warp leaves together with one agreed result.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, long long limit_cycles = (1ll << 28)) {
-    int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, limit_cycles) ? 1 : 0;
-    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+    bool ok = mbar_try_wait(bar, parity);
+    if (__all_sync(0xffffffffu, ok)) return true;
+    if (!ok) ok = mbar_wait_poll(bar, parity, limit_cycles);
+    return __all_sync(0xffffffffu, ok);
 }
 
 // ---- proxies / fences -------------------------------------------------------------------------

@@ -13,6 +13,7 @@
 #include "gemv_w4a8.cuh"
 #include "gemv_w4a8_mma.cuh"
 #include "gemm_w4a8_tc.cuh"
+#include "gemm_w4a8_tcf.cuh"
 
 namespace w4a8 {
 
@@ -98,6 +99,10 @@ static int check_common(const void *a, const void *b, const void *c, const void 
 
 using namespace w4a8;
 
+#ifndef W4A8_GEMM_DEFAULT
+#define W4A8_GEMM_DEFAULT 1
+#endif
+
 W4A8_API int w4a8_version(void) { return 100; }
 W4A8_API const char *w4a8_last_error(void) { return err_buf(); }
 
@@ -174,8 +179,29 @@ static int gemv_dispatch(const int8_t *xq, const float *xs, const uint8_t *Wq, c
     return launch_gemv(xq, xs, Wq, sw, Y, IN, OUT, S, scale_dtype, st);
 }
 
+// GEMM kernel policy: 0 = fp16-operand tensor-core kernel (kind::f16, exact float group dots), 1 = int8-operand kernel
+// (kind::i8, int32 group dots).  Same results bit for bit.  Environment W4A8_GEMM = f16 | i8.
+static int g_gemm_policy = -1;
+static int gemm_policy() {
+    if (g_gemm_policy < 0) {
+        const char *e = getenv("W4A8_GEMM");
+        g_gemm_policy = !e ? W4A8_GEMM_DEFAULT : (e[0] == 'i' ? 1 : 0);
+    }
+    return g_gemm_policy;
+}
+static int gemm_launch(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int M, int N, int K,
+                       int scale_dtype, int nsplit, int gsplit, cudaStream_t st) {
+    if (gemm_policy() == 1) return gemm::launch_tc(X, xs, Wq, sw, Y, M, N, K, scale_dtype, nsplit, gsplit, st);
+    return gemmf::launch(X, xs, Wq, sw, Y, M, N, K, scale_dtype, nsplit, gsplit, st);
+}
+
 W4A8_API int w4a8_config(const char *key, int value) {
     if (!key) return fail(W4A8_ERR_ARG, "config: null key");
+    if (!strcmp(key, "gemm_kernel")) {
+        if (value < 0 || value > 1) return fail(W4A8_ERR_ARG, "config: gemm_kernel = 0 (fp16 operands), 1 (int8 operands); got %d", value);
+        g_gemm_policy = value;
+        return W4A8_OK;
+    }
     if (!strcmp(key, "gemv_kernel")) {
         if (value < 0 || value > 2) return fail(W4A8_ERR_ARG, "config: gemv_kernel = 0 (auto), 1 (dp4a), 2 (tensor path); got %d", value);
         g_gemv_policy = value;
@@ -214,7 +240,7 @@ W4A8_API int w4a8_gemm(const int8_t *X, const float *xs, const uint8_t *Wq, cons
         cudaError_t e = cudaMemsetAsync(Y, 0, (size_t)M * N * sizeof(float), (cudaStream_t)stream);
         return e == cudaSuccess ? W4A8_OK : cuda_fail(e, "gemm: memset");
     }
-    return gemm::launch_tc(X, xs, Wq, sw, Y, M, N, K, scale_dtype, 1, K / QBLK, (cudaStream_t)stream);
+    return gemm_launch(X, xs, Wq, sw, Y, M, N, K, scale_dtype, 1, K / QBLK, (cudaStream_t)stream);
 }
 
 // Split count and groups per split.  Boundaries follow the reference: K-tiles of 64 (2 groups), ranges of
@@ -253,12 +279,12 @@ W4A8_API int w4a8_gemm_splitk(const int8_t *X, const float *xs, const uint8_t *W
     int ns, gs;
     splitk_plan(N, K, splitk, &ns, &gs);
     cudaStream_t st = (cudaStream_t)stream;
-    if (ns == 1) return gemm::launch_tc(X, xs, Wq, sw, Y, M, N, K, scale_dtype, 1, K / QBLK, st);
+    if (ns == 1) return gemm_launch(X, xs, Wq, sw, Y, M, N, K, scale_dtype, 1, K / QBLK, st);
     const size_t need = (size_t)ns * M * N * sizeof(float);
     if (!workspace || workspace_bytes < need)
         return fail(W4A8_ERR_WORKSPACE, "gemm_splitk: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
     if (!aligned(workspace, 16)) return fail(W4A8_ERR_ALIGN, "gemm_splitk: workspace must be 16-byte aligned");
-    rc = gemm::launch_tc(X, xs, Wq, sw, (float *)workspace, M, N, K, scale_dtype, ns, gs, st);
+    rc = gemm_launch(X, xs, Wq, sw, (float *)workspace, M, N, K, scale_dtype, ns, gs, st);
     if (rc != W4A8_OK) return rc;
     const long MN = (long)M * N;
     long want = (MN + 255) / 256, cap = (long)sm_count() * 8;
@@ -308,13 +334,13 @@ W4A8_API int w4a8_gemm_splitk_static(const int8_t *X, const float *xs, const uin
     rc = require_sm100();
     if (rc != W4A8_OK) return rc;
     cudaStream_t st = (cudaStream_t)stream;
-    if (ns == 1) return gemm::launch_tc(X, xs, Wq, sw, Y, M, N, K, scale_dtype, 1, K / QBLK, st);
+    if (ns == 1) return gemm_launch(X, xs, Wq, sw, Y, M, N, K, scale_dtype, 1, K / QBLK, st);
     float *scratch = nullptr;
     rc = splitk_static_ptr(&scratch);
     if (rc != W4A8_OK) return rc;
     // kernel 1 writes every partial sum [split][m][n], m < M, n < N (an empty K range writes zeros), kernel 2 reads
     // exactly those: nothing left over from an earlier call is ever read, so nothing needs clearing.
-    rc = gemm::launch_tc(X, xs, Wq, sw, scratch, M, N, K, scale_dtype, ns, gs, st);
+    rc = gemm_launch(X, xs, Wq, sw, scratch, M, N, K, scale_dtype, ns, gs, st);
     if (rc != W4A8_OK) return rc;
     const long MN = (long)M * N;
     long want = (MN + 255) / 256, cap = (long)sm_count() * 8;
@@ -333,7 +359,11 @@ W4A8_API int w4a8_group_dots(const int8_t *xq, const uint8_t *Wq, int32_t *D, in
         if (!aligned(xq, 16) || !aligned(Wq, 16)) return fail(W4A8_ERR_ALIGN, "group_dots: tensor-core path needs 16-byte aligned operands");
         return gemm::launch_tc_dump(xq, Wq, D, M, N, K, st);
     }
-    if (path != 0) return fail(W4A8_ERR_ARG, "group_dots: path=%d (0 dp4a, 1 tcgen05)", path);
+    if (path == 2) {
+        if (!aligned(xq, 16) || !aligned(Wq, 16)) return fail(W4A8_ERR_ALIGN, "group_dots: tensor-core path needs 16-byte aligned operands");
+        return gemmf::launch_dump(xq, Wq, D, M, N, K, st);
+    }
+    if (path != 0) return fail(W4A8_ERR_ARG, "group_dots: path=%d (0 dp4a, 1 tcgen05 int8, 2 tcgen05 fp16)", path);
     if (!aligned(xq, 4) || !aligned(Wq, 4)) return fail(W4A8_ERR_ALIGN, "group_dots: operands must be 4-byte aligned");
     const long total = (long)M * N * (K / QBLK);
     long want = (total + 255) / 256, cap = (long)sm_count() * 8;

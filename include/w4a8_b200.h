@@ -62,7 +62,13 @@ int w4a8_device_status(uint32_t *detail);
  *                  supports (K % 256 == 0, 16-byte aligned Wq and sw).  The tensor-path kernel evaluates fp32 in
  *                  the MMQ order (bit-identical to w4a8_gemm and to the reference's MMQ kernels); the dp4a kernel
  *                  in its own fixed order (within 1e-5).  Policy 2 therefore makes a row's bits independent of S
- *                  for all S >= 1 (the reference's batch == single invariant), policy 0 for all S >= 2. */
+ *                  for all S >= 1 (the reference's batch == single invariant), policy 0 for all S >= 2.
+ *   "gemm_kernel": which tensor-core kernel w4a8_gemm / w4a8_gemm_splitk / w4a8_linear use (environment:
+ *                  W4A8_GEMM = i8 | f16).  1 = int8 operands, tcgen05.mma kind::i8, int32 group dots converted in
+ *                  the epilogue (default, the faster one); 0 = operands converted to fp16 on the way into shared
+ *                  memory (every int4 and int8 value is exact in fp16), tcgen05.mma kind::f16 with fp32
+ *                  accumulation of one 32-element group, which is exact as well (|sum| <= 32*127*8 < 2^24).
+ *                  Both give the same bits. */
 int w4a8_config(const char *key, int value);
 
 /* ---- a1: activation quantization ------------------------------------------------------------------
@@ -130,8 +136,9 @@ int w4a8_gemm_splitk_static(const int8_t *X, const float *xs, const uint8_t *Wq,
 
 /* ---- exact integer group dots (debug / parity) ------------------------------------------------------
  * D[m,n,b] = sum_{k in b} xq[m,k]*(Wq[n,k]-8) as int32, D laid out [M][N][K/32].  `path` selects the
- * producer: 0 = the GEMV kernels' dp4a path, 1 = the GEMM kernel's tcgen05 path (accumulators read
- * back from tensor memory).  Checks the bit-exactness the fp32 entry points rest on
+ * producer: 0 = the GEMV kernels' dp4a path, 1 = the int8 GEMM kernel's tcgen05 kind::i8 path (accumulators
+ * read back from tensor memory), 2 = the fp16-operand GEMM kernel's kind::f16 path (fp32 accumulators, exact,
+ * converted back to int32).  Checks the bit-exactness the fp32 entry points rest on
  * (tests/test_mma_b0.cu:46-49). */
 int w4a8_group_dots(const int8_t *xq, const uint8_t *Wq, int32_t *D, int M, int N, int K, int path,
                     void *stream);

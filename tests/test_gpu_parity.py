@@ -69,7 +69,7 @@ def make_case(oracle, M, N, K, seed, scale_dtype=0, outliers=False):
     return xq, xs, Wq, sw
 
 
-@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("path", [0, 1, 2])
 @pytest.mark.parametrize("M,N,K", [(1, 64, 256), (16, 8, 256), (5, 200, 160), (130, 140, 96), (200, 300, 1024)])
 def test_group_dots_bit_exact(w4a8, oracle, cuda, path, M, N, K):
     xq, xs, Wq, sw = make_case(oracle, M, N, K, seed=300 + M + N)
@@ -163,6 +163,24 @@ def test_gemm_parity(w4a8, oracle, cuda, M, N, K, scale_dtype):
     assert rel_err(y, oracle.gemv_w4a8(xq, xs, Wq, sw)) < REL_TOL                                        # tests/test_gemm_mmq.cu:28
     terms = oracle.abs_terms(xq, xs, Wq, sw)                                                             # tests/gemma4_mmq/shape.cu:105-117
     assert np.max(np.abs(y - oracle.w4a8_f64(xq, xs, Wq, sw)) / np.maximum(terms, 1e-30)) < REL_TOL
+
+
+@pytest.mark.parametrize("scale_dtype", [0, 1])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 512), (200, 300, 256), (129, 140, 160), (17, 8, 32), (513, 1000, 2048), (1, 5, 96)])
+def test_gemm_fp16_operand_kernel_same_bits(w4a8, oracle, cuda, M, N, K, scale_dtype):
+    """config("gemm_kernel", 0) selects the fp16-operand tensor-core kernel: the same bits as the int8 one."""
+    xq, xs, Wq, sw = make_case(oracle, M, N, K, seed=1900 + M + N + K, scale_dtype=scale_dtype, outliers=True)
+    d = [to_dev(a, cuda) for a in (xq, xs, Wq, sw)]
+    want = oracle.gemm_mmq_w4a8(xq, xs, Wq, sw).view(np.uint32)
+    try:
+        for kernel in (0, 1):
+            w4a8.config("gemm_kernel", kernel)
+            Y = torch.full((M, N), float("nan"), dtype=torch.float32, device=cuda)
+            w4a8.launch_gemm_mmq_w4a8(d[0], d[1], d[2], d[3], Y, M, N, K, scale_dtype)
+            w4a8.device_status()
+            assert np.array_equal(Y.cpu().numpy().view(np.uint32), want), kernel
+    finally:
+        w4a8.config("gemm_kernel", 1)
 
 
 def test_gemm_deterministic_and_row_independent(w4a8, oracle, cuda):
