@@ -14,10 +14,14 @@
 //               accumulator buffers in tensor memory; tcgen05.commit signals operand release / result ready
 //   warps 2-3   expand int4 -> int8 (as 16*(w-8), see unpack8_x16) from the packed stage into the swizzled
 //               K-major operand stage the MMA reads (generic-proxy writes + fence.proxy.async), and stage
-//               the weight scales of the K-tile (pre-multiplied by the exact 1/16) transposed to [group][n]
-//   warps 4-11  epilogue: tcgen05.ld the int32 group dots (lane = row, 64 columns per warp, loaded as two
-//               32-column chunks so that one chunk's load is in flight while the other is processed), convert,
-//               scale and accumulate in registers; store the fp32 tile at the end of the K loop
+//               both scale slices of the K-tile in shared memory: weight scales transposed to [group][n] and
+//               pre-multiplied by the exact 1/16, activation scales transposed to [group][m]
+//   warps 4-19  epilogue: tcgen05.ld the int32 group dots (lane = row, 32 columns per warp, loaded as two
+//               16-column chunks so that one chunk's load is in flight while the other is processed), convert,
+//               scale and accumulate in registers; store the fp32 tile at the end of the K loop.  The loop
+//               touches no global memory.  Sixteen warps rather than eight because each warp's instruction
+//               stream is a chain of waits (tensor-memory load, barrier, conversion pipe): four epilogue
+//               warps per scheduler overlap them better than two (1253 -> 1214 us at M = 2048).
 // Ragged M, N and a last partial K-tile are handled by TMA zero fill plus guards on scales and stores.
 #pragma once
 #include <cuda.h>
@@ -44,11 +48,14 @@ constexpr int SW_STAGE = GPK * (BN + BM) * 4; // 4 KB: weight scales [group][n],
 #ifndef W4A8_EPI_UNROLL
 #define W4A8_EPI_UNROLL 4
 #endif
-constexpr int DEQ_WARPS = W4A8_DEQ_WARPS, EPI_WARPS = 8;
+#ifndef W4A8_EPI_WARPS
+#define W4A8_EPI_WARPS 16
+#endif
+constexpr int DEQ_WARPS = W4A8_DEQ_WARPS, EPI_WARPS = W4A8_EPI_WARPS;
 constexpr int EPI_UNROLL = W4A8_EPI_UNROLL;
-constexpr int EPI_COLS = BN / (EPI_WARPS / 4);  // accumulator columns per epilogue warp (64)
-constexpr int EPI_CH = EPI_COLS / 2;           // columns per tcgen05.ld chunk (32)
-constexpr int THREADS = (2 + DEQ_WARPS + EPI_WARPS) * 32;  // 384: up to 168 registers per thread
+constexpr int EPI_COLS = BN / (EPI_WARPS / 4);  // accumulator columns per epilogue warp (32)
+constexpr int EPI_CH = EPI_COLS / 2;           // columns per tcgen05.ld chunk (16)
+constexpr int THREADS = (2 + DEQ_WARPS + EPI_WARPS) * 32;  // 640: up to 96 registers per thread
 constexpr int OFF_A = 0;
 constexpr int OFF_B8 = OFF_A + SA * A_STAGE;
 constexpr int OFF_BP = OFF_B8 + S8 * B8_STAGE;
@@ -92,16 +99,26 @@ __device__ __forceinline__ void unpack_f32x2(uint64_t v, float &lo, float &hi) {
 }
 template <int EPI, int NC>
 __device__ __forceinline__ void epi_chunk(const uint32_t (&d)[NC], float x, const float *__restrict__ sw16, float *__restrict__ acc) {
-    constexpr bool MAGIC = (EPI & 1) != 0, PACKED = (EPI & 2) != 0;
+    constexpr bool PACKED = (EPI & 2) != 0, MIXED = (EPI & 4) != 0;
     if (PACKED) {
         const uint64_t xx = pack_f32x2(x, x);
 #pragma unroll
         for (int j4 = 0; j4 < NC / 4; j4++) {
             const float4 s4 = *reinterpret_cast<const float4 *>(sw16 + j4 * 4);
+            // EPI bit 2: alternate between the two conversions so that neither the conversion pipe nor the
+            // fp32 pipe carries all of them
+            const bool MAGIC = MIXED ? ((j4 & 1) != 0) : ((EPI & 1) != 0);
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 const int j = j4 * 4 + 2 * h;
-                const uint64_t f2 = pack_f32x2(cvt_exact(d[j], MAGIC), cvt_exact(d[j + 1], MAGIC));
+                uint64_t f2;
+                if (MAGIC) {
+                    const uint64_t i2 = pack_f32x2(__int_as_float((int)d[j] + 0x4B400000), __int_as_float((int)d[j + 1] + 0x4B400000));
+                    const uint64_t c2 = pack_f32x2(-12582912.0f, -12582912.0f);
+                    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(f2) : "l"(i2), "l"(c2));
+                } else {
+                    f2 = pack_f32x2(__int2float_rn((int)d[j]), __int2float_rn((int)d[j + 1]));
+                }
                 const uint64_t s2 = h == 0 ? pack_f32x2(s4.x, s4.y) : pack_f32x2(s4.z, s4.w);
                 uint64_t a2 = pack_f32x2(acc[j], acc[j + 1]);
                 uint64_t t2;
@@ -111,6 +128,7 @@ __device__ __forceinline__ void epi_chunk(const uint32_t (&d)[NC], float x, cons
             }
         }
     } else {
+        constexpr bool MAGIC = (EPI & 1) != 0;
 #pragma unroll
         for (int j4 = 0; j4 < NC / 4; j4++) {
             const float4 s4 = *reinterpret_cast<const float4 *>(sw16 + j4 * 4);
@@ -533,7 +551,7 @@ inline int epi_variant() {
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("W4A8_GEMM_EPI");
-        v = e ? atoi(e) & 3 : 2;
+        v = e ? atoi(e) & 7 : 2;
     }
     return v;
 }
@@ -544,6 +562,7 @@ inline int launch_tc_t(const int8_t *X, const float *xs, const uint8_t *Wq, cons
         case 1: return launch_tc_e<ST, DUMP, 1>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
         case 2: return launch_tc_e<ST, DUMP, 2>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
         case 3: return launch_tc_e<ST, DUMP, 3>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
+        case 6: return launch_tc_e<ST, DUMP, 6>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
         default: return launch_tc_e<ST, DUMP, 0>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
     }
 }
