@@ -441,14 +441,66 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_kernel_case(args):
+    """Small single-kernel run for profiler captures: `--kernel-case gemv_m1 | gemv_m8 | gemv_m16 | gemm_m512` launches that
+    kernel `--steps` times (eagerly, no graph) over 3 rotating copies of the K=5120 x N=17408 weights (167 MB, larger
+    than L2, well under 1 GB on the device) and prints its CUDA-event time.  Not a bench line."""
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    w = load_package()
+    w.lib()
+    name = args.kernel_case
+    kind, M = name.split("_m")
+    M = int(M)
+    K, N, nb = K_DIM, N_DIM, K_DIM // 32
+    g = torch.Generator(device=dev)
+    g.manual_seed(20260003)
+    Wqs = [torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=g) for _ in range(3)]
+    sws = [(torch.randn(N, nb, device=dev, generator=g).abs() * (0.02 / 7.0)) for _ in range(3)]
+    X = torch.randn(M, K, device=dev, generator=g)
+    xq = torch.empty((M, K), dtype=torch.int8, device=dev)
+    xs = torch.empty((M, nb), dtype=torch.float32, device=dev)
+    xsum = torch.empty((M, nb), dtype=torch.int32, device=dev)
+    w.launch_quantize_x_q8(X, xq, xs, xsum, K, M)
+    Y = torch.empty((M, N), dtype=torch.float32, device=dev)
+    s = torch.cuda.Stream()
+    steps = max(1, min(args.steps, 20))
+
+    def launch(i):
+        if kind == "gemv":
+            w.launch_gemv_w4a8_sb(xq, xs, Wqs[i % 3], sws[i % 3], Y, K, N, M, 0, s.cuda_stream)
+        elif kind == "gemm":
+            w.launch_gemm_mmq_w4a8(xq, xs, Wqs[i % 3], sws[i % 3], Y, M, N, K, 0, s.cuda_stream)
+        else:
+            raise SystemExit("unknown kernel case " + name)
+    with torch.cuda.stream(s):
+        for i in range(3):
+            launch(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        for i in range(steps):
+            launch(i)
+        e1.record(s)
+        torch.cuda.synchronize()
+    w.device_status()
+    print(json.dumps({"kernel_case": name, "launches": steps, "us_per_launch": e0.elapsed_time(e1) * 1e3 / steps}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kernel-case", default=None, help="profiler helper: gemv_m1, gemv_m8, gemv_m16 or gemm_m512 (see run_kernel_case)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.kernel_case:
+        run_kernel_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
