@@ -25,6 +25,10 @@ namespace w4a8 {
 namespace gemv_mma {
 
 constexpr int WARPS = 8;
+#ifndef W4A8_GEMV_RELAY
+#define W4A8_GEMV_RELAY 1
+#endif
+constexpr bool RELAY = W4A8_GEMV_RELAY != 0;
 // A step = 16 weight rows x GS groups (GS * 16 B contiguous per row) plus the 16 x GS scales (slot sized for fp32).
 __host__ __device__ constexpr int step_w(int GS) { return 16 * GS * 16; }
 __host__ __device__ constexpr int step_bytes(int GS) { return 16 * GS * 16 + 16 * GS * 4; }
@@ -86,22 +90,31 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_w4a8_mma_kernel(
     const int units = (OUT + 7) / 8;
     const int u0 = (int)(((long)units * blockIdx.x) / gridDim.x), u1 = (int)(((long)units * (blockIdx.x + 1)) / gridDim.x);
     const int ntiles_cta = (u1 - u0 + 1) / 2;
-    const int my_tiles = ntiles_cta > warp ? (ntiles_cta - warp + WARPS - 1) / WARPS : 0;
+    int my_tiles = ntiles_cta > warp ? (ntiles_cta - warp + WARPS - 1) / WARPS : 0;
     // When the CTA has fewer tiles than warps (narrow matrices), the idle warps' ring slots are lent to the working
     // ones: a warp that is alone with a long row range needs more bytes in flight to stream at full speed.
     int mult = 1;
-    while (mult < 4 && ntiles_cta * mult * 2 <= WARPS) mult *= 2;
+    // Narrow matrices, MH == 1: K relay.  A CTA with at most WARPS/2 tiles gives each tile KS warps; warp (tile, ks)
+    // streams steps ks, ks + KS, ... of the tile and computes their products t = (float)D * xs, and the fp32
+    // accumulators travel from the warp of step q to the warp of step q + 1 through a mailbox in shared memory, so
+    // that every accumulator still sees its groups in ascending order (the bits do not change) while KS rings of
+    // copies are in flight per tile instead of one.
+    int KS = 1;
+    if (MH == 1 && RELAY) while (KS < WARPS && ntiles_cta * KS * 2 <= WARPS) KS *= 2;
+    if (KS == 1) while (mult < 4 && ntiles_cta * mult * 2 <= WARPS) mult *= 2;
+    const int rtile = warp / KS, rks = warp % KS;            // relay: tile of this warp inside the CTA, first step
     const int depth = STAGES * mult;
+    if (KS > 1) my_tiles = (rtile < ntiles_cta && rks < nsteps) ? 1 : 0;
     unsigned char *ring = ring0 + (size_t)warp * mult * STAGES * STEP_BYTES;   // only warps < ntiles_cta use theirs when mult > 1
     const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring);
     const size_t wpitch = (size_t)(IN / 2);
 
     // Producer side of the warp's ring: copies of the next step (tile it, step iq) into slot isl.  One weight-copy
     // instruction covers 32/GS rows x GS*16 contiguous bytes each.
-    int it = 0, iq = 0, isl = 0;
+    int it = 0, iq = KS > 1 ? rks : 0, isl = 0;
     auto issue = [&]() {
         if (it < my_tiles) {
-            const int base = (u0 + 2 * (warp + it * WARPS)) * 8;
+            const int base = (u0 + 2 * (KS > 1 ? rtile : warp + it * WARPS)) * 8;
             const uint32_t slot = ring_u32 + (uint32_t)isl * STEP_BYTES;
             constexpr int RPI = 32 / GS;                         // rows per copy instruction
             const int lr = lane / GS, lj = lane % GS;
@@ -126,7 +139,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_w4a8_mma_kernel(
             }
         }
         cp_async_commit();                                        // one group per step, also when empty
-        if (++iq == nsteps) { iq = 0; it++; }
+        iq += KS;
+        if (iq >= nsteps) { iq = KS > 1 ? rks : 0; it++; }
         if (++isl == depth) isl = 0;
     };
 
@@ -159,6 +173,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_w4a8_mma_kernel(
             }
         }
     }
+    __shared__ float4 relay_box[WARPS / 2][32];
+    __shared__ unsigned int relay_flag[WARPS / 2];
+    if (tid < WARPS / 2) relay_flag[tid] = 0u;
     for (int i = tid; i < nb * 8 * MH; i += WARPS * 32) {
         const int b = i / (8 * MH), m = i % (8 * MH);
         sxs[i] = (m < S) ? xs[(size_t)m * nb + b] * 0.0625f : 0.f;   // exact 1/16: undoes the 16x of the expansion
@@ -169,6 +186,97 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_w4a8_mma_kernel(
     // ldmatrix row address of this lane inside a slot: matrix i = lane/8 -> rows (i&1)*8.., group 2*jj + (i>>1)
     const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8, lgrp = lane >> 4;
     int csl = 0;
+    if (MH == 1 && RELAY && KS > 1) {
+        if (my_tiles > 0) {
+            volatile unsigned int *flag = &relay_flag[rtile];
+            bool alive = true;
+            for (int q = rks; q < nsteps && alive; q += KS) {
+                issue();
+                cp_async_wait<STAGES - 1>();
+                __syncwarp();
+                const uint32_t slot = ring_u32 + (uint32_t)csl * STEP_BYTES;
+                const unsigned char *slot_p = ring + (size_t)csl * STEP_BYTES;
+                // ---- all products of this step first: tb[j][i] = (float)D * xs for group j of the step
+                float tb[GS][4];
+#pragma unroll
+                for (int j2 = 0; j2 < GS / 2; j2++) {
+                    uint32_t w[4];
+                    ldmatrix_x4(slot + lrow * (GS * 16) + (((2 * j2 + lgrp) ^ swz(lrow, GS)) << 4), w[0], w[1], w[2], w[3]);
+#pragma unroll
+                    for (int k = 0; k < 2; k++) {
+                        const int j = 2 * j2 + k, b = q * GS + j;
+                        uint32_t a0, a1, a2, a3;
+                        unpack8_x16(w[2 * k], a0, a2);
+                        unpack8_x16(w[2 * k + 1], a1, a3);
+                        const uint2 bx = (g < S) ? xqp[(size_t)g * pitch2 + 4 * b + t] : make_uint2(0u, 0u);
+                        int c[4];
+                        mma_s8(c, a0, a1, a2, a3, bx.x, bx.y);
+                        const float2 xv = *reinterpret_cast<const float2 *>(sxs + (size_t)b * 8 + 2 * t);
+                        tb[j][0] = (float)c[0] * xv.x; tb[j][1] = (float)c[1] * xv.y;
+                        tb[j][2] = (float)c[2] * xv.x; tb[j][3] = (float)c[3] * xv.y;
+                    }
+                }
+                // ---- take the accumulators over from the warp of step q - 1 (bounded wait)
+                float a[4] = {0.f, 0.f, 0.f, 0.f};
+                if (q > 0) {
+                    unsigned int n = 0;
+                    while (*flag < (unsigned)q) {
+                        if (++n > (1u << 24)) { dev_set_error(0x300u | (unsigned)warp); alive = false; break; }
+                    }
+                    alive = __all_sync(0xffffffffu, alive);
+                    if (!alive) break;
+                    __threadfence_block();
+                    const float4 v = relay_box[rtile][lane];
+                    a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w;
+                }
+                // ---- this step's groups, ascending
+#pragma unroll
+                for (int j4 = 0; j4 < GS / 4; j4++) {
+                    float swA[4], swB[4];
+                    if (sizeof(ST) == 4) {
+                        const float4 fa = *reinterpret_cast<const float4 *>(slot_p + STEP_W + g * (GS * 4) + j4 * 16);
+                        const float4 fb = *reinterpret_cast<const float4 *>(slot_p + STEP_W + (g + 8) * (GS * 4) + j4 * 16);
+                        swA[0] = fa.x; swA[1] = fa.y; swA[2] = fa.z; swA[3] = fa.w;
+                        swB[0] = fb.x; swB[1] = fb.y; swB[2] = fb.z; swB[3] = fb.w;
+                    } else {
+                        const __half *ha = reinterpret_cast<const __half *>(slot_p + STEP_W + g * (GS * 2) + j4 * 8);
+                        const __half *hb = reinterpret_cast<const __half *>(slot_p + STEP_W + (g + 8) * (GS * 2) + j4 * 8);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) { swA[j] = __half2float(ha[j]); swB[j] = __half2float(hb[j]); }
+                    }
+#pragma unroll
+                    for (int js = 0; js < 4; js++) {
+                        const int j = 4 * j4 + js;
+                        a[0] = fmaf(tb[j][0], swA[js], a[0]);
+                        a[1] = fmaf(tb[j][1], swA[js], a[1]);
+                        a[2] = fmaf(tb[j][2], swB[js], a[2]);
+                        a[3] = fmaf(tb[j][3], swB[js], a[3]);
+                    }
+                }
+                if (q + 1 < nsteps) {                          // hand over to the warp of step q + 1
+                    relay_box[rtile][lane] = make_float4(a[0], a[1], a[2], a[3]);
+                    __threadfence_block();
+                    __syncwarp();
+                    if (lane == 0) *flag = (unsigned)(q + 1);
+                } else {                                       // last step: these are the outputs
+                    const int base = (u0 + 2 * rtile) * 8;
+                    const int lim = min(OUT, u1 * 8);
+                    const int m0 = 2 * t, rA = base + g, rB = base + 8 + g;
+                    if (rA < lim) {
+                        if (m0 < S) store_out<PEER>(Y, oa, OUT, m0, rA, a[0]);
+                        if (m0 + 1 < S) store_out<PEER>(Y, oa, OUT, m0 + 1, rA, a[1]);
+                    }
+                    if (rB < lim) {
+                        if (m0 < S) store_out<PEER>(Y, oa, OUT, m0, rB, a[2]);
+                        if (m0 + 1 < S) store_out<PEER>(Y, oa, OUT, m0 + 1, rB, a[3]);
+                    }
+                }
+                __syncwarp();                                  // the slot is refilled by the next iteration's copies
+                if (++csl == depth) csl = 0;
+            }
+        }
+        my_tiles = 0;                                          // nothing left for the ordinary loop
+    }
     for (int ti = 0; ti < my_tiles; ti++) {
 #pragma unroll
         for (int h = 0; h < MH; h++) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;

@@ -154,7 +154,9 @@ int w4a8_linear(const float *X, int8_t *xq, float *xs, int32_t *xsum, const uint
 /* mm() for a caller whose activations and results live in HOST memory (the daemon side of the reference's pipe
  * protocol, runtime/serving_online.h): copies X_host[S,K] to X_dev, runs w4a8_linear into Y_dev, copies Y_dev[S,N]
  * to Y_host and synchronises the stream, so Y_host is complete on return.  All device buffers are the caller's
- * (same scratch as w4a8_linear plus X_dev and Y_dev); pinned host memory makes the copies asynchronous. */
+ * (same scratch as w4a8_linear plus X_dev and Y_dev); pinned host memory makes the copies asynchronous, and a
+ * small pinned X (up to 1 MiB) is read by the quantizer directly over the bus instead of being copied first
+ * (X_dev is then unused). */
 int w4a8_linear_host(const float *X_host, float *Y_host, float *X_dev, int8_t *xq, float *xs, int32_t *xsum,
                      float *Y_dev, const uint8_t *Wq, const void *sw, int S, int N, int K, int scale_dtype,
                      void *stream);

@@ -276,21 +276,27 @@ def test_linear_dispatch_and_loader(w4a8, oracle, cuda, tmp_path):
     assert ei.value.code == w4a8.ERR_IO
 
 
-def test_linear_host_entry(w4a8, oracle, cuda):
-    """mm() with host buffers: H2D, quantize + product, D2H, synchronous."""
-    S, N, K = 3, 200, 512
+@pytest.mark.parametrize("pinned", [True, False])
+@pytest.mark.parametrize("S,N,K", [(3, 200, 512), (1, 1000, 1024), (40, 7000, 1024)])
+def test_linear_host_entry(w4a8, oracle, cuda, S, N, K, pinned):
+    """mm() with host buffers: X in, quantize + product, Y out, synchronous.  Pinned buffers of a small step are read
+    and written by the kernels themselves; pageable buffers, and steps above 1 MiB, go through the copy engines."""
     X = oracle.make_activations(S, K, seed=8)
     Wq, sw = oracle.make_weights(N, K, seed=9)
-    Xh = torch.from_numpy(X).pin_memory()
-    Yh = torch.empty((S, N), dtype=torch.float32).pin_memory()
+    Xh = torch.from_numpy(X)
+    Yh = torch.full((S, N), float("nan"), dtype=torch.float32)
+    if pinned:
+        Xh, Yh = Xh.pin_memory(), Yh.pin_memory()
     Xd = torch.empty((S, K), dtype=torch.float32, device=cuda)
     xq = torch.empty((S, K), dtype=torch.int8, device=cuda)
     xs = torch.empty((S, K // 32), dtype=torch.float32, device=cuda)
     xsum = torch.empty((S, K // 32), dtype=torch.int32, device=cuda)
     Yd = torch.empty((S, N), dtype=torch.float32, device=cuda)
     w4a8.linear_host(Xh, Yh, Xd, xq, xs, xsum, Yd, to_dev(Wq, cuda), to_dev(sw, cuda), S, N, K)
+    w4a8.device_status()
     xq_o, xs_o, _ = oracle.quantize_x_q8(X)
-    assert np.array_equal(Yh.numpy().view(np.uint32), gemv_expected(oracle, xq_o, xs_o, Wq, sw).view(np.uint32))
+    want = gemv_expected(oracle, xq_o, xs_o, Wq, sw) if S <= 16 else oracle.gemm_mmq_w4a8(xq_o, xs_o, Wq, sw)
+    assert np.array_equal(Yh.numpy().view(np.uint32), want.view(np.uint32))
 
 
 # ---- BASELINE.json configs at their full shapes -----------------------------------------------------------------
