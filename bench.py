@@ -340,6 +340,16 @@ def run_ours(args):
         us_h = ms_h * 1e3 / args.steps
         extra["gemv_m1_fp16_scales"] = {"us": us_h, "gbps": gemv_bytes(1, N, K, 2) / (us_h * 1e-6) / 1e9}
         del sws16
+        # ---- an lm_head-sized matrix (vocabulary 151936 x K=5120, 487 MB): auto policy streams it with bulk copies ----
+        Nv = 151936
+        vq = [torch.randint(0, 256, (Nv, K // 2), dtype=torch.uint8, device=dev, generator=g) for _ in range(2)]
+        vs = [(torch.randn(Nv, nb, device=dev, generator=g).abs() * (0.02 / 7.0)) for _ in range(2)]
+        Yv = torch.empty((1, Nv), dtype=torch.float32, device=dev)
+        ms_v = time_steps(lambda i, st: w.launch_gemv_w4a8_sb(xq, xs, vq[i % 2], vs[i % 2], Yv, K, Nv, 1, 0, st), 20, 3, graph=True)
+        us_v = ms_v * 1e3 / 20
+        gb_v = gemv_bytes(1, Nv, K) / (us_v * 1e-6) / 1e9
+        extra["gemv_m1_lm_head_k5120_n151936"] = {"us": us_v, "gbps": gb_v, "frac_of_measured_hbm": gb_v / hbm_peak}
+        del vq, vs, Yv
         # ---- BASELINE configs[2]: Gemma4-12B-class layer set at M=8, launched back to back --------------------------
         layer = [(3840, 4096), (3840, 3840), (3840, 15360), (3840, 15360), (15360, 3840)]
         reps = 5                                                     # 5 distinct layers' worth of weights (648 MB > L2)

@@ -12,6 +12,7 @@
 #include "quantize_x.cuh"
 #include "gemv_w4a8.cuh"
 #include "gemv_w4a8_mma.cuh"
+#include "gemv_w4a8_bulk.cuh"
 #include "gemm_w4a8_tc.cuh"
 #include "gemm_w4a8_tcf.cuh"
 
@@ -137,7 +138,7 @@ static int g_gemv_policy = -1;
 static int gemv_policy() {
     if (g_gemv_policy < 0) {
         const char *e = getenv("W4A8_GEMV");
-        g_gemv_policy = !e ? 0 : (e[0] == 'm' ? 2 : (e[0] == 'd' ? 1 : 0));
+        g_gemv_policy = !e ? 0 : (e[0] == 'm' ? 2 : (e[0] == 'd' ? 1 : (e[0] == 'b' ? 3 : 0)));
     }
     return g_gemv_policy;
 }
@@ -175,6 +176,17 @@ static int gemv_dispatch(const int8_t *xq, const float *xs, const uint8_t *Wq, c
             return W4A8_OK;
         }
     }
+    // One row: the bulk-copy stream has the higher steady rate (about 6.5 TB/s against 5.8) but the larger fixed cost
+    // per launch, so auto takes it from about 100 MB of weights up (an lm_head, not a 56 MB MLP matrix).  Same fp32
+    // order as the dp4a kernel, so the choice never changes a result.
+    const size_t wbytes = (size_t)OUT * ((size_t)IN / 2 + (size_t)(IN / QBLK) * (scale_dtype == 1 ? 2 : 4));
+    if (S == 1 && !current_out().peers && (gemv_policy() == 3 || (gemv_policy() == 0 && wbytes >= (100u << 20)))) {
+        gemv_bulk::Plan bp;
+        if (gemv_bulk::plan_for(xq, Wq, sw, IN, scale_dtype, &bp)) {
+            if (count_only) { *count_only = 1; return W4A8_OK; }
+            return gemv_bulk::launch(xq, xs, Wq, sw, Y, IN, OUT, scale_dtype, bp, st);
+        }
+    }
     if (count_only) { *count_only = (S + GEMV_MT_MAX - 1) / GEMV_MT_MAX; return W4A8_OK; }
     return launch_gemv(xq, xs, Wq, sw, Y, IN, OUT, S, scale_dtype, st);
 }
@@ -203,7 +215,7 @@ W4A8_API int w4a8_config(const char *key, int value) {
         return W4A8_OK;
     }
     if (!strcmp(key, "gemv_kernel")) {
-        if (value < 0 || value > 2) return fail(W4A8_ERR_ARG, "config: gemv_kernel = 0 (auto), 1 (dp4a), 2 (tensor path); got %d", value);
+        if (value < 0 || value > 3) return fail(W4A8_ERR_ARG, "config: gemv_kernel = 0 (auto), 1 (dp4a), 2 (tensor path), 3 (bulk-copy stream for S = 1); got %d", value);
         g_gemv_policy = value;
         return W4A8_OK;
     }

@@ -87,13 +87,14 @@ GEMV_SHAPES = [(1024, 256, 1), (1024, 2048, 1), (3584, 1024, 1), (1024, 4096, 5)
 
 def gemv_expected(oracle, xq, xs, Wq, sw, policy=0):
     """The documented fp32 order of w4a8_gemv: the tensor-path kernel (MMQ order) serves S >= 2 (every S under
-    policy 2; also S = 1 with fp16 scales) when K % 256 == 0, the dp4a kernel (its own chain order) everything else."""
+    policy 2; also S = 1 with fp16 scales) when K % 256 == 0, the dp4a kernel (its own chain order) everything else;
+    policy 3 streams a single row through the bulk-copy kernel, which keeps the dp4a kernel's order."""
     S, K = xq.shape
     mma = K % 256 == 0 and (policy == 2 or (policy == 0 and (S >= 2 or sw.dtype == np.float16)))
     return oracle.gemm_mmq_w4a8(xq, xs, Wq, sw) if mma else oracle.gemv_b200_order(xq, xs, Wq, sw)
 
 
-@pytest.mark.parametrize("policy", [0, 1, 2])
+@pytest.mark.parametrize("policy", [0, 1, 2, 3])
 @pytest.mark.parametrize("scale_dtype", [0, 1])
 @pytest.mark.parametrize("IN,OUT,S", GEMV_SHAPES)
 def test_gemv_parity(w4a8, oracle, cuda, IN, OUT, S, scale_dtype, policy):
