@@ -63,6 +63,9 @@ int w4a8_device_status(uint32_t *detail);
  *                  the MMQ order (bit-identical to w4a8_gemm and to the reference's MMQ kernels); the dp4a kernel
  *                  in its own fixed order (within 1e-5).  Policy 2 therefore makes a row's bits independent of S
  *                  for all S >= 1 (the reference's batch == single invariant), policy 0 for all S >= 2.
+ *                  3 = single rows through the bulk-copy streaming kernel wherever it applies (K % 128 == 0, K <= 8192,
+ *                  16-byte aligned Wq and sw); it evaluates in the dp4a kernel's order, bit for bit, and auto already
+ *                  picks it for matrices of 100 MB and more.
  *   "gemm_kernel": which tensor-core kernel w4a8_gemm / w4a8_gemm_splitk / w4a8_linear use (environment:
  *                  W4A8_GEMM = i8 | f16).  1 = int8 operands, tcgen05.mma kind::i8, int32 group dots converted in
  *                  the epilogue (default, the faster one); 0 = operands converted to fp16 on the way into shared
