@@ -3,15 +3,18 @@
 // reference's kernels/gemv_w4a8.cuh:119-151): lane l of the warp that owns a row takes groups l, l+32, ... in
 // ascending order, acc = fma((xs*sw)/16, (float)(16*D), acc), then the shfl_down tree — bit-identical results.
 //
-// Why a second M=1 kernel: a 12-microsecond stream is bound by the bytes it keeps in flight.  With register loads a
-// lane holds five 16-byte loads, 24 warps per SM -> about 60 KB per SM.  Here the rows of a CTA are contiguous in
-// memory, so ROWS consecutive weight rows are one contiguous block: one elected thread issues one bulk copy per
-// block (plus one for the block's scales) and the copy engine keeps up to the whole ring (about 100 KB per CTA, two
-// CTAs per SM) in flight without holding a register or an issue slot.  The activation row lives in registers (a
-// lane always meets the same groups), so the consumers read only weights and scales from shared memory.
+// Why a second M=1 kernel: a 10-microsecond stream is bound by the bytes it keeps in flight and by what a launch
+// costs before and after its steady state.  With register loads a lane holds five 16-byte loads, 24 warps per SM ->
+// about 60 KB per SM, and every byte in flight holds a register and an issue slot.  Here the rows of a CTA are
+// contiguous in memory, so ROWS consecutive weight rows are one contiguous block: one elected thread issues one bulk
+// copy per block (plus one for the block's scales) and the copy engine keeps the whole ring (4 stages of 12 rows,
+// about 150 KB per SM) in flight.  The activation row lives in registers (a lane always meets the same groups), so
+// the consumers read only weights and scales from shared memory.  Measured on K=5120, N=17408: 10.2 us against
+// 11.5 us for the register-load kernel; K=5120, N=151936: 71 us = 6.9 TB/s.  One CTA per SM with 12 consumer warps
+// measured best; two smaller CTAs per SM, or rings deeper than 4 stages, were slower.
 //
-// Preconditions (else the caller uses the dp4a kernel): S = 1, K % 128 = 0 (K % 256 = 0 with fp16 scales: scale rows
-// are multiples of 16 bytes), K <= 8192, Wq and sw 16-byte aligned.
+// Preconditions (else the caller uses another kernel): S = 1, K % 128 = 0 (K % 256 = 0 with fp16 scales: scale rows
+// are multiples of 16 bytes), K <= 8192, Wq and sw 16-byte aligned.  No peer-store epilogue and no expert grouping.
 #pragma once
 #include "common.cuh"
 #include "ptx_sm100.cuh"
@@ -20,9 +23,12 @@
 namespace w4a8 {
 namespace gemv_bulk {
 
-constexpr int CW = 8;                   // consumer warps per CTA
+#ifndef W4A8_BULK_CW
+#define W4A8_BULK_CW 12
+#endif
+constexpr int CW = W4A8_BULK_CW;        // consumer warps per CTA
 #ifndef W4A8_BULK_RPW
-#define W4A8_BULK_RPW 2
+#define W4A8_BULK_RPW 1
 #endif
 constexpr int RPW = W4A8_BULK_RPW;      // rows per warp and stage, processed interleaved (independent chains)
 constexpr int ROWS = CW * RPW;          // weight rows per ring stage
@@ -176,12 +182,12 @@ inline bool plan_for(const void *xq, const void *Wq, const void *sw, int IN, int
     if (!aligned(Wq, 16) || !aligned(sw, 16) || !aligned(xq, 4)) return false;
     const size_t stage = (size_t)ROWS * ((size_t)IN / 2 + (size_t)nb * (scale_dtype == 1 ? 2 : 4));
     static const int want_st = [] { const char *e = getenv("W4A8_GEMV_BULK_STAGES"); return e ? atoi(e) : 0; }();
-    static const int want_occ = [] { const char *e = getenv("W4A8_GEMV_BULK_OCC"); return e ? atoi(e) : 2; }();
+    static const int want_occ = [] { const char *e = getenv("W4A8_GEMV_BULK_OCC"); return e ? atoi(e) : 1; }();
     int occ = want_occ >= 2 ? 2 : 1;
     int st = (int)((112u * 1024u - BAR_BYTES) / stage);
     if (occ == 2 && st < 2) occ = 1;
     if (occ == 1) st = (int)((224u * 1024u - BAR_BYTES) / stage);
-    if (st > MAX_STAGES) st = MAX_STAGES;
+    if (st > (occ == 1 ? 4 : MAX_STAGES)) st = occ == 1 ? 4 : MAX_STAGES;   // one CTA per SM: deeper than 4 stages measured slower
     if (want_st > 0 && want_st < st) st = want_st;
     if (st < 2) return false;
     p->NG = (nb + 31) / 32; p->stages = st; p->ctas_per_sm = occ; p->smem = BAR_BYTES + (size_t)st * stage;

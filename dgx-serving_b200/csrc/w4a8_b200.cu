@@ -153,6 +153,15 @@ static bool gemv_use_mma(int S, int scale_dtype) {
 // launched, *count_only receives the number of kernel launches the call would make.
 static int gemv_dispatch(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int IN, int OUT, int S,
                          int scale_dtype, cudaStream_t st, int *count_only) {
+    // One row: the bulk-copy stream (same fp32 order as the dp4a kernel, so the choice never changes a result for fp32
+    // scales) is the faster kernel from rows of 2048 elements up; shorter rows make its copies too small.
+    if (S == 1 && !current_out().peers && (gemv_policy() == 3 || (gemv_policy() == 0 && IN >= 2048))) {
+        gemv_bulk::Plan bp;
+        if (gemv_bulk::plan_for(xq, Wq, sw, IN, scale_dtype, &bp)) {
+            if (count_only) { *count_only = 1; return W4A8_OK; }
+            return gemv_bulk::launch(xq, xs, Wq, sw, Y, IN, OUT, scale_dtype, bp, st);
+        }
+    }
     if (gemv_use_mma(S, scale_dtype)) {
         // rows go in passes of up to 16 (8 when 16 rows of activations do not fit in shared memory next to the ring)
         gemv_mma::Plan plan;
@@ -174,17 +183,6 @@ static int gemv_dispatch(const int8_t *xq, const float *xs, const uint8_t *Wq, c
                 if (rc != W4A8_OK) return rc;
             }
             return W4A8_OK;
-        }
-    }
-    // One row: the bulk-copy stream has the higher steady rate (about 6.5 TB/s against 5.8) but the larger fixed cost
-    // per launch, so auto takes it from about 100 MB of weights up (an lm_head, not a 56 MB MLP matrix).  Same fp32
-    // order as the dp4a kernel, so the choice never changes a result.
-    const size_t wbytes = (size_t)OUT * ((size_t)IN / 2 + (size_t)(IN / QBLK) * (scale_dtype == 1 ? 2 : 4));
-    if (S == 1 && !current_out().peers && (gemv_policy() == 3 || (gemv_policy() == 0 && wbytes >= (100u << 20)))) {
-        gemv_bulk::Plan bp;
-        if (gemv_bulk::plan_for(xq, Wq, sw, IN, scale_dtype, &bp)) {
-            if (count_only) { *count_only = 1; return W4A8_OK; }
-            return gemv_bulk::launch(xq, xs, Wq, sw, Y, IN, OUT, scale_dtype, bp, st);
         }
     }
     if (count_only) { *count_only = (S + GEMV_MT_MAX - 1) / GEMV_MT_MAX; return W4A8_OK; }

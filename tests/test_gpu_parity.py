@@ -86,11 +86,14 @@ GEMV_SHAPES = [(1024, 256, 1), (1024, 2048, 1), (3584, 1024, 1), (1024, 4096, 5)
 
 
 def gemv_expected(oracle, xq, xs, Wq, sw, policy=0):
-    """The documented fp32 order of w4a8_gemv: the tensor-path kernel (MMQ order) serves S >= 2 (every S under
-    policy 2; also S = 1 with fp16 scales) when K % 256 == 0, the dp4a kernel (its own chain order) everything else;
-    policy 3 streams a single row through the bulk-copy kernel, which keeps the dp4a kernel's order."""
+    """The documented fp32 order of w4a8_gemv.  Auto: a single row of 2048..8192 elements goes through the bulk-copy
+    stream, which keeps the dp4a kernel's chain order; the tensor-path kernel (MMQ order) serves S >= 2, and S = 1 with
+    fp16 scales outside that range, when K % 256 == 0; the dp4a kernel everything else.  Policy 1: dp4a for every S;
+    2: tensor path for every S it supports; 3: bulk-copy stream for every single row it supports, dp4a otherwise."""
     S, K = xq.shape
-    mma = K % 256 == 0 and (policy == 2 or (policy == 0 and (S >= 2 or sw.dtype == np.float16)))
+    fp16 = sw.dtype == np.float16
+    bulk = S == 1 and K % (256 if fp16 else 128) == 0 and K <= 8192 and (policy == 3 or (policy == 0 and K >= 2048))
+    mma = not bulk and K % 256 == 0 and (policy == 2 or (policy == 0 and (S >= 2 or fp16)))
     return oracle.gemm_mmq_w4a8(xq, xs, Wq, sw) if mma else oracle.gemv_b200_order(xq, xs, Wq, sw)
 
 
