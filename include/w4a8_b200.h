@@ -57,15 +57,15 @@ int w4a8_device_status(uint32_t *detail);
 
 /* Run-time policy switches (the reference keeps such switches in runtime/knobs.h, read from the environment;
  * the same names are read here once: W4A8_GEMV = dp4a | mma, W4A8_PDL = 0 | 1).
- *   "gemv_kernel": 0 = auto (default): one activation row with fp32 scales uses the dp4a streaming kernel,
- *                  2..16 rows (and one row with fp16 scales) the tensor-path kernel; 1 = dp4a kernel for every S; 2 = tensor-path kernel for every S it
- *                  supports (K % 256 == 0, 16-byte aligned Wq and sw).  The tensor-path kernel evaluates fp32 in
- *                  the MMQ order (bit-identical to w4a8_gemm and to the reference's MMQ kernels); the dp4a kernel
- *                  in its own fixed order (within 1e-5).  Policy 2 therefore makes a row's bits independent of S
- *                  for all S >= 1 (the reference's batch == single invariant), policy 0 for all S >= 2.
- *                  3 = single rows through the bulk-copy streaming kernel wherever it applies (K % 128 == 0, K <= 8192,
- *                  16-byte aligned Wq and sw); it evaluates in the dp4a kernel's order, bit for bit, and auto already
- *                  picks it for matrices of 100 MB and more.
+ *   "gemv_kernel": 0 = auto (default): one activation row of 2048..8192 elements uses the bulk-copy streaming kernel,
+ *                  2..16 rows (and one row with fp16 scales outside that range) the tensor-path kernel, everything
+ *                  else the dp4a streaming kernel; 1 = dp4a kernel for every S; 2 = tensor-path kernel for every S it
+ *                  supports (K % 256 == 0, 16-byte aligned Wq and sw); 3 = bulk-copy kernel for every single row it
+ *                  supports (K % 128 == 0, K <= 8192, 16-byte aligned Wq and sw), dp4a otherwise.
+ *                  The tensor-path kernel evaluates fp32 in the MMQ order (bit-identical to w4a8_gemm and to the
+ *                  reference's MMQ kernels); the dp4a and bulk-copy kernels share one fixed order of their own (within
+ *                  1e-5).  Policy 2 therefore makes a row's bits independent of S for all S >= 1 (the reference's
+ *                  batch == single invariant), policy 0 for all S >= 2.
  *   "gemm_kernel": which tensor-core kernel w4a8_gemm / w4a8_gemm_splitk / w4a8_linear use (environment:
  *                  W4A8_GEMM = i8 | f16).  1 = int8 operands, tcgen05.mma kind::i8, int32 group dots converted in
  *                  the epilogue (default, the faster one); 0 = operands converted to fp16 on the way into shared
