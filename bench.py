@@ -404,6 +404,32 @@ def run_ours(args):
                 ref.ref_quantize_x_q8(P(Xd2), P(xq2), P(xs2), P(xsum2), K, 2048, ctypes.c_void_p(st))
                 ref.ref_gemm_mmq_w4a8(P(xq2), P(xs2), P(Wqs[i % nbuf]), P(sws[i % nbuf]), P(Y2), 2048, N, K, 0, ctypes.c_void_p(st))
             ms_rg = time_steps(ref_gemm, 3, 3, graph=False)
+            # ---- quantize_x fused into its producer, against the reference's two kernels (decode, one row) -----------
+            ref.ref_rmsnorm.restype = ctypes.c_int
+            ref.ref_glu.restype = ctypes.c_int
+            H, F = K, N
+            xh = torch.randn(1, H, device=dev, generator=g); wn = torch.randn(H, device=dev, generator=g) * 0.1
+            nrm = torch.empty(1, H, device=dev)
+            gg = torch.randn(1, F, device=dev, generator=g); uu = torch.randn(1, F, device=dev, generator=g)
+            act = torch.empty(1, F, device=dev)
+            fq = torch.empty((1, F), dtype=torch.int8, device=dev); fs = torch.empty((1, F // 32), dtype=torch.float32, device=dev)
+            fsum = torch.empty((1, F // 32), dtype=torch.int32, device=dev)
+
+            def ref_norm_q(i, st):
+                ref.ref_rmsnorm(P(xh), P(wn), P(nrm), 1, H, ctypes.c_float(1e-6), 1, ctypes.c_void_p(st))
+                ref.ref_quantize_x_q8(P(nrm), P(fq), P(fs), P(fsum), H, 1, ctypes.c_void_p(st))
+
+            def ref_glu_q(i, st):
+                ref.ref_glu(P(gg), P(uu), P(act), ctypes.c_long(F), 0, ctypes.c_void_p(st))
+                ref.ref_quantize_x_q8(P(act), P(fq), P(fs), P(fsum), F, 1, ctypes.c_void_p(st))
+            fused = {}
+            for name, ours, theirs in (
+                    ("rmsnorm_zc+quantize_h5120", lambda i, st: w.launch_rmsnorm_quantize_x_q8(xh, wn, 1e-6, 1, None, fq, fs, fsum, H, 1, st), ref_norm_q),
+                    ("swiglu+quantize_f17408", lambda i, st: w.launch_glu_quantize_x_q8(gg, uu, 0, None, fq, fs, fsum, F, 1, st), ref_glu_q)):
+                us_o = time_steps(ours, 100, 3, graph=True) * 1e3 / 100
+                us_t = time_steps(theirs, 100, 3, graph=True) * 1e3 / 100
+                fused[name] = {"us_fused": us_o, "us_reference_two_kernels": us_t}
+            extra["fused_quantize_m1"] = fused
             extra["reference_kernels_sm100a"] = {
                 "gemv_w4a8_mlp2_m1": {"us": us_r, "gbps": gemv_bytes(1, N, K) / (us_r * 1e-6) / 1e9},
                 "quantize+gemm_mmq_m2048": {"us": ms_rg * 1e3 / 3, "int8_tops": 2.0 * 2048 * N * K / (ms_rg / 3 * 1e-3) / 1e12}}

@@ -42,6 +42,8 @@ _SIGNATURES = {
     "w4a8_device_status": (_I, [ctypes.POINTER(ctypes.c_uint32)]),
     "w4a8_config": (_I, [ctypes.c_char_p, _I]),
     "w4a8_quantize_x_q8": (_I, [_P, _P, _P, _P, _I, _I, _P]),
+    "w4a8_rmsnorm_quantize_x_q8": (_I, [_P, _P, ctypes.c_float, _I, _P, _P, _P, _P, _I, _I, _P]),
+    "w4a8_glu_quantize_x_q8": (_I, [_P, _P, _I, _P, _P, _P, _P, _I, _I, _P]),
     "w4a8_gemv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "w4a8_gemm": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "w4a8_gemm_splitk_workspace_bytes": (_Z, [_I, _I, _I, _I]),
@@ -119,6 +121,18 @@ def device_status():
 
 def launch_quantize_x_q8(X, xq, xs, xsum, IN, S, stream=None):
     _check(lib().w4a8_quantize_x_q8(_ptr(X), _ptr(xq), _ptr(xs), _ptr(xsum), IN, S, _stream(stream)))
+
+
+def launch_rmsnorm_quantize_x_q8(X, W, eps, variant, Y, xq, xs, xsum, IN, S, stream=None):
+    """RMSNorm (variant 0: * W, 1: * (1 + W), 2: no scale) and quantize_x in one kernel; Y (may be None) also gets the
+    fp32 intermediate.  Same bits as the reference's launch_rmsnorm* followed by launch_quantize_x_q8."""
+    _check(lib().w4a8_rmsnorm_quantize_x_q8(_ptr(X), _ptr(W), float(eps), variant, _ptr(Y), _ptr(xq), _ptr(xs), _ptr(xsum), IN, S,
+                                            _stream(stream)))
+
+
+def launch_glu_quantize_x_q8(G, U, act, Y, xq, xs, xsum, IN, S, stream=None):
+    """SwiGLU (act 0) or GeGLU (act 1) of (G, U) and quantize_x in one kernel; Y (may be None) also gets the fp32 product."""
+    _check(lib().w4a8_glu_quantize_x_q8(_ptr(G), _ptr(U), act, _ptr(Y), _ptr(xq), _ptr(xs), _ptr(xsum), IN, S, _stream(stream)))
 
 
 def launch_gemv_w4a8(xq, xs, xsum, Wq, sw, Y, IN, OUT, S, scale_dtype=0, stream=None):

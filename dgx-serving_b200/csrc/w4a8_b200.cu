@@ -10,6 +10,7 @@
 
 #include "common.cuh"
 #include "quantize_x.cuh"
+#include "fused_quantize.cuh"
 #include "gemv_w4a8.cuh"
 #include "gemv_w4a8_mma.cuh"
 #include "gemv_w4a8_bulk.cuh"
@@ -129,6 +130,32 @@ W4A8_API int w4a8_quantize_x_q8(const float *X, int8_t *xq, float *xs, int32_t *
     int rc = require_sm100();
     if (rc != W4A8_OK) return rc;
     return launch_quantize_x(X, xq, xs, xsum, IN, S, (cudaStream_t)stream);
+}
+
+W4A8_API int w4a8_rmsnorm_quantize_x_q8(const float *X, const float *W, float eps, int variant, float *Y, int8_t *xq, float *xs,
+                                        int32_t *xsum, int IN, int S, void *stream) {
+    if (S < 0 || IN < 0 || IN % QBLK != 0) return fail(W4A8_ERR_ARG, "rmsnorm_quantize_x_q8: IN=%d S=%d (IN must be a multiple of %d)", IN, S, QBLK);
+    if (variant < 0 || variant > 2) return fail(W4A8_ERR_ARG, "rmsnorm_quantize_x_q8: variant=%d (0 scale, 1 one-plus-scale, 2 no scale)", variant);
+    if (S == 0 || IN == 0) return W4A8_OK;
+    if (!X || !xq || !xs || (variant != 2 && !W)) return fail(W4A8_ERR_ARG, "rmsnorm_quantize_x_q8: null pointer argument");
+    if (!aligned(X, 16) || !aligned(xq, 4) || (W && !aligned(W, 16)) || (Y && !aligned(Y, 16)))
+        return fail(W4A8_ERR_ALIGN, "rmsnorm_quantize_x_q8: X, W and Y must be 16-byte aligned");
+    int rc = require_sm100();
+    if (rc != W4A8_OK) return rc;
+    return launch_rmsnorm_quantize(X, W, eps, variant, Y, xq, xs, xsum, IN, S, (cudaStream_t)stream);
+}
+
+W4A8_API int w4a8_glu_quantize_x_q8(const float *G, const float *U, int act, float *Y, int8_t *xq, float *xs, int32_t *xsum, int IN,
+                                    int S, void *stream) {
+    if (S < 0 || IN < 0 || IN % QBLK != 0) return fail(W4A8_ERR_ARG, "glu_quantize_x_q8: IN=%d S=%d (IN must be a multiple of %d)", IN, S, QBLK);
+    if (act < 0 || act > 1) return fail(W4A8_ERR_ARG, "glu_quantize_x_q8: act=%d (0 SwiGLU, 1 GeGLU)", act);
+    if (S == 0 || IN == 0) return W4A8_OK;
+    if (!G || !U || !xq || !xs) return fail(W4A8_ERR_ARG, "glu_quantize_x_q8: null pointer argument");
+    if (!aligned(G, 16) || !aligned(U, 16) || !aligned(xq, 4) || (Y && !aligned(Y, 16)))
+        return fail(W4A8_ERR_ALIGN, "glu_quantize_x_q8: G, U and Y must be 16-byte aligned");
+    int rc = require_sm100();
+    if (rc != W4A8_OK) return rc;
+    return launch_glu_quantize(G, U, act, Y, xq, xs, xsum, IN, S, (cudaStream_t)stream);
 }
 
 // GEMV kernel policy: 0 auto (one activation row with fp32 scales -> dp4a kernel, else tensor-path kernel), 1 always dp4a,

@@ -56,7 +56,7 @@ const char *w4a8_last_error(void);
 int w4a8_device_status(uint32_t *detail);
 
 /* Run-time policy switches (the reference keeps such switches in runtime/knobs.h, read from the environment;
- * the same names are read here once: W4A8_GEMV = dp4a | mma, W4A8_PDL = 0 | 1).
+ * the same names are read here once: W4A8_GEMV = dp4a | mma | bulk, W4A8_PDL = 0 | 1).
  *   "gemv_kernel": 0 = auto (default): one activation row of 2048..8192 elements uses the bulk-copy streaming kernel,
  *                  2..16 rows (and one row with fp16 scales outside that range) the tensor-path kernel, everything
  *                  else the dp4a streaming kernel; 1 = dp4a kernel for every S; 2 = tensor-path kernel for every S it
@@ -80,6 +80,22 @@ int w4a8_config(const char *key, int value);
  * the block; may be NULL).  Bit-exact with the reference: d = amax/127.0f, q = rintf(x/d) clamped to
  * +-127, all-zero block -> q = 0, d = 0. */
 int w4a8_quantize_x_q8(const float *X, int8_t *xq, float *xs, int32_t *xsum, int IN, int S, void *stream);
+
+/* ---- quantize_x fused into its producer (the first of the follow-ups after the path itself) ------------------------
+ * The reference's graphs run norm -> quantize_x -> matmul and activation -> quantize_x -> down projection as
+ * separate kernels (models/qwen35_decode.cu:148-149 and 215-218).  These two entries do producer and quantizer in
+ * one kernel and give the SAME xq / xs / xsum, bit for bit, as the reference's two-kernel sequence:
+ *   w4a8_rmsnorm_quantize_x_q8 = launch_rmsnorm (variant 0, y = x*inv*W, kernels/rmsnorm.cuh:8-25),
+ *     launch_rmsnorm_zc (variant 1, y = x*inv*(1+W), :30-47) or launch_rmsnorm_noscale (variant 2, :50-67)
+ *     followed by launch_quantize_x_q8; inv = rsqrtf(mean(x^2) + eps) with the reference's reduction order.
+ *   w4a8_glu_quantize_x_q8 = launch_swiglu (act 0, kernels/swiglu.cuh:5-14) or launch_geglu (act 1, :19-33)
+ *     followed by launch_quantize_x_q8.
+ * Y, if not NULL, also receives the fp32 intermediate [S, IN] (for a consumer that is not quantized).  X, W, G, U, Y
+ * must be 16-byte aligned; IN a multiple of 32. */
+int w4a8_rmsnorm_quantize_x_q8(const float *X, const float *W, float eps, int variant, float *Y, int8_t *xq,
+                               float *xs, int32_t *xsum, int IN, int S, void *stream);
+int w4a8_glu_quantize_x_q8(const float *G, const float *U, int act, float *Y, int8_t *xq, float *xs,
+                           int32_t *xsum, int IN, int S, void *stream);
 
 /* ---- a4-a8: decode GEMV family (S = 1..16 rows; any S >= 1 is accepted) --------------------------
  * Replaces launch_gemv_w4a8 / _mlp<U> / _mlp_auto / _g4 (kernels/gemv_w4a8.cuh:93,102,155,316; their

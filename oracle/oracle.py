@@ -80,6 +80,25 @@ def quantize_x_q8(X):
     return xq, xs, xsum
 
 
+def rmsnorm(X, W, eps, variant=0):
+    """RMSNorm in the reference's reduction order (variant 0: * W, 1: * (1 + W), 2: no scale); float32 [rows, hh]."""
+    X = np.ascontiguousarray(X, dtype=np.float32)
+    rows, hh = X.shape
+    Wc = np.ascontiguousarray(W if W is not None else np.zeros(hh), dtype=np.float32)
+    Y = np.empty_like(X)
+    lib().oracle_rmsnorm(_p(X), _p(Wc), _p(Y), rows, hh, ctypes.c_float(eps), variant)
+    return Y
+
+
+def glu(G, U, act=0):
+    """SwiGLU (act 0) or GeGLU (act 1) of float32 arrays of equal shape."""
+    G = np.ascontiguousarray(G, dtype=np.float32)
+    U = np.ascontiguousarray(U, dtype=np.float32)
+    Y = np.empty_like(G)
+    lib().oracle_glu(_p(G), _p(U), _p(Y), ctypes.c_long(G.size), act)
+    return Y
+
+
 def pack_q4(W, zero_scale=1.0):
     """W[OUT,IN] float32 -> (Wq uint8 [OUT,IN/2], sc float32 [OUT,IN/32]); RTN, scale = max|w|/7."""
     W = np.ascontiguousarray(W, dtype=np.float32)

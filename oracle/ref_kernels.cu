@@ -6,6 +6,8 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 #include "kernels/quantize_x.cuh"
+#include "kernels/rmsnorm.cuh"
+#include "kernels/swiglu.cuh"
 #include "kernels/gemv_w4a8.cuh"
 #include "kernels/gemm_batch.cuh"
 #include "kernels/gemm_mma.cuh"
@@ -54,4 +56,17 @@ REF_API int ref_gemm_mmq_raster_w4a8(const int8_t *X, const float *xs, const uin
 REF_API int ref_gemm_bm16_splitk(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw,
                                  float *Y, int M, int N, int K, int sd, void *st) {
     launch_gemm_bm16_splitk(X, xs, Wq, sw, Y, M, N, K, sd, (cudaStream_t)st); return ref_status();
+}
+
+// The producers of quantize_x in the graphs (models/qwen35_decode.cu:148-149, 215-218), for the fused entries' parity.
+REF_API int ref_rmsnorm(const float *X, const float *W, float *Y, int rows, int hh, float eps, int variant, void *st) {
+    if (variant == 0) launch_rmsnorm(X, W, Y, rows, hh, eps, (cudaStream_t)st);
+    else if (variant == 1) launch_rmsnorm_zc(X, W, Y, rows, hh, eps, (cudaStream_t)st);
+    else launch_rmsnorm_noscale(X, Y, rows, hh, eps, (cudaStream_t)st);
+    return ref_status();
+}
+REF_API int ref_glu(const float *g, const float *u, float *Y, long n, int act, void *st) {
+    if (act == 0) launch_swiglu(g, u, Y, (size_t)n, (cudaStream_t)st);
+    else launch_geglu(g, u, Y, (size_t)n, (cudaStream_t)st);
+    return ref_status();
 }

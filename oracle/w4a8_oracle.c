@@ -118,6 +118,48 @@ API void oracle_quantize_x_q8(const float *X, int8_t *xq, float *xs, int32_t *xs
     }
 }
 
+/* ---- producers of quantize_x in the graphs (for the fused entry points) ------------------------------
+ * RMSNorm in the order of kernels/rmsnorm.cuh:8-20 + kernels/reduce.cuh:6-24: 256 threads, thread t adds the
+ * squares of elements t, t+256, ... (fused multiply-add), a shfl_down tree per warp of 32 threads, then one
+ * more tree over the 8 warp sums; inv = 1/sqrt(ss/hh + eps).  The GPU uses its reciprocal-square-root
+ * approximation (rsqrtf), so this restatement is close (a few ulp), not bit-equal: the bitwise proof of the
+ * fused kernels is against the reference's own kernels on the GPU.  variant 0: y = x*inv*W, 1: y = x*inv*(1+W),
+ * 2: y = x*inv. */
+static float tree32(float *v) { /* lane 0's value after shfl_down by 16, 8, 4, 2, 1 (lanes past the end keep their own value) */
+    for (int o = 16; o > 0; o >>= 1)
+        for (int l = 0; l < 32; l++) v[l] = v[l] + (l + o < 32 ? v[l + o] : v[l]);
+    return v[0];
+}
+API void oracle_rmsnorm(const float *X, const float *W, float *Y, int rows, int hh, float eps, int variant) {
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; r++) {
+        const float *x = X + (size_t)r * hh;
+        float part[256], ws[32];
+        for (int t = 0; t < 256; t++) {
+            float ss = 0.0f;
+            for (int i = t; i < hh; i += 256) ss = fmaf(x[i], x[i], ss);
+            part[t] = ss;
+        }
+        for (int w = 0; w < 32; w++) ws[w] = 0.0f;
+        for (int w = 0; w < 8; w++) ws[w] = tree32(part + 32 * w);
+        const float ss = tree32(ws);
+        const float inv = 1.0f / sqrtf(ss / (float)hh + eps);
+        for (int i = 0; i < hh; i++) {
+            const float xi = x[i] * inv;
+            Y[(size_t)r * hh + i] = variant == 0 ? xi * W[i] : (variant == 1 ? xi * (1.0f + W[i]) : xi);
+        }
+    }
+}
+/* SwiGLU (act 0, kernels/swiglu.cuh:5-8) and GeGLU (act 1, :19-27); the C library's expf / tanhf stand for the GPU's. */
+API void oracle_glu(const float *g, const float *u, float *Y, long n, int act) {
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < n; i++) {
+        const float x = g[i];
+        if (act == 0) { const float s = x / (1.0f + expf(-x)); Y[i] = s * u[i]; }
+        else { const float t = tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)); Y[i] = 0.5f * x * (1.0f + t) * u[i]; }
+    }
+}
+
 /* ---- weight producers ----------------------------------------------------------------------- */
 /* Round-to-nearest int4 packer.  zero_scale = 1.0f restates tests/test_w4a8.cu:19-27
  * (lrintf = round half to even); zero_scale = 1e-8f restates tools/extract_weights.py:124-140

@@ -168,3 +168,23 @@ def test_moe_oracle_is_dense_product_per_expert(oracle):
         t = slot // topk
         ref = oracle.gemm_mmq_w4a8(xq[t:t + 1], xs[t:t + 1], Wq[e * N:(e + 1) * N], sw[e * N:(e + 1) * N])
         assert np.array_equal(Y[slot], ref[0])
+
+
+def test_oracle_rmsnorm_and_glu_against_float64(oracle):
+    """The producers restated for the fused quantize entries: the reference's formulas (kernels/rmsnorm.cuh:5,28,50,
+    kernels/swiglu.cuh:4,17) evaluated in float64 agree with the fp32 restatement to fp32 rounding."""
+    rng = np.random.default_rng(3)
+    X = rng.normal(0, 2, size=(4, 5120)).astype(np.float32)
+    W = rng.normal(0, 0.3, size=5120).astype(np.float32)
+    x64 = X.astype(np.float64)
+    inv = 1.0 / np.sqrt(np.mean(x64 * x64, axis=1, keepdims=True) + 1e-6)
+    for variant, want in ((0, x64 * inv * W), (1, x64 * inv * (1.0 + W.astype(np.float64))), (2, x64 * inv)):
+        got = oracle.rmsnorm(X, W, 1e-6, variant)
+        assert np.max(np.abs(got - want) / (np.abs(want) + 1e-6)) < 2e-6
+    G = rng.normal(0, 2, size=(3, 768)).astype(np.float32)
+    U = rng.normal(0, 1, size=(3, 768)).astype(np.float32)
+    g64, u64 = G.astype(np.float64), U.astype(np.float64)
+    silu = g64 / (1.0 + np.exp(-g64)) * u64
+    gelu = 0.5 * g64 * (1.0 + np.tanh(0.7978845608028654 * (g64 + 0.044715 * g64 ** 3))) * u64
+    assert np.max(np.abs(oracle.glu(G, U, 0) - silu)) < 2e-6 * np.max(np.abs(silu))
+    assert np.max(np.abs(oracle.glu(G, U, 1) - gelu)) < 2e-6 * np.max(np.abs(gelu))
