@@ -340,6 +340,21 @@ def run_ours(args):
         us_h = ms_h * 1e3 / args.steps
         extra["gemv_m1_fp16_scales"] = {"us": us_h, "gbps": gemv_bytes(1, N, K, 2) / (us_h * 1e-6) / 1e9}
         del sws16
+        # ---- gate + up against one quantized row: two launches, or one w4a8_gemv_multi launch -------------------------
+        Yg, Yu = torch.empty((1, N), dtype=torch.float32, device=dev), torch.empty((1, N), dtype=torch.float32, device=dev)
+
+        def two_launches(i, st):
+            w.launch_gemv_w4a8_sb(xq, xs, Wqs[(2 * i) % nbuf], sws[(2 * i) % nbuf], Yg, K, N, 1, 0, st)
+            w.launch_gemv_w4a8_sb(xq, xs, Wqs[(2 * i + 1) % nbuf], sws[(2 * i + 1) % nbuf], Yu, K, N, 1, 0, st)
+
+        def one_launch(i, st):
+            a, b = (2 * i) % nbuf, (2 * i + 1) % nbuf
+            w.gemv_multi(xq, xs, [Wqs[a], Wqs[b]], [sws[a], sws[b]], [Yg, Yu], [N, N], K, 1, 0, st)
+        ns = max(20, args.steps // 2)
+        us_two = time_steps(two_launches, ns, 3, graph=True) * 1e3 / ns
+        us_one = time_steps(one_launch, ns, 3, graph=True) * 1e3 / ns
+        extra["gate_up_pair_m1"] = {"us_two_launches": us_two, "us_one_launch": us_one,
+                                    "gbps_one_launch": 2 * gemv_bytes(1, N, K) / (us_one * 1e-6) / 1e9}
         # ---- an lm_head-sized matrix (vocabulary 151936 x K=5120, 487 MB): auto policy streams it with bulk copies ----
         Nv = 151936
         vq = [torch.randint(0, 256, (Nv, K // 2), dtype=torch.uint8, device=dev, generator=g) for _ in range(2)]

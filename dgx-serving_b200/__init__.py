@@ -45,6 +45,7 @@ _SIGNATURES = {
     "w4a8_rmsnorm_quantize_x_q8": (_I, [_P, _P, ctypes.c_float, _I, _P, _P, _P, _P, _I, _I, _P]),
     "w4a8_glu_quantize_x_q8": (_I, [_P, _P, _I, _P, _P, _P, _P, _I, _I, _P]),
     "w4a8_gemv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "w4a8_gemv_multi": (_I, [_P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _P]),
     "w4a8_gemm": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "w4a8_gemm_splitk_workspace_bytes": (_Z, [_I, _I, _I, _I]),
     "w4a8_gemm_splitk": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _Z, _P]),
@@ -133,6 +134,15 @@ def launch_rmsnorm_quantize_x_q8(X, W, eps, variant, Y, xq, xs, xsum, IN, S, str
 def launch_glu_quantize_x_q8(G, U, act, Y, xq, xs, xsum, IN, S, stream=None):
     """SwiGLU (act 0) or GeGLU (act 1) of (G, U) and quantize_x in one kernel; Y (may be None) also gets the fp32 product."""
     _check(lib().w4a8_glu_quantize_x_q8(_ptr(G), _ptr(U), act, _ptr(Y), _ptr(xq), _ptr(xs), _ptr(xsum), IN, S, _stream(stream)))
+
+
+def gemv_multi(xq, xs, Wqs, sws, Ys, OUTs, IN, S, scale_dtype=0, stream=None):
+    """Several matrices (at most 4) against the same activation rows in one call; one launch for a single row on the
+    bulk-copy kernel.  Each Ys[i] equals launch_gemv_w4a8 of matrix i."""
+    n = len(Wqs)
+    arr = lambda xs_: (ctypes.c_void_p * n)(*[_ptr(t) for t in xs_])
+    outs = (ctypes.c_int * n)(*[int(o) for o in OUTs])
+    _check(lib().w4a8_gemv_multi(_ptr(xq), _ptr(xs), n, arr(Wqs), arr(sws), arr(Ys), outs, IN, S, scale_dtype, _stream(stream)))
 
 
 def launch_gemv_w4a8(xq, xs, xsum, Wq, sw, Y, IN, OUT, S, scale_dtype=0, stream=None):

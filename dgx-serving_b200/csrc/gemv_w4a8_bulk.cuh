@@ -48,11 +48,29 @@ struct Ring {
     __device__ void advance() { if (++stage == depth) { stage = 0; phase ^= 1u; } }
 };
 
+// Up to MAX_MATS matrices that share one activation row (gate + up, q + k + v): one launch, the CTAs of the grid
+// are divided between the matrices in proportion to their rows (cta0[i] = first CTA of matrix i).
+constexpr int MAX_MATS = 4;
+struct Mats {
+    const uint8_t *Wq[MAX_MATS];
+    const void *sw[MAX_MATS];
+    float *Y[MAX_MATS];
+    int OUT[MAX_MATS];
+    int cta0[MAX_MATS + 1];
+    int count;
+};
+
 // NG = groups per lane = ceil(K / 1024).
 template <int NG, typename ST>
 __global__ void __launch_bounds__(THREADS) gemv_w4a8_bulk_kernel(
-    const int8_t *__restrict__ xq, const float *__restrict__ xs, const uint8_t *__restrict__ Wq,
-    const ST *__restrict__ sw, float *__restrict__ Y, int IN, int OUT, int nstages) {
+    const int8_t *__restrict__ xq, const float *__restrict__ xs, const Mats mats, int IN, int nstages) {
+    int mi = 0;
+    while (mi + 1 < mats.count && (int)blockIdx.x >= mats.cta0[mi + 1]) mi++;
+    const uint8_t *__restrict__ Wq = mats.Wq[mi];
+    const ST *__restrict__ sw = static_cast<const ST *>(mats.sw[mi]);
+    float *__restrict__ Y = mats.Y[mi];
+    const int OUT = mats.OUT[mi];
+    const int cta = (int)blockIdx.x - mats.cta0[mi], nctas = mats.cta0[mi + 1] - mats.cta0[mi];
     extern __shared__ __align__(128) unsigned char smem[];
     const int nb = IN / QBLK;
     const uint32_t wrow = (uint32_t)IN / 2, srow = (uint32_t)nb * sizeof(ST);
@@ -65,7 +83,7 @@ __global__ void __launch_bounds__(THREADS) gemv_w4a8_bulk_kernel(
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // rows [r0, r1) of this CTA: a balanced contiguous partition of OUT over the grid
-    const int r0 = (int)(((long)OUT * blockIdx.x) / gridDim.x), r1 = (int)(((long)OUT * (blockIdx.x + 1)) / gridDim.x);
+    const int r0 = (int)(((long)OUT * cta) / nctas), r1 = (int)(((long)OUT * (cta + 1)) / nctas);
     const int nchunks = (r1 - r0 + ROWS - 1) / ROWS;
 
     if (tid == 0) {
@@ -195,8 +213,7 @@ inline bool plan_for(const void *xq, const void *Wq, const void *sw, int IN, int
 }
 
 template <int NG, typename ST>
-inline int launch_t(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int IN, int OUT,
-                    const Plan &p, cudaStream_t st) {
+inline int launch_t(const int8_t *xq, const float *xs, const Mats &mats_in, int IN, const Plan &p, cudaStream_t st) {
     auto kern = gemv_w4a8_bulk_kernel<NG, ST>;
     static size_t configured = 0;   // grow-only; single host thread per device (library convention)
     if (p.smem > configured) {
@@ -204,33 +221,55 @@ inline int launch_t(const int8_t *xq, const float *xs, const uint8_t *Wq, const 
         if (e != cudaSuccess) return cuda_fail(e, "gemv_bulk smem opt-in");
         configured = p.smem;
     }
-    const long want = (OUT + ROWS - 1) / ROWS, cap = (long)sm_count() * p.ctas_per_sm;
-    const dim3 grid((unsigned)(want < cap ? want : cap));
-    cudaError_t le = launch_pdl(kern, grid, dim3(THREADS), p.smem, st, xq, xs, Wq, sw, Y, IN, OUT, p.stages);
+    // grid: one persistent CTA per SM (p.ctas_per_sm of them), fewer when there are not enough rows; the CTAs are
+    // dealt to the matrices in proportion to their rows, at least one each
+    Mats m = mats_in;
+    long total = 0;
+    for (int i = 0; i < m.count; i++) total += m.OUT[i];
+    const long want = (total + ROWS - 1) / ROWS, cap = (long)sm_count() * p.ctas_per_sm;
+    long grid = want < cap ? want : cap;
+    if (grid < m.count) grid = m.count;
+    m.cta0[0] = 0;
+    long acc_rows = 0;
+    for (int i = 0; i < m.count; i++) {
+        acc_rows += m.OUT[i];
+        long end = (grid * acc_rows + total / 2) / total;
+        if (end < m.cta0[i] + 1) end = m.cta0[i] + 1;                       // at least one CTA per matrix
+        const long room = grid - (m.count - 1 - i);                        // leave one for each matrix still to come
+        if (end > room) end = room;
+        m.cta0[i + 1] = (int)end;
+    }
+    m.cta0[m.count] = (int)grid;
+    cudaError_t le = launch_pdl(kern, dim3((unsigned)grid), dim3(THREADS), p.smem, st, xq, xs, m, IN, p.stages);
     if (le != cudaSuccess) return cuda_fail(le, "gemv_w4a8_bulk launch");
     return launch_status("gemv_w4a8_bulk");
 }
 
 template <typename ST>
-inline int launch_st(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int IN, int OUT,
-                     const Plan &p, cudaStream_t st) {
+inline int launch_st(const int8_t *xq, const float *xs, const Mats &m, int IN, const Plan &p, cudaStream_t st) {
     switch (p.NG) {
-        case 1: return launch_t<1, ST>(xq, xs, Wq, sw, Y, IN, OUT, p, st);
-        case 2: return launch_t<2, ST>(xq, xs, Wq, sw, Y, IN, OUT, p, st);
-        case 3: return launch_t<3, ST>(xq, xs, Wq, sw, Y, IN, OUT, p, st);
-        case 4: return launch_t<4, ST>(xq, xs, Wq, sw, Y, IN, OUT, p, st);
-        case 5: return launch_t<5, ST>(xq, xs, Wq, sw, Y, IN, OUT, p, st);
-        case 6: return launch_t<6, ST>(xq, xs, Wq, sw, Y, IN, OUT, p, st);
-        case 7: return launch_t<7, ST>(xq, xs, Wq, sw, Y, IN, OUT, p, st);
-        case 8: return launch_t<8, ST>(xq, xs, Wq, sw, Y, IN, OUT, p, st);
+        case 1: return launch_t<1, ST>(xq, xs, m, IN, p, st);
+        case 2: return launch_t<2, ST>(xq, xs, m, IN, p, st);
+        case 3: return launch_t<3, ST>(xq, xs, m, IN, p, st);
+        case 4: return launch_t<4, ST>(xq, xs, m, IN, p, st);
+        case 5: return launch_t<5, ST>(xq, xs, m, IN, p, st);
+        case 6: return launch_t<6, ST>(xq, xs, m, IN, p, st);
+        case 7: return launch_t<7, ST>(xq, xs, m, IN, p, st);
+        case 8: return launch_t<8, ST>(xq, xs, m, IN, p, st);
     }
     return fail(W4A8_ERR_UNSUPPORTED, "gemv_bulk: no kernel for %d groups per lane", p.NG);
 }
 
+inline int launch_multi(const int8_t *xq, const float *xs, const Mats &m, int IN, int scale_dtype, const Plan &p, cudaStream_t st) {
+    if (scale_dtype == 1) return launch_st<__half>(xq, xs, m, IN, p, st);
+    return launch_st<float>(xq, xs, m, IN, p, st);
+}
+
 inline int launch(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int IN, int OUT,
                   int scale_dtype, const Plan &p, cudaStream_t st) {
-    if (scale_dtype == 1) return launch_st<__half>(xq, xs, Wq, (const __half *)sw, Y, IN, OUT, p, st);
-    return launch_st<float>(xq, xs, Wq, (const float *)sw, Y, IN, OUT, p, st);
+    Mats m = {};
+    m.Wq[0] = Wq; m.sw[0] = sw; m.Y[0] = Y; m.OUT[0] = OUT; m.count = 1;
+    return launch_multi(xq, xs, m, IN, scale_dtype, p, st);
 }
 
 }  // namespace gemv_bulk

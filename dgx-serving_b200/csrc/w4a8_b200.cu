@@ -263,6 +263,37 @@ W4A8_API int w4a8_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, con
     return gemv_dispatch(xq, xs, Wq, sw, Y, IN, OUT, S, scale_dtype, (cudaStream_t)stream, nullptr);
 }
 
+W4A8_API int w4a8_gemv_multi(const int8_t *xq, const float *xs, int count, const uint8_t *const *Wq, const void *const *sw,
+                             float *const *Y, const int *OUT, int IN, int S, int scale_dtype, void *stream) {
+    if (count < 0 || count > gemv_bulk::MAX_MATS) return fail(W4A8_ERR_ARG, "gemv_multi: count=%d (0..%d)", count, gemv_bulk::MAX_MATS);
+    if (count == 0 || S == 0) return W4A8_OK;
+    if (!Wq || !sw || !Y || !OUT) return fail(W4A8_ERR_ARG, "gemv_multi: null array argument");
+    // One launch when every matrix can take the bulk-copy stream (one row, the auto policy's conditions); else the
+    // matrices go one after the other through w4a8_gemv.  Either way each output equals w4a8_gemv's, bit for bit.
+    bool one = S == 1 && !current_out().peers && (gemv_policy() == 3 || (gemv_policy() == 0 && IN >= 2048));
+    gemv_bulk::Plan bp;
+    gemv_bulk::Mats m = {};
+    for (int i = 0; i < count && one; i++) {
+        if (OUT[i] <= 0 || !Wq[i] || !sw[i] || !Y[i] || !xq || !xs) { one = false; break; }
+        gemv_bulk::Plan pi;
+        if (!gemv_bulk::plan_for(xq, Wq[i], sw[i], IN, scale_dtype, &pi)) { one = false; break; }
+        bp = pi;
+        m.Wq[i] = Wq[i]; m.sw[i] = sw[i]; m.Y[i] = Y[i]; m.OUT[i] = OUT[i];
+    }
+    if (one) {
+        if (scale_dtype != 0 && scale_dtype != 1) return fail(W4A8_ERR_ARG, "gemv_multi: scale_dtype=%d", scale_dtype);
+        int rc = require_sm100();
+        if (rc != W4A8_OK) return rc;
+        m.count = count;
+        return gemv_bulk::launch_multi(xq, xs, m, IN, scale_dtype, bp, (cudaStream_t)stream);
+    }
+    for (int i = 0; i < count; i++) {
+        int rc = w4a8_gemv(xq, xs, Wq[i], sw[i], Y[i], IN, OUT[i], S, scale_dtype, stream);
+        if (rc != W4A8_OK) return rc;
+    }
+    return W4A8_OK;
+}
+
 W4A8_API int w4a8_gemm(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int M, int N, int K,
                        int scale_dtype, void *stream) {
     if (M < 0 || N < 0) return fail(W4A8_ERR_ARG, "gemm: negative size M=%d N=%d", M, N);

@@ -36,3 +36,15 @@ static inline void launch_gemv_w4a8_sb_g4(const int8_t *xq, const float *xs, con
                                           int IN, int OUT, int S, int scale_dtype = 0, cudaStream_t st = 0) {
     launch_gemv_w4a8_sb(xq, xs, Wq, sw, Y, IN, OUT, S, scale_dtype, st);
 }
+
+// Two matrices against one quantized input (gate + up, k + v) in one call: one kernel launch for a single decode row
+// (no counterpart in the reference; same bits as two launch_gemv_w4a8 calls).
+static inline void launch_gemv_w4a8_pair(const int8_t *xq, const float *xs, const uint8_t *Wq1, const void *sc1, float *Y1, int OUT1,
+                                         const uint8_t *Wq2, const void *sc2, float *Y2, int OUT2, int IN, int S, int scale_dtype = 0,
+                                         cudaStream_t st = 0) {
+    const uint8_t *wq[2] = {Wq1, Wq2};
+    const void *sc[2] = {sc1, sc2};
+    float *y[2] = {Y1, Y2};
+    const int out[2] = {OUT1, OUT2};
+    w4a8_shim_check(w4a8_gemv_multi(xq, xs, 2, wq, sc, y, out, IN, S, scale_dtype, (void *)st), "gemv_w4a8_pair");
+}

@@ -107,6 +107,15 @@ int w4a8_glu_quantize_x_q8(const float *G, const float *U, int act, float *Y, in
 int w4a8_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y,
               int IN, int OUT, int S, int scale_dtype, void *stream);
 
+/* Several matrices against the SAME activation rows in one call (gate + up, q + k + v: the pairs that share one
+ * quantized input in the graphs, models/qwen35_decode.cu:215 "n2 quantized once, shared by gate/up", G4_QUANT_SHARE in
+ * models/gemma4_decode.cu:110-112).  Y[i][S, OUT[i]] = w4a8_gemv(xq, xs, Wq[i], sw[i]) for i < count <= 4, bit for bit.
+ * A single row whose matrices all qualify for the bulk-copy streaming kernel goes out as ONE kernel launch with the
+ * SMs divided between the matrices in proportion to their rows; anything else is the same as `count` calls. */
+int w4a8_gemv_multi(const int8_t *xq, const float *xs, int count, const uint8_t *const *Wq,
+                    const void *const *sw, float *const *Y, const int *OUT, int IN, int S, int scale_dtype,
+                    void *stream);
+
 /* ---- a9-a12: prefill / verify GEMM family ---------------------------------------------------------
  * Replaces launch_gemm_mmq_w4a8 / _kt<KT> / _auto, launch_gemm_mmq_tmpl<...>
  * (kernels/gemm_mmq.cuh:222-233, gemm_mmq_tmpl.cuh:100-119), launch_gemm_mmq_raster_w4a8

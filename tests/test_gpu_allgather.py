@@ -21,9 +21,11 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("S,N,K", [(1, 520, 512), (5, 520, 512), (16, 1000, 1024), (20, 264, 256), (3, 37, 96)])
-def test_fused_allgather_two_ranks_emulated(w4a8, oracle, cuda, S, N, K):
-    world = 2
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("S,N,K", [(1, 520, 512), (5, 520, 512), (16, 1000, 1024), (20, 264, 256), (3, 37, 96), (1, 1000, 2048)])
+def test_fused_allgather_ranks_emulated(w4a8, oracle, cuda, S, N, K, world):
+    """`world` ranks emulated on one GPU: their kernels run one after the other over `world` arenas (never two waiting
+    kernels at once), then every rank's wait finds all flags set."""
     xq, xs, Wq, sw = make_case(oracle, S, N, K, seed=31 + S + N)
     xq_d, xs_d = to_dev(xq, cuda), to_dev(xs, cuda)
     ybytes = S * N * 4

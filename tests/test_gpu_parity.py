@@ -364,3 +364,28 @@ def test_config5_moe_shapes(w4a8, oracle, cuda):
                       tokens * topk, topk, per_slot, N, K, E)
         torch.cuda.synchronize()
         assert rel_err(Y.cpu().numpy(), oracle.moe_w4a8(xq, xs, Wq, sw, idx, topk, per_slot, N, K)) < REL_TOL
+
+
+# ---- several matrices against one quantized input (gate + up, q + k + v) --------------------------------------
+@pytest.mark.parametrize("scale_dtype", [0, 1])
+@pytest.mark.parametrize("S,K,OUTS", [(1, 5120, (1000, 1000)), (1, 2048, (40, 3000, 7)), (1, 4096, (512, 256, 256, 77)),
+                                      (1, 512, (100, 60)), (5, 2048, (300, 200)), (1, 5120, (17408,))])
+def test_gemv_multi_equals_separate_calls(w4a8, oracle, cuda, S, K, OUTS, scale_dtype):
+    """w4a8_gemv_multi (one launch on the bulk-copy kernel for a single row of 2048..8192 elements; else one call per
+    matrix) gives each matrix the bits of its own w4a8_gemv call, and those are the documented order."""
+    mats = [make_case(oracle, S, n, K, seed=4000 + n + i, scale_dtype=scale_dtype) for i, n in enumerate(OUTS)]
+    xq, xs = mats[0][0], mats[0][1]
+    xq_d, xs_d = to_dev(xq, cuda), to_dev(xs, cuda)
+    Wq_d = [to_dev(m[2], cuda) for m in mats]
+    sw_d = [to_dev(m[3], cuda) for m in mats]
+    Ys = [torch.full((S + 1, n), float("nan"), dtype=torch.float32, device=cuda) for n in OUTS]     # last row: canary
+    w4a8.gemv_multi(xq_d, xs_d, Wq_d, sw_d, Ys, OUTS, K, S, scale_dtype)
+    w4a8.device_status()
+    for i, n in enumerate(OUTS):
+        Y1 = torch.empty((S, n), dtype=torch.float32, device=cuda)
+        w4a8.launch_gemv_w4a8_sb(xq_d, xs_d, Wq_d[i], sw_d[i], Y1, K, n, S, scale_dtype)
+        torch.cuda.synchronize()
+        y = Ys[i].cpu().numpy()
+        assert np.all(np.isnan(y[S]))
+        assert np.array_equal(y[:S].view(np.uint32), Y1.cpu().numpy().view(np.uint32))
+        assert np.array_equal(y[:S].view(np.uint32), gemv_expected(oracle, xq, xs, mats[i][2], mats[i][3]).view(np.uint32))
