@@ -14,7 +14,7 @@
 // measured best; two smaller CTAs per SM, or rings deeper than 4 stages, were slower.
 //
 // Preconditions (else the caller uses another kernel): S = 1, K % 128 = 0 (K % 256 = 0 with fp16 scales: scale rows
-// are multiples of 16 bytes), K <= 8192, Wq and sw 16-byte aligned.  No peer-store epilogue and no expert grouping.
+// are multiples of 16 bytes), K <= 8192, Wq and sw 16-byte aligned.  No expert grouping.
 #pragma once
 #include "common.cuh"
 #include "ptx_sm100.cuh"
@@ -61,9 +61,10 @@ struct Mats {
 };
 
 // NG = groups per lane = ceil(K / 1024).
-template <int NG, typename ST>
+// PEER: outputs go to every rank's arena and the last CTA publishes the step's epoch (peer_allgather.cuh); single matrix.
+template <int NG, typename ST, bool PEER>
 __global__ void __launch_bounds__(THREADS) gemv_w4a8_bulk_kernel(
-    const int8_t *__restrict__ xq, const float *__restrict__ xs, const Mats mats, int IN, int nstages) {
+    const int8_t *__restrict__ xq, const float *__restrict__ xs, const Mats mats, int IN, int nstages, OutArgs oa) {
     int mi = 0;
     while (mi + 1 < mats.count && (int)blockIdx.x >= mats.cta0[mi + 1]) mi++;
     const uint8_t *__restrict__ Wq = mats.Wq[mi];
@@ -180,7 +181,7 @@ __global__ void __launch_bounds__(THREADS) gemv_w4a8_bulk_kernel(
                 if (lane == 0) {
 #pragma unroll
                     for (int i = 0; i < RPW; i++)
-                        if (row + CW * i < r1) Y[row + CW * i] = acc[i];
+                        if (row + CW * i < r1) store_out<PEER>(Y, oa, OUT, 0, row + CW * i, acc[i]);
                 }
             }
             __syncwarp();
@@ -188,6 +189,7 @@ __global__ void __launch_bounds__(THREADS) gemv_w4a8_bulk_kernel(
             r.advance();
         }
     }
+    publish_out<PEER>(oa, lane == 0 && warp < CW);
 }
 
 struct Plan { int NG, stages, ctas_per_sm; size_t smem; };
@@ -212,9 +214,9 @@ inline bool plan_for(const void *xq, const void *Wq, const void *sw, int IN, int
     return true;
 }
 
-template <int NG, typename ST>
-inline int launch_t(const int8_t *xq, const float *xs, const Mats &mats_in, int IN, const Plan &p, cudaStream_t st) {
-    auto kern = gemv_w4a8_bulk_kernel<NG, ST>;
+template <int NG, typename ST, bool PEER>
+inline int launch_p(const int8_t *xq, const float *xs, const Mats &mats_in, int IN, const Plan &p, cudaStream_t st) {
+    auto kern = gemv_w4a8_bulk_kernel<NG, ST, PEER>;
     static size_t configured = 0;   // grow-only; single host thread per device (library convention)
     if (p.smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
@@ -240,9 +242,15 @@ inline int launch_t(const int8_t *xq, const float *xs, const Mats &mats_in, int 
         m.cta0[i + 1] = (int)end;
     }
     m.cta0[m.count] = (int)grid;
-    cudaError_t le = launch_pdl(kern, dim3((unsigned)grid), dim3(THREADS), p.smem, st, xq, xs, m, IN, p.stages);
+    cudaError_t le = launch_pdl(kern, dim3((unsigned)grid), dim3(THREADS), p.smem, st, xq, xs, m, IN, p.stages, current_out());
     if (le != cudaSuccess) return cuda_fail(le, "gemv_w4a8_bulk launch");
     return launch_status("gemv_w4a8_bulk");
+}
+
+template <int NG, typename ST>
+inline int launch_t(const int8_t *xq, const float *xs, const Mats &m, int IN, const Plan &p, cudaStream_t st) {
+    if (current_out().peers) return launch_p<NG, ST, true>(xq, xs, m, IN, p, st);
+    return launch_p<NG, ST, false>(xq, xs, m, IN, p, st);
 }
 
 template <typename ST>

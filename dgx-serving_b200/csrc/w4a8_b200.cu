@@ -182,7 +182,7 @@ static int gemv_dispatch(const int8_t *xq, const float *xs, const uint8_t *Wq, c
                          int scale_dtype, cudaStream_t st, int *count_only) {
     // One row: the bulk-copy stream (same fp32 order as the dp4a kernel, so the choice never changes a result for fp32
     // scales) is the faster kernel from rows of 2048 elements up; shorter rows make its copies too small.
-    if (S == 1 && !current_out().peers && (gemv_policy() == 3 || (gemv_policy() == 0 && IN >= 2048))) {
+    if (S == 1 && (gemv_policy() == 3 || (gemv_policy() == 0 && IN >= 2048))) {
         gemv_bulk::Plan bp;
         if (gemv_bulk::plan_for(xq, Wq, sw, IN, scale_dtype, &bp)) {
             if (count_only) { *count_only = 1; return W4A8_OK; }
