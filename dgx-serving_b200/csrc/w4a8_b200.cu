@@ -181,8 +181,10 @@ static bool gemv_use_mma(int S, int scale_dtype) {
 static int gemv_dispatch(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int IN, int OUT, int S,
                          int scale_dtype, cudaStream_t st, int *count_only) {
     // One row: the bulk-copy stream (same fp32 order as the dp4a kernel, so the choice never changes a result for fp32
-    // scales) is the faster kernel from rows of 2048 elements up; shorter rows make its copies too small.
-    if (S == 1 && (gemv_policy() == 3 || (gemv_policy() == 0 && IN >= 2048))) {
+    // scales) is the faster kernel from rows of 2048 elements up; shorter rows make its copies too small.  With the
+    // peer-store epilogue (a rank's slice of an N-sharded matrix: few rows per SM) the dp4a kernel's smaller fixed
+    // cost wins (2 GPUs, M=1: 20.8 against 23.5 us per step), so auto keeps it there; policy 3 forces the bulk kernel.
+    if (S == 1 && (gemv_policy() == 3 || (gemv_policy() == 0 && IN >= 2048 && !current_out().peers))) {
         gemv_bulk::Plan bp;
         if (gemv_bulk::plan_for(xq, Wq, sw, IN, scale_dtype, &bp)) {
             if (count_only) { *count_only = 1; return W4A8_OK; }
