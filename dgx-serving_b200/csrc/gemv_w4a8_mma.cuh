@@ -24,7 +24,10 @@
 namespace w4a8 {
 namespace gemv_mma {
 
-constexpr int WARPS = 8;
+#ifndef W4A8_MMA_WARPS
+#define W4A8_MMA_WARPS 8
+#endif
+constexpr int WARPS = W4A8_MMA_WARPS;
 #ifndef W4A8_GEMV_RELAY
 #define W4A8_GEMV_RELAY 1
 #endif
@@ -152,33 +155,68 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_w4a8_mma_kernel(
     // ---- stage the activations once per CTA -----------------------------------------------------------------
     // (only rows m < S are read; the rest of the 8*MH rows is zero.)  Two chunks per 128-bit load when xq is 16-byte
     // aligned, else the reference's 4-byte loads.
+    // Loads go out in batches (one piece of up to eight rows) before any of them is stored: the compiler cannot tell that the stores to shared
+    // memory do not alias the loads, so in a plain loop every load would wait for the store before it (with 8 rows
+    // of 5120 elements that serial chain was a quarter of the kernel's time).
     const bool x16 = (reinterpret_cast<uintptr_t>(xq) & 15) == 0;
-    for (int m = 0; m < S; m++) {
-        uint2 *dstrow = xqp + (size_t)m * pitch2;
-        if (x16) {
-            const uint4 *src = reinterpret_cast<const uint4 *>(xq + (size_t)m * IN);
-            for (int c2 = tid; c2 < IN / 16; c2 += WARPS * 32) {          // chunks 2*c2 and 2*c2 + 1
-                const uint4 v = src[c2];
-                uint32_t e0, o0, e1, o1;
-                split_even_odd(v.x, v.y, e0, o0);
-                split_even_odd(v.z, v.w, e1, o1);
-                *reinterpret_cast<uint4 *>(dstrow + 2 * c2) = make_uint4(e0, o0, e1, o1);
+    constexpr int NT = WARPS * 32, UB = 8;
+    if (x16) {
+        const int n16 = IN / 16;                                           // 16-byte piece c2 = chunks 2*c2, 2*c2+1
+        for (int c2 = tid; c2 < n16; c2 += NT) {
+            for (int m0 = 0; m0 < S; m0 += UB) {                           // the same piece of up to UB rows at once
+                uint4 v[UB];
+#pragma unroll
+                for (int u = 0; u < UB; u++)
+                    if (m0 + u < S) v[u] = reinterpret_cast<const uint4 *>(xq + (size_t)(m0 + u) * IN)[c2];
+#pragma unroll
+                for (int u = 0; u < UB; u++) {
+                    if (m0 + u < S) {
+                        uint32_t e0, o0, e1, o1;
+                        split_even_odd(v[u].x, v[u].y, e0, o0);
+                        split_even_odd(v[u].z, v[u].w, e1, o1);
+                        *reinterpret_cast<uint4 *>(xqp + (size_t)(m0 + u) * pitch2 + 2 * c2) = make_uint4(e0, o0, e1, o1);
+                    }
+                }
             }
-        } else {
-            const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + (size_t)m * IN);
-            for (int c = tid; c < IN / 8; c += WARPS * 32) {              // 8-element chunk c = 4*b + t
-                uint32_t e, od;
-                split_even_odd(src[2 * c], src[2 * c + 1], e, od);
-                dstrow[c] = make_uint2(e, od);
+        }
+    } else {
+        const int n8 = IN / 8;                                             // 8-element chunk c = 4*b + t
+        for (int c = tid; c < n8; c += NT) {
+            for (int m0 = 0; m0 < S; m0 += UB) {
+                uint2 v[UB];
+#pragma unroll
+                for (int u = 0; u < UB; u++) {
+                    if (m0 + u < S) {
+                        const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + (size_t)(m0 + u) * IN);
+                        v[u] = make_uint2(src[2 * c], src[2 * c + 1]);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < UB; u++) {
+                    if (m0 + u < S) {
+                        uint32_t e, od;
+                        split_even_odd(v[u].x, v[u].y, e, od);
+                        xqp[(size_t)(m0 + u) * pitch2 + c] = make_uint2(e, od);
+                    }
+                }
             }
         }
     }
     __shared__ float4 relay_box[WARPS / 2][32];
     __shared__ unsigned int relay_flag[WARPS / 2];
     if (tid < WARPS / 2) relay_flag[tid] = 0u;
-    for (int i = tid; i < nb * 8 * MH; i += WARPS * 32) {
-        const int b = i / (8 * MH), m = i % (8 * MH);
-        sxs[i] = (m < S) ? xs[(size_t)m * nb + b] * 0.0625f : 0.f;   // exact 1/16: undoes the 16x of the expansion
+    for (int i0 = tid; i0 < nb * 8 * MH; i0 += NT * 4) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i = i0 + u * NT, b = i / (8 * MH), m = i % (8 * MH);
+            v[u] = (i < nb * 8 * MH && m < S) ? xs[(size_t)m * nb + b] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i = i0 + u * NT;
+            if (i < nb * 8 * MH) sxs[i] = v[u] * 0.0625f;               // exact 1/16: undoes the 16x of the expansion
+        }
     }
     __syncthreads();
 
