@@ -34,7 +34,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 K_DIM, N_DIM = 5120, 17408
 L2_BYTES = 126 * 1024 * 1024
 NCU_TRAFFIC = {  # dram__bytes_read.sum + dram__bytes_write.sum per launch, from profiles/ (one ncu capture each)
-    "gemv_m1": 55.74e6,   # profiles/gemv_w4a8_bulk_m1_k5120_n17408.md (55.733 MB read + 0.005 MB written)
+    "gemv_m1": 55.77e6,   # profiles/gemv_w4a8_dp4a_m1_k5120_n17408.md (dram read + written bytes of one launch)
 }
 
 
@@ -478,7 +478,7 @@ def run_ours(args):
                        "launch": "CUDA graph of %d steps" % args.steps},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": NCU_TRAFFIC["gemv_m1"] if world == 1 else None, "peak_kind": "of " + peak_kind,
-                         "kernel": "gemv_w4a8_bulk_kernel (w4a8_gemv, M=1), rank-local slice of %d rows" % rows, "us_per_launch": per_launch_us,
+                         "kernel": "gemv_w4a8_dp4a_kernel (w4a8_gemv, M=1, auto policy), rank-local slice of %d rows" % rows, "us_per_launch": per_launch_us,
                          "algorithmic_bytes_per_launch": gemv_bytes(1, rows, K), "frac_of_nominal_8tbs": achieved / 8000.0},
             "cpu_baseline": cpu_baseline,
             "e2e": {"value": e2e_gbps, "unit": "GB/s", "h2d_bytes_per_step": K * 4, "d2h_bytes_per_step": rows * 4,

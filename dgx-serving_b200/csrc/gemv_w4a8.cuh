@@ -143,19 +143,39 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_dp4a_kernel(
     // Stage activations: one task = one 8-element chunk (two 4-byte loads, like the reference's x0/x1).
 #pragma unroll
     for (int m = 0; m < MT; m++) {
-        for (int c = tid; c < IN / 8; c += GEMV_WARPS * 32) {
-            uint32_t x0 = 0, x1 = 0;
-            if (m < S) {
-                const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + (size_t)m * IN + 8 * c);
-                x0 = src[0]; x1 = src[1];
+        // loads in batches of UB ahead of the stores: the compiler cannot tell that the shared-memory stores do not
+        // alias the loads, and a long row would otherwise pay one L2 round trip per chunk
+        constexpr int NT = GEMV_WARPS * 32, UB = 8;
+        for (int c0 = tid; c0 < IN / 8; c0 += NT * UB) {
+            uint32_t x0[UB], x1[UB];
+#pragma unroll
+            for (int u = 0; u < UB; u++) {
+                const int c = c0 + u * NT;
+                x0[u] = 0; x1[u] = 0;
+                if (m < S && c < IN / 8) {
+                    const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + (size_t)m * IN + 8 * c);
+                    x0[u] = src[0]; x1[u] = src[1];
+                }
             }
-            uint32_t e, od;
-            split_even_odd(x0, x1, e, od);
-            const int b = c >> 2, w = c & 3;
-            uint2 *dst = reinterpret_cast<uint2 *>((w < 2 ? plane0 : plane1) + (size_t)m * nb + b) + (w & 1);
-            *dst = make_uint2(e, od);
+#pragma unroll
+            for (int u = 0; u < UB; u++) {
+                const int c = c0 + u * NT;
+                if (c < IN / 8) {
+                    uint32_t e, od;
+                    split_even_odd(x0[u], x1[u], e, od);
+                    const int b = c >> 2, w = c & 3;
+                    uint2 *dst = reinterpret_cast<uint2 *>((w < 2 ? plane0 : plane1) + (size_t)m * nb + b) + (w & 1);
+                    *dst = make_uint2(e, od);
+                }
+            }
         }
-        for (int b = tid; b < nb; b += GEMV_WARPS * 32) sxs[m * nb + b] = (m < S) ? xs[(size_t)m * nb + b] : 0.f;
+        for (int b0 = tid; b0 < nb; b0 += NT * 4) {
+            float v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) { const int b = b0 + u * NT; v[u] = (m < S && b < nb) ? xs[(size_t)m * nb + b] : 0.f; }
+#pragma unroll
+            for (int u = 0; u < 4; u++) { const int b = b0 + u * NT; if (b < nb) sxs[m * nb + b] = v[u]; }
+        }
     }
     __syncthreads();
 

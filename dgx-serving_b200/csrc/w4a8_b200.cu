@@ -180,11 +180,15 @@ static bool gemv_use_mma(int S, int scale_dtype) {
 // launched, *count_only receives the number of kernel launches the call would make.
 static int gemv_dispatch(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int IN, int OUT, int S,
                          int scale_dtype, cudaStream_t st, int *count_only) {
-    // One row: the bulk-copy stream (same fp32 order as the dp4a kernel, so the choice never changes a result for fp32
-    // scales) is the faster kernel from rows of 2048 elements up; shorter rows make its copies too small.  With the
-    // peer-store epilogue (a rank's slice of an N-sharded matrix: few rows per SM) the dp4a kernel's smaller fixed
-    // cost wins (2 GPUs, M=1: 20.8 against 23.5 us per step), so auto keeps it there; policy 3 forces the bulk kernel.
-    if (S == 1 && (gemv_policy() == 3 || (gemv_policy() == 0 && IN >= 2048 && !current_out().peers))) {
+    // One row.  The bulk-copy stream and the dp4a kernel give the same bits; which is faster depends on the matrix: the
+    // bulk-copy stream has the higher steady rate (6.5-6.9 TB/s against 6.0) and the larger fixed cost per launch
+    // (about 2.7 against 1.1 us), so auto takes it from 96 MB of weights up (K=5120: N >= 30k, an lm_head) and for
+    // fp16 scales, whose two-byte loads slow the dp4a kernel down; a 56 MB MLP matrix stays on the dp4a kernel
+    // (10.7 against 11.0 us).  Rows shorter than 2048 elements make the bulk copies too small.  With the peer-store
+    // epilogue (a rank's slice of an N-sharded matrix) the dp4a kernel's smaller fixed cost wins as well.
+    const size_t wbytes = (size_t)OUT * ((size_t)IN / 2 + (size_t)(IN / QBLK) * (scale_dtype == 1 ? 2 : 4));
+    const bool bulk_auto = IN >= 2048 && !current_out().peers && (scale_dtype == 1 || wbytes >= ((size_t)96 << 20));
+    if (S == 1 && (gemv_policy() == 3 || (gemv_policy() == 0 && bulk_auto))) {
         gemv_bulk::Plan bp;
         if (gemv_bulk::plan_for(xq, Wq, sw, IN, scale_dtype, &bp)) {
             if (count_only) { *count_only = 1; return W4A8_OK; }

@@ -86,10 +86,10 @@ GEMV_SHAPES = [(1024, 256, 1), (1024, 2048, 1), (3584, 1024, 1), (1024, 4096, 5)
 
 
 def gemv_expected(oracle, xq, xs, Wq, sw, policy=0):
-    """The documented fp32 order of w4a8_gemv.  Auto: a single row of 2048..8192 elements goes through the bulk-copy
-    stream, which keeps the dp4a kernel's chain order; the tensor-path kernel (MMQ order) serves S >= 2, and S = 1 with
-    fp16 scales outside that range, when K % 256 == 0; the dp4a kernel everything else.  Policy 1: dp4a for every S;
-    2: tensor path for every S it supports; 3: bulk-copy stream for every single row it supports, dp4a otherwise."""
+    """The documented fp32 order of w4a8_gemv.  A single row goes through the dp4a kernel or the bulk-copy stream, which
+    share one chain order (auto picks by size and scale type; policy 3 forces the bulk-copy stream, 1 the dp4a kernel);
+    the tensor-path kernel (MMQ order) serves S >= 2, and S = 1 with fp16 scales when the bulk-copy stream does not
+    take the row (K outside 2048..8192), when K % 256 == 0; the dp4a kernel everything else."""
     S, K = xq.shape
     fp16 = sw.dtype == np.float16
     bulk = S == 1 and K % (256 if fp16 else 128) == 0 and K <= 8192 and (policy == 3 or (policy == 0 and K >= 2048))
