@@ -57,11 +57,12 @@ int w4a8_device_status(uint32_t *detail);
 
 /* Run-time policy switches (the reference keeps such switches in runtime/knobs.h, read from the environment;
  * the same names are read here once: W4A8_GEMV = dp4a | mma | bulk, W4A8_PDL = 0 | 1).
- *   "gemv_kernel": 0 = auto (default): one activation row of 2048..8192 elements uses the bulk-copy streaming kernel,
- *                  2..16 rows (and one row with fp16 scales outside that range) the tensor-path kernel, everything
- *                  else the dp4a streaming kernel; 1 = dp4a kernel for every S; 2 = tensor-path kernel for every S it
- *                  supports (K % 256 == 0, 16-byte aligned Wq and sw); 3 = bulk-copy kernel for every single row it
- *                  supports (K % 128 == 0, K <= 8192, 16-byte aligned Wq and sw), dp4a otherwise.
+ *   "gemv_kernel": 0 = auto (default): 2..16 activation rows use the tensor-path kernel; one row uses the dp4a
+ *                  streaming kernel, or the bulk-copy streaming kernel when the row has 2048..8192 elements and the
+ *                  matrix is large (96 MB of weights or more) or its scales are fp16; one row with fp16 scales outside
+ *                  that range uses the tensor-path kernel.  1 = dp4a kernel for every S; 2 = tensor-path kernel for
+ *                  every S it supports (K % 256 == 0, 16-byte aligned Wq and sw); 3 = bulk-copy kernel for every
+ *                  single row it supports (K % 128 == 0, K <= 8192, 16-byte aligned Wq and sw), dp4a otherwise.
  *                  The tensor-path kernel evaluates fp32 in the MMQ order (bit-identical to w4a8_gemm and to the
  *                  reference's MMQ kernels); the dp4a and bulk-copy kernels share one fixed order of their own (within
  *                  1e-5).  Policy 2 therefore makes a row's bits independent of S for all S >= 1 (the reference's
