@@ -309,6 +309,43 @@ def run_ours(args):
             ms_m, gb_m, _ = gemv_case(M, max(20, args.steps // 2), 3)
             sw_[str(M)] = {"us": ms_m * 1e3 / max(20, args.steps // 2), "gbps": gb_m}
         extra["gemv_sweep_fused_allgather"] = sw_
+        # ---- N-sharded prefill GEMM M=2048: quantize_x + GEMM on the rank's rows; Y[M, N] complete on every rank either by
+        # peer stores from the GEMM epilogue + flag wait (w4a8_gemm_allgather) or by an NCCL all-gather of the slices ----------
+        Mg = 2048
+        Xh2, Xd2, xq2, xs2, xsum2 = make_x(Mg, outliers=True)
+        Yl2 = torch.empty((Mg, rows), dtype=torch.float32, device=dev)
+        gstride = (Mg * N * 4 + 255) // 256 * 256
+        garena = w.Arena(2 * gstride, rank, world)
+        ghandles = [None] * world
+        dist.all_gather_object(ghandles, garena.export_handle())
+        garena.connect_handles(ghandles)
+        dist.barrier()
+        gepoch = [0]
+
+        def gemm_fused(i, st):
+            gepoch[0] += 1
+            w.launch_quantize_x_q8(Xd2, xq2, xs2, xsum2, K, Mg, st)
+            garena.gemm_allgather(xq2, xs2, Wqs[i % nbuf], sws[i % nbuf], (gepoch[0] % 2) * gstride, Mg, rows, row0, N, K, 0, gepoch[0], st)
+            garena.wait(gepoch[0], 5000000, st)
+
+        def gemm_nccl(i, st):
+            w.linear(Xd2, xq2, xs2, xsum2, Wqs[i % nbuf], sws[i % nbuf], Yl2, Mg, rows, K, 0, 0, st)
+            sharded.all_gather_columns(Yl2, plan)
+
+        def gemm_local(i, st):
+            w.linear(Xd2, xq2, xs2, xsum2, Wqs[i % nbuf], sws[i % nbuf], Yl2, Mg, rows, K, 0, 0, st)
+        ms_gf = time_steps(gemm_fused, 5, 3, graph=False) / 5
+        w.device_status()
+        ms_g = time_steps(gemm_nccl, 5, 3, graph=False) / 5
+        ms_gl = time_steps(gemm_local, 5, 3, graph=False) / 5
+        w.device_status()
+        barrier()
+        garena.close()
+        tops = lambda ms_: 2.0 * Mg * N * K / (ms_ * 1e-3) / 1e12
+        extra["gemm_m2048_n_sharded"] = {"ms_per_step_fused_allgather": ms_gf, "int8_tops_whole_job_fused_allgather": tops(ms_gf),
+                                         "ms_per_step_nccl_allgather": ms_g, "int8_tops_whole_job_nccl_allgather": tops(ms_g),
+                                         "ms_rank_local_quantize_gemm": ms_gl, "int8_tops_without_allgather": tops(ms_gl)}
+        del Yl2
     if world == 1:
         # ---- sweep M = 2..16 on the same shape ------------------------------------------------------------
         sweep = {"1": {"us": per_launch_us, "gbps": achieved, "frac_of_measured_hbm": achieved / hbm_peak,

@@ -66,6 +66,7 @@ _SIGNATURES = {
     "w4a8_ipc_open": (_I, [ctypes.c_char_p, ctypes.POINTER(_P)]),
     "w4a8_ipc_close": (_I, [_P]),
     "w4a8_gemv_allgather": (_I, [_P, _P, _P, _P, _P, _Z, _I, _I, _I, _I, _I, _I, ctypes.c_uint32, _P]),
+    "w4a8_gemm_allgather": (_I, [_P, _P, _P, _P, _P, _Z, _I, _I, _I, _I, _I, _I, ctypes.c_uint32, _P]),
     "w4a8_allgather_wait": (_I, [_P, ctypes.c_uint32, _I, _P]),
     "w4a8_arena_advance_epoch": (_I, [_P, ctypes.c_uint32, _P]),
 }
@@ -282,6 +283,10 @@ class Arena:
 
     def gemv_allgather(self, xq, xs, Wq, sw, y_offset, IN, rows, row0, ldY, S, scale_dtype, epoch, stream=None):
         _check(lib().w4a8_gemv_allgather(_ptr(xq), _ptr(xs), _ptr(Wq), _ptr(sw), self.handle, y_offset, IN, rows, row0, ldY, S,
+                                         scale_dtype, epoch, _stream(stream)))
+
+    def gemm_allgather(self, X, xs, Wq, sw, y_offset, M, rows, row0, ldY, K, scale_dtype, epoch, stream=None):
+        _check(lib().w4a8_gemm_allgather(_ptr(X), _ptr(xs), _ptr(Wq), _ptr(sw), self.handle, y_offset, M, rows, row0, ldY, K,
                                          scale_dtype, epoch, _stream(stream)))
 
     def wait(self, epoch, timeout_us=1000000, stream=None):

@@ -27,6 +27,7 @@
 #include <cuda.h>
 #include "common.cuh"
 #include "ptx_sm100.cuh"
+#include "peer_allgather.cuh"
 
 namespace w4a8 {
 namespace gemm {
@@ -186,11 +187,14 @@ __device__ __forceinline__ Work decode_work(int w, int m_tiles, int num_tiles, i
     return k;
 }
 
-template <typename ST, bool DUMP, int EPI>
+// PEER (N-sharded weights, no split-K): every output tile is stored straight into EVERY rank's Y[M, ld] at its final
+// columns (oa.col0 + n: plain 16-byte peer stores over NVLink) and the last CTA publishes the step's epoch, so the
+// all-gather costs no extra pass over the outputs (peer_allgather.cuh).
+template <typename ST, bool DUMP, int EPI, bool PEER = false>
 __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
     const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
     const float *__restrict__ xs, const ST *__restrict__ sw, float *__restrict__ Y, int32_t *__restrict__ Dout,
-    int M, int N, int K, int nsplit, int gsplit) {
+    int M, int N, int K, int nsplit, int gsplit, const OutArgs oa) {
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t raw = ptx::smem_u32(smem_dyn);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -453,21 +457,26 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
             }
             if (!ok) break;
             if (!DUMP && ok && m < M) {
-                float *yrow = Y + (size_t)wk.split * ((size_t)M * N) + (size_t)m * N + n0 + col0;
                 const int nleft = N - (n0 + col0);
-                if (nleft >= EPI_COLS && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0)) {
+                const int targets = PEER ? oa.peers->world : 1;
+                for (int k = 0; k < targets; k++) {
+                    float *yrow = PEER ? reinterpret_cast<float *>(oa.peers->base[k] + oa.y_off) + (size_t)m * oa.ld + oa.col0 + n0 + col0
+                                       : Y + (size_t)wk.split * ((size_t)M * N) + (size_t)m * N + n0 + col0;
+                    if (nleft >= EPI_COLS && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0)) {
 #pragma unroll
-                    for (int j = 0; j < EPI_COLS; j += 4)
-                        *reinterpret_cast<float4 *>(yrow + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-                } else {
+                        for (int j = 0; j < EPI_COLS; j += 4)
+                            *reinterpret_cast<float4 *>(yrow + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < EPI_COLS; j++)
-                        if (j < nleft) yrow[j] = acc[j];
+                        for (int j = 0; j < EPI_COLS; j++)
+                            if (j < nleft) yrow[j] = acc[j];
+                    }
                 }
             }
         }
     }
 
+    publish_out<PEER>(oa, warp >= 2 + DEQ_WARPS);
     // ---------------- teardown ----------------
     ptx::tc_fence_before_sync();
     __syncthreads();
@@ -522,7 +531,7 @@ inline int make_tmap_u8(CUtensorMap *tm, const void *ptr, uint64_t row_bytes, ui
     return W4A8_OK;
 }
 
-template <typename ST, bool DUMP, int EPI>
+template <typename ST, bool DUMP, int EPI, bool PEER = false>
 inline int launch_tc_e(const int8_t *X, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int32_t *D,
                        int M, int N, int K, int nsplit, int gsplit, cudaStream_t st) {
     CUtensorMap tmA, tmB;
@@ -530,7 +539,7 @@ inline int launch_tc_e(const int8_t *X, const float *xs, const uint8_t *Wq, cons
     if (rc != W4A8_OK) return rc;
     rc = make_tmap_u8(&tmB, Wq, (uint64_t)K / 2, (uint64_t)N, KT / 2, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != W4A8_OK) return rc;
-    auto kern = gemm_w4a8_tc_kernel<ST, DUMP, EPI>;
+    auto kern = gemm_w4a8_tc_kernel<ST, DUMP, EPI, PEER>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -540,7 +549,7 @@ inline int launch_tc_e(const int8_t *X, const float *xs, const uint8_t *Wq, cons
     const long tiles = (long)((M + BM - 1) / BM) * ((N + BN - 1) / BN) * nsplit;
     const int sms = sm_count();
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, xs, sw, Y, D, M, N, K, nsplit, gsplit);
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, xs, sw, Y, D, M, N, K, nsplit, gsplit, PEER ? current_out() : OutArgs());
     return launch_status("gemm_w4a8_tc");
 }
 
@@ -558,6 +567,7 @@ inline int epi_variant() {
 template <typename ST, bool DUMP>
 inline int launch_tc_t(const int8_t *X, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int32_t *D,
                        int M, int N, int K, int nsplit, int gsplit, cudaStream_t st) {
+    if (!DUMP && current_out().peers) return launch_tc_e<ST, false, 2, true>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
     switch (DUMP ? 0 : epi_variant()) {
         case 1: return launch_tc_e<ST, DUMP, 1>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
         case 2: return launch_tc_e<ST, DUMP, 2>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);

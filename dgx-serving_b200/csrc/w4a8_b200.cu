@@ -708,6 +708,31 @@ W4A8_API int w4a8_gemv_allgather(const int8_t *xq, const float *xs, const uint8_
     return W4A8_OK;
 }
 
+W4A8_API int w4a8_gemm_allgather(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a, size_t y_offset,
+                                 int M, int rows, int row0, int ldY, int K, int scale_dtype, uint32_t epoch, void *stream) {
+    if (!a || !a->connected) return fail(W4A8_ERR_ARG, "gemm_allgather: arena not connected");
+    if (M < 0 || rows < 0 || row0 < 0 || ldY < row0 + rows) return fail(W4A8_ERR_ARG, "gemm_allgather: bad shape M=%d rows=%d row0=%d ldY=%d", M, rows, row0, ldY);
+    if (y_offset % 16 != 0 || y_offset + (size_t)M * ldY * sizeof(float) > a->bytes)
+        return fail(W4A8_ERR_ARG, "gemm_allgather: Y[%d x %d] at offset %zu does not fit the %zu-byte arena", M, ldY, y_offset, a->bytes);
+    if (K <= 0) return fail(W4A8_ERR_ARG, "gemm_allgather: K must be positive");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (M == 0 || rows == 0) {                       // nothing to compute: this rank still has to publish the step
+        allgather_publish_kernel<<<1, 32, 0, st>>>(a->desc_dev, epoch);
+        return launch_status("allgather_publish");
+    }
+    float *Ylocal = reinterpret_cast<float *>(a->base + y_offset);   // unused by the peer path; keeps the argument checks happy
+    int rc = check_common(X, xs, Wq, sw, Ylocal, K, scale_dtype, "gemm_allgather");
+    if (rc != W4A8_OK) return rc;
+    if (!aligned(X, 16) || !aligned(Wq, 16)) return fail(W4A8_ERR_ALIGN, "gemm_allgather: X and Wq must be 16-byte aligned (TMA)");
+    rc = require_sm100();
+    if (rc != W4A8_OK) return rc;
+    OutArgs &oa = current_out();
+    oa.peers = a->desc_dev; oa.y_off = y_offset; oa.ld = ldY; oa.col0 = row0; oa.epoch = epoch; oa.publish = 1;
+    rc = gemm::launch_tc(X, xs, Wq, sw, Ylocal, M, rows, K, scale_dtype, 1, K / QBLK, st);   // the int8 kernel carries the peer epilogue
+    oa = OutArgs();
+    return rc;
+}
+
 W4A8_API int w4a8_allgather_wait(w4a8_arena *a, uint32_t epoch, int timeout_us, void *stream) {
     if (!a || !a->connected) return fail(W4A8_ERR_ARG, "allgather_wait: arena not connected");
     if (timeout_us <= 0) timeout_us = 1000000;

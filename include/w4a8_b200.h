@@ -253,6 +253,12 @@ int w4a8_ipc_close(void *dev_ptr);
 int w4a8_gemv_allgather(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a,
                         size_t y_offset, int IN, int rows, int row0, int ldY, int S, int scale_dtype,
                         uint32_t epoch, void *stream);
+/* The same for the prefill / verify GEMM (M rows of activations, w4a8_gemm semantics on the rank's `rows` weight rows):
+ * every output tile goes straight to columns [row0, row0+rows) of Y[M, ldY] in every rank's arena with 16-byte peer
+ * stores, then the epoch is published; no split-K.  X and Wq 16-byte aligned as for w4a8_gemm. */
+int w4a8_gemm_allgather(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a,
+                        size_t y_offset, int M, int rows, int row0, int ldY, int K, int scale_dtype,
+                        uint32_t epoch, void *stream);
 int w4a8_allgather_wait(w4a8_arena *a, uint32_t epoch, int timeout_us, void *stream);
 /* The epoch a kernel publishes / waits for is `epoch` plus a per-arena base kept in device memory (initially 0).
  * This enqueues base += delta.  A CUDA graph that captured steps with epochs 1..n ends with

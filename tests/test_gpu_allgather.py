@@ -56,6 +56,40 @@ def test_fused_allgather_ranks_emulated(w4a8, oracle, cuda, S, N, K, world):
             a.close()
 
 
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("M,N,K,scale_dtype", [(130, 520, 512, 0), (17, 264, 256, 1), (300, 1000, 1024, 0), (64, 37 * 4, 96, 0)])
+def test_fused_gemm_allgather_ranks_emulated(w4a8, oracle, cuda, M, N, K, scale_dtype, world):
+    """The GEMM with the peer-store epilogue: `world` ranks emulated on one GPU, kernels one after the other; every
+    rank's arena ends up with the whole Y[M, N], bit-identical to w4a8_gemm on the unsharded matrix (MMQ order)."""
+    xq, xs, Wq, sw = make_case(oracle, M, N, K, seed=77 + M + N, scale_dtype=scale_dtype)
+    xq_d, xs_d = to_dev(xq, cuda), to_dev(xs, cuda)
+    ystride = (M * N * 4 + 255) // 256 * 256
+    arenas = [w4a8.Arena(2 * ystride, r, world) for r in range(world)]
+    try:
+        for a in arenas:
+            a.connect_pointers([b.base for b in arenas])
+        shards = []
+        for r in range(world):
+            row0, rows = w4a8.shard_rows(N, r, world)
+            shards.append((row0, rows, to_dev(Wq[row0:row0 + rows], cuda), to_dev(sw[row0:row0 + rows], cuda)))
+        expect = oracle.gemm_mmq_w4a8(xq, xs, Wq, sw)
+        for epoch in (1, 2):
+            off = (epoch % 2) * ystride
+            for r, a in enumerate(arenas):
+                row0, rows, Wq_r, sw_r = shards[r]
+                a.gemm_allgather(xq_d, xs_d, Wq_r, sw_r, off, M, rows, row0, N, K, scale_dtype, epoch)
+            for a in arenas:
+                a.wait(epoch, timeout_us=200000)
+            w4a8.device_status()
+            for a in arenas:
+                y = a.tensor(off, (M, N)).cpu().numpy()
+                assert np.array_equal(y.view(np.uint32), expect.view(np.uint32))
+                a.tensor(off, (M, N)).fill_(float("nan"))
+    finally:
+        for a in arenas:
+            a.close()
+
+
 def test_allgather_wait_gives_up_and_reports(w4a8, oracle, cuda):
     """Failure detection without a GPU fault: a flag that nothing sets makes the bounded wait run out."""
     arenas = [w4a8.Arena(4096, r, 2) for r in range(2)]
