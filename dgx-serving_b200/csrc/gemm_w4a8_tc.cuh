@@ -460,6 +460,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
                 const int nleft = N - (n0 + col0);
                 const int targets = PEER ? oa.peers->world : 1;
                 for (int k = 0; k < targets; k++) {
+                    if (PEER && oa.local_only && k != oa.peers->rank) continue;
                     float *yrow = PEER ? reinterpret_cast<float *>(oa.peers->base[k] + oa.y_off) + (size_t)m * oa.ld + oa.col0 + n0 + col0
                                        : Y + (size_t)wk.split * ((size_t)M * N) + (size_t)m * N + n0 + col0;
                     if (nleft >= EPI_COLS && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0)) {

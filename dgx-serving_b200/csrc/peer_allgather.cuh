@@ -29,6 +29,7 @@ struct OutArgs {                    // passed by value to the GEMV kernels; peer
     long ld = 0, col0 = 0;          // row pitch of the gathered Y (= total N) and this rank's first column (= row0)
     unsigned int epoch = 0;         // value published in the flags when this launch's stores are complete
     int publish = 0;                // 1: the last CTA of this launch publishes; 0: a later launch of the same call does
+    int local_only = 0;             // 1 (GEMM): store only into this rank's own arena; allgather_scatter_kernel sends the slice on
 };
 
 // Set by w4a8_gemv_allgather around its call into the ordinary launch path (single host thread per device).
@@ -96,6 +97,46 @@ __global__ void allgather_wait_kernel(const PeerDesc *p, unsigned int epoch, lon
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
         if ((int)(v - epoch) >= 0) return;
         if (clock64() - t0 > limit_cycles) { dev_set_error(0x200u | (unsigned)r); return; }
+    }
+}
+
+// Sends this rank's finished slice Y[0..M, col0..col0+cols) of its OWN arena to the same place in every other rank's
+// arena and publishes `epoch`.  Consecutive lanes copy consecutive 16-byte pieces of a row, so the NVLink writes are
+// whole rows' worth of contiguous bytes (the GEMM's own epilogue can only offer 16-byte pieces of 32 different rows
+// per instruction, which reached about 300 GB/s).  Needs col0, cols and ld multiples of 4 for the 16-byte path.
+__global__ void __launch_bounds__(256) allgather_scatter_kernel(const PeerDesc *p, size_t y_off, int M, long ld, long col0, int cols,
+                                                                unsigned int epoch) {
+    const int world = p->world, rank = p->rank;
+    const float *src = reinterpret_cast<const float *>(p->base[rank] + y_off);
+    const bool v4 = ((ld | col0 | cols) & 3) == 0;
+    const long per_row = v4 ? cols / 4 : cols, total = (long)M * per_row;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long m = i / per_row, c = i - m * per_row;
+        if (v4) {
+            const size_t off = (size_t)m * ld + col0 + 4 * c;
+            const float4 v = *reinterpret_cast<const float4 *>(src + off);
+            for (int k = 0; k < world; k++)
+                if (k != rank) *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p->base[k] + y_off) + off) = v;
+        } else {
+            const size_t off = (size_t)m * ld + col0 + c;
+            const float v = src[off];
+            for (int k = 0; k < world; k++)
+                if (k != rank) reinterpret_cast<float *>(p->base[k] + y_off)[off] = v;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(p->counter, 1u);
+        if (prev == gridDim.x - 1) {               // last CTA: every CTA's stores are fenced
+            *p->counter = 0u;
+            __threadfence_system();
+            const unsigned int e = *p->epoch_base + epoch;
+            for (int k = 0; k < world; k++) {
+                unsigned int *f = reinterpret_cast<unsigned int *>(p->base[k] + p->flag_off) + rank;
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(e) : "memory");
+            }
+        }
     }
 }
 

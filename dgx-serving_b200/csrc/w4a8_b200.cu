@@ -726,11 +726,20 @@ W4A8_API int w4a8_gemm_allgather(const int8_t *X, const float *xs, const uint8_t
     if (!aligned(X, 16) || !aligned(Wq, 16)) return fail(W4A8_ERR_ALIGN, "gemm_allgather: X and Wq must be 16-byte aligned (TMA)");
     rc = require_sm100();
     if (rc != W4A8_OK) return rc;
+    // Two ways to get the slice to the peers: (default) the GEMM writes only its own arena and a copy kernel sends the
+    // finished slice on with row-contiguous 16-byte stores; or (W4A8_GEMM_ALLGATHER=stores) the GEMM's epilogue stores
+    // every tile into every arena itself, which overlaps with the compute but offers NVLink only 16-byte pieces.
+    static const bool direct = [] { const char *e = getenv("W4A8_GEMM_ALLGATHER"); return e && e[0] == 's'; }();
     OutArgs &oa = current_out();
-    oa.peers = a->desc_dev; oa.y_off = y_offset; oa.ld = ldY; oa.col0 = row0; oa.epoch = epoch; oa.publish = 1;
+    oa.peers = a->desc_dev; oa.y_off = y_offset; oa.ld = ldY; oa.col0 = row0; oa.epoch = epoch;
+    oa.publish = direct ? 1 : 0; oa.local_only = direct ? 0 : 1;
     rc = gemm::launch_tc(X, xs, Wq, sw, Ylocal, M, rows, K, scale_dtype, 1, K / QBLK, st);   // the int8 kernel carries the peer epilogue
     oa = OutArgs();
-    return rc;
+    if (rc != W4A8_OK || direct) return rc;
+    const long units = (long)M * ((((long)ldY | row0 | rows) & 3) == 0 ? rows / 4 : rows);
+    long want = (units + 255) / 256, cap = (long)sm_count() * 4;
+    allgather_scatter_kernel<<<(unsigned)(want < cap ? (want > 0 ? want : 1) : cap), 256, 0, st>>>(a->desc_dev, y_offset, M, (long)ldY, (long)row0, rows, epoch);
+    return launch_status("allgather_scatter");
 }
 
 W4A8_API int w4a8_allgather_wait(w4a8_arena *a, uint32_t epoch, int timeout_us, void *stream) {

@@ -254,8 +254,10 @@ int w4a8_gemv_allgather(const int8_t *xq, const float *xs, const uint8_t *Wq, co
                         size_t y_offset, int IN, int rows, int row0, int ldY, int S, int scale_dtype,
                         uint32_t epoch, void *stream);
 /* The same for the prefill / verify GEMM (M rows of activations, w4a8_gemm semantics on the rank's `rows` weight rows):
- * every output tile goes straight to columns [row0, row0+rows) of Y[M, ldY] in every rank's arena with 16-byte peer
- * stores, then the epoch is published; no split-K.  X and Wq 16-byte aligned as for w4a8_gemm. */
+ * the tiles go to columns [row0, row0+rows) of Y[M, ldY] in the rank's own arena, a copy kernel sends the finished
+ * slice to the same place in every other rank's arena with row-contiguous 16-byte peer stores, then the epoch is
+ * published (environment W4A8_GEMM_ALLGATHER=stores: the GEMM's epilogue stores into every arena itself instead);
+ * no split-K.  X and Wq 16-byte aligned as for w4a8_gemm. */
 int w4a8_gemm_allgather(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a,
                         size_t y_offset, int M, int rows, int row0, int ldY, int K, int scale_dtype,
                         uint32_t epoch, void *stream);
