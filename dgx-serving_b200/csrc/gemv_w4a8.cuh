@@ -298,11 +298,130 @@ inline int launch_gemv_st(const int8_t *xq, const float *xs, const uint8_t *Wq, 
     return W4A8_OK;
 }
 
+template <typename ST>
+inline int launch_gemv_short(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int IN, int OUT,
+                             cudaStream_t st, const GroupedArgs &ga);
+
 inline int launch_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y,
                        int IN, int OUT, int S, int scale_dtype, cudaStream_t st) {
     if (S == 0 || OUT == 0) return W4A8_OK;
+    if (S == 1 && IN <= 32 * QBLK && !current_out().peers) {        // one short row: the R-rows-per-warp kernel (same bits)
+        if (scale_dtype == 1) return launch_gemv_short<__half>(xq, xs, Wq, (const __half *)sw, Y, IN, OUT, st, GroupedArgs());
+        return launch_gemv_short<float>(xq, xs, Wq, (const float *)sw, Y, IN, OUT, st, GroupedArgs());
+    }
     if (scale_dtype == 1) return launch_gemv_st<__half>(xq, xs, Wq, (const __half *)sw, Y, IN, OUT, S, st);
     return launch_gemv_st<float>(xq, xs, Wq, (const float *)sw, Y, IN, OUT, S, st);
+}
+
+// ---- short rows (K <= 1024: at most one group per lane), one activation row, optional expert grouping -----------
+// With one group per lane the persistent kernel above keeps only two 16-byte loads per lane in flight (its batches
+// are "groups of one row"), far too few to stream at HBM speed: the 768-wide expert down projection ran at 2.3 TB/s.
+// Here a warp takes R consecutive output rows at a time — lane b loads group b of each of them, with the next R rows'
+// loads issued before the current ones are used — so 2R loads are in flight per lane.  Same arithmetic per row as the
+// persistent kernel (acc = fma((xs*sw)/16, (float)(16*D), 0) in lane b, then the shfl_down tree): identical bits.
+template <int R, typename ST>
+__global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_short_kernel(
+    const int8_t *__restrict__ xq, const float *__restrict__ xs, const uint8_t *__restrict__ Wq,
+    const ST *__restrict__ sw, float *__restrict__ Y, int IN, int OUT, bool w_a16, GroupedArgs ga) {
+    const int nb = IN / QBLK;                                       // <= 32
+    if (ga.idx) {                                                   // blockIdx.y = slot (see the persistent kernel)
+        const int slot = blockIdx.y;
+        const int e = ga.idx[slot];
+        if (e < 0 || e >= ga.num_experts) return;
+        const int row = ga.x_per_slot ? slot : slot / ga.topk;
+        xq += (size_t)row * IN;
+        xs += (size_t)row * nb;
+        Wq += (size_t)e * ((size_t)OUT * (IN / 2));
+        sw += (size_t)e * ((size_t)OUT * nb);
+        Y += (size_t)slot * OUT;
+    }
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t wpitch = (size_t)(IN / 2);
+    // units of R rows, dealt round-robin to the warps of the grid
+    const int units = (OUT + R - 1) / R;
+    const int gw = blockIdx.x * GEMV_WARPS + warp, nw = gridDim.x * GEMV_WARPS;
+    const bool live = lane < nb;
+    uint4 wa[R], wb[R];
+    float sa[R], sb_[R];
+    auto load = [&](int unit, uint4 (&w)[R], float (&sc)[R]) {
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            const int r = unit * R + i;
+            if (live && r < OUT) { w[i] = ldg_w16(Wq + (size_t)r * wpitch + 16 * lane, w_a16); sc[i] = load_scale(sw + (size_t)r * nb, lane); }
+            else { w[i] = make_uint4(0, 0, 0, 0); sc[i] = 0.f; }
+        }
+    };
+    pdl_launch_dependents();
+    if (gw < units) load(gw, wa, sa);                               // weights only: allowed before the dependency wait
+    pdl_wait();
+    // this lane's group of the activation row, split into even / odd bytes to match unpack8_x16
+    uint32_t xe[4] = {0u, 0u, 0u, 0u}, xo[4] = {0u, 0u, 0u, 0u};
+    float xsv = 0.f;
+    if (live) {
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + (size_t)lane * QBLK);
+        uint32_t v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = src[i];
+#pragma unroll
+        for (int i = 0; i < 4; i++) split_even_odd(v[2 * i], v[2 * i + 1], xe[i], xo[i]);
+        xsv = xs[lane];
+    }
+    auto compute = [&](int unit, const uint4 (&w)[R], const float (&sc)[R]) {
+        float acc[R];
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            uint32_t e0, o0, e1, o1, e2, o2, e3, o3;
+            unpack8_x16(w[i].x, e0, o0); unpack8_x16(w[i].y, e1, o1);
+            unpack8_x16(w[i].z, e2, o2); unpack8_x16(w[i].w, e3, o3);
+            int d = __dp4a((int)xe[0], (int)e0, 0);
+            d = __dp4a((int)xo[0], (int)o0, d);
+            d = __dp4a((int)xe[1], (int)e1, d);
+            d = __dp4a((int)xo[1], (int)o1, d);
+            d = __dp4a((int)xe[2], (int)e2, d);
+            d = __dp4a((int)xo[2], (int)o2, d);
+            d = __dp4a((int)xe[3], (int)e3, d);
+            d = __dp4a((int)xo[3], (int)o3, d);                     // d = 16 * D[o,b], exact
+            const float scv = (xsv * sc[i]) * 0.0625f;              // exact 1/16
+            acc[i] = live ? fmaf(scv, (float)d, 0.f) : 0.f;
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+            for (int i = 0; i < R; i++) acc[i] += __shfl_down_sync(0xffffffffu, acc[i], off);
+        if (lane == 0) {
+#pragma unroll
+            for (int i = 0; i < R; i++)
+                if (unit * R + i < OUT) Y[unit * R + i] = acc[i];
+        }
+    };
+    for (int u = gw; u < units; u += 2 * nw) {
+        if (u + nw < units) load(u + nw, wb, sb_);
+        compute(u, wa, sa);
+        if (u + nw >= units) break;
+        if (u + 2 * nw < units) load(u + 2 * nw, wa, sa);
+        compute(u + nw, wb, sb_);
+    }
+}
+
+template <typename ST>
+inline int launch_gemv_short(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int IN, int OUT,
+                             cudaStream_t st, const GroupedArgs &ga) {
+    constexpr int R = 4;
+    auto kern = gemv_w4a8_short_kernel<R, ST>;
+    static int occ = 0;
+    if (occ == 0) {
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, GEMV_WARPS * 32, 0);
+        if (e != cudaSuccess) return cuda_fail(e, "gemv_short occupancy query");
+        occ = n > 0 ? n : 1;
+    }
+    const long units = (OUT + R - 1) / R;
+    long want = (units + GEMV_WARPS - 1) / GEMV_WARPS, cap = (long)sm_count() * occ;
+    if (ga.idx) cap = cap / ga.nslots > 1 ? cap / ga.nslots : 1;
+    const dim3 grid((unsigned)(want < cap ? want : cap), (unsigned)(ga.idx ? ga.nslots : 1));
+    cudaError_t le = launch_pdl(kern, grid, dim3(GEMV_WARPS * 32), 0, st, xq, xs, Wq, sw, Y, IN, OUT, aligned(Wq, 16), ga);
+    if (le != cudaSuccess) return cuda_fail(le, "gemv_w4a8_short launch");
+    return launch_status("gemv_w4a8_short");
 }
 
 // Grouped experts: one launch, grid.y = slots, each slot one activation row against its expert.
@@ -313,6 +432,10 @@ inline int launch_moe_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq,
     if (nslots > 65535) return fail(W4A8_ERR_UNSUPPORTED, "moe_gemv: at most 65535 slots per launch (got %d)", nslots);
     GroupedArgs ga;
     ga.idx = idx; ga.topk = topk; ga.x_per_slot = x_per_slot; ga.num_experts = num_experts; ga.nslots = nslots;
+    if (K <= 32 * QBLK && !current_out().peers) {                  // short rows: the R-rows-per-warp kernel
+        if (scale_dtype == 1) return launch_gemv_short<__half>(xq, xs, Wq, (const __half *)sw, Y, K, N, st, ga);
+        return launch_gemv_short<float>(xq, xs, Wq, (const float *)sw, Y, K, N, st, ga);
+    }
     if (scale_dtype == 1) return launch_gemv_dp4a_u<1, __half>(xq, xs, Wq, (const __half *)sw, Y, K, N, 1, st, ga);
     return launch_gemv_dp4a_u<1, float>(xq, xs, Wq, (const float *)sw, Y, K, N, 1, st, ga);
 }
