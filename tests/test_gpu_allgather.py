@@ -151,6 +151,28 @@ for (S, N, K) in [(1, 17408, 5120), (8, 4096, 1024), (16, 1001, 512)]:
     assert np.array_equal(Y.cpu().numpy().view(np.uint32), expect.view(np.uint32))
     dist.barrier()
     a.close()
+# the prefill GEMM with the fused exchange: every rank ends up with the whole Y[M, N] in MMQ order
+for (M, N, K) in [(256, 1024, 1024), (130, 520, 512)]:
+    xq, xs, Wq, sw = make_case(O, M, N, K, seed=9 + M)
+    expect = O.gemm_mmq_w4a8(xq, xs, Wq, sw)
+    row0, rows = w.shard_rows(N, rank, world)
+    xq_d, xs_d = to_dev(xq, dev), to_dev(xs, dev)
+    Wq_r, sw_r = to_dev(Wq[row0:row0 + rows], dev), to_dev(sw[row0:row0 + rows], dev)
+    ystride = (M * N * 4 + 255) // 256 * 256
+    a = w.Arena(2 * ystride, rank, world)
+    handles = [None] * world
+    dist.all_gather_object(handles, a.export_handle())
+    a.connect_handles(handles)
+    dist.barrier()
+    for epoch in range(1, 4):
+        off = (epoch % 2) * ystride
+        a.gemm_allgather(xq_d, xs_d, Wq_r, sw_r, off, M, rows, row0, N, K, 0, epoch)
+        a.wait(epoch, timeout_us=2000000)
+        w.device_status()
+        y = a.tensor(off, (M, N)).cpu().numpy()
+        assert np.array_equal(y.view(np.uint32), expect.view(np.uint32)), (M, N, K, epoch, rank)
+    dist.barrier()
+    a.close()
 dist.destroy_process_group()
 print("rank", rank, "ok")
 '''
