@@ -33,6 +33,20 @@ inline int launch_status(const char *what) {
 }
 inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
+// A value per CUDA device, selected by the current device: launch-side caches of per-device facts (function
+// attributes such as the dynamic shared-memory opt-in, occupancy answers) must not leak from one GPU to the next in
+// a process that drives several.
+template <typename T>
+struct PerDevice {
+    static constexpr int MAX_DEV = 64;
+    T v[MAX_DEV] = {};
+    T &get() {
+        int d = 0;
+        if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= MAX_DEV) d = 0;
+        return v[d];
+    }
+};
+
 // Number of SMs of the current device (148 on B200), cached per device.
 int sm_count();
 // W4A8_OK if the current device is compute capability 10.x, else W4A8_ERR_UNSUPPORTED.

@@ -28,6 +28,7 @@
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 #include "peer_allgather.cuh"
+#include "tmap_cache.cuh"
 
 namespace w4a8 {
 namespace gemm {
@@ -500,48 +501,17 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
 }
 
 // ---- host side ------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-inline EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
-// 2-D byte tensor [rows][row_bytes] (pitch = row_bytes), box [box_rows][box_bytes].
-inline int make_tmap_u8(CUtensorMap *tm, const void *ptr, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes,
-                        uint32_t box_rows, CUtensorMapSwizzle swz) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (!fn) return fail(W4A8_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
-    cuuint64_t dims[2] = {row_bytes, rows};
-    cuuint64_t strides[1] = {row_bytes};
-    cuuint32_t box[2] = {box_bytes, box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(W4A8_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d)", (int)r);
-    return W4A8_OK;
-}
-
 template <typename ST, bool DUMP, int EPI, bool PEER = false>
 inline int launch_tc_e(const int8_t *X, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int32_t *D,
-                       int M, int N, int K, int nsplit, int gsplit, cudaStream_t st) {
+                       int M, int N, int K, int nsplit, int gsplit, cudaStream_t st, const OutArgs &oa) {
     CUtensorMap tmA, tmB;
     int rc = make_tmap_u8(&tmA, X, (uint64_t)K, (uint64_t)M, KT, BM, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != W4A8_OK) return rc;
     rc = make_tmap_u8(&tmB, Wq, (uint64_t)K / 2, (uint64_t)N, KT / 2, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != W4A8_OK) return rc;
     auto kern = gemm_w4a8_tc_kernel<ST, DUMP, EPI, PEER>;
-    static bool configured = false;
+    static PerDevice<bool> configured_dev;              // the opt-in is a per-device function attribute
+    bool &configured = configured_dev.get();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return cuda_fail(e, "gemm smem opt-in");
@@ -550,7 +520,7 @@ inline int launch_tc_e(const int8_t *X, const float *xs, const uint8_t *Wq, cons
     const long tiles = (long)((M + BM - 1) / BM) * ((N + BN - 1) / BN) * nsplit;
     const int sms = sm_count();
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, xs, sw, Y, D, M, N, K, nsplit, gsplit, PEER ? current_out() : OutArgs());
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, xs, sw, Y, D, M, N, K, nsplit, gsplit, PEER ? oa : OutArgs());
     return launch_status("gemm_w4a8_tc");
 }
 
@@ -567,27 +537,27 @@ inline int epi_variant() {
 }
 template <typename ST, bool DUMP>
 inline int launch_tc_t(const int8_t *X, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int32_t *D,
-                       int M, int N, int K, int nsplit, int gsplit, cudaStream_t st) {
-    if (!DUMP && current_out().peers) return launch_tc_e<ST, false, 2, true>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
+                       int M, int N, int K, int nsplit, int gsplit, cudaStream_t st, const OutArgs &oa) {
+    if (!DUMP && oa.peers) return launch_tc_e<ST, false, 2, true>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st, oa);
     switch (DUMP ? 0 : epi_variant()) {
-        case 1: return launch_tc_e<ST, DUMP, 1>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
-        case 2: return launch_tc_e<ST, DUMP, 2>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
-        case 3: return launch_tc_e<ST, DUMP, 3>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
-        case 6: return launch_tc_e<ST, DUMP, 6>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
-        default: return launch_tc_e<ST, DUMP, 0>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st);
+        case 1: return launch_tc_e<ST, DUMP, 1>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st, oa);
+        case 2: return launch_tc_e<ST, DUMP, 2>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st, oa);
+        case 3: return launch_tc_e<ST, DUMP, 3>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st, oa);
+        case 6: return launch_tc_e<ST, DUMP, 6>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st, oa);
+        default: return launch_tc_e<ST, DUMP, 0>(X, xs, Wq, sw, Y, D, M, N, K, nsplit, gsplit, st, oa);
     }
 }
 
 // nsplit = 1: Y is the output.  nsplit > 1: Y is the [nsplit][M][N] partial-sum workspace and gsplit the
 // number of groups per split.
 inline int launch_tc(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int M, int N, int K,
-                     int scale_dtype, int nsplit, int gsplit, cudaStream_t st) {
+                     int scale_dtype, int nsplit, int gsplit, cudaStream_t st, const OutArgs &oa = OutArgs()) {
     if (scale_dtype == 1)
-        return launch_tc_t<__half, false>(X, xs, Wq, (const __half *)sw, Y, nullptr, M, N, K, nsplit, gsplit, st);
-    return launch_tc_t<float, false>(X, xs, Wq, (const float *)sw, Y, nullptr, M, N, K, nsplit, gsplit, st);
+        return launch_tc_t<__half, false>(X, xs, Wq, (const __half *)sw, Y, nullptr, M, N, K, nsplit, gsplit, st, oa);
+    return launch_tc_t<float, false>(X, xs, Wq, (const float *)sw, Y, nullptr, M, N, K, nsplit, gsplit, st, oa);
 }
 inline int launch_tc_dump(const int8_t *X, const uint8_t *Wq, int32_t *D, int M, int N, int K, cudaStream_t st) {
-    return launch_tc_t<float, true>(X, nullptr, Wq, (const float *)nullptr, nullptr, D, M, N, K, 1, K / QBLK, st);
+    return launch_tc_t<float, true>(X, nullptr, Wq, (const float *)nullptr, nullptr, D, M, N, K, 1, K / QBLK, st, OutArgs());
 }
 
 }  // namespace gemm

@@ -22,7 +22,7 @@
 #include <cuda.h>
 #include "common.cuh"
 #include "ptx_sm100.cuh"
-#include "gemm_w4a8_tc.cuh"   // Work / decode_work / Ring / pack_f32x2 / make_tmap_u8 / error codes
+#include "gemm_w4a8_tc.cuh"   // Work / decode_work / Ring / pack_f32x2 / error codes
 
 namespace w4a8 {
 namespace gemmf {
@@ -412,12 +412,13 @@ template <typename ST, bool DUMP>
 inline int launch_t(const int8_t *X, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int32_t *D,
                     int M, int N, int K, int nsplit, int gsplit, cudaStream_t st) {
     CUtensorMap tmA, tmB;
-    int rc = gemm::make_tmap_u8(&tmA, X, (uint64_t)K, (uint64_t)M, KT, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
+    int rc = make_tmap_u8(&tmA, X, (uint64_t)K, (uint64_t)M, KT, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != W4A8_OK) return rc;
-    rc = gemm::make_tmap_u8(&tmB, Wq, (uint64_t)K / 2, (uint64_t)N, KT / 2, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
+    rc = make_tmap_u8(&tmB, Wq, (uint64_t)K / 2, (uint64_t)N, KT / 2, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != W4A8_OK) return rc;
     auto kern = gemm_w4a8_tcf_kernel<ST, DUMP>;
-    static bool configured = false;
+    static PerDevice<bool> configured_dev;              // the opt-in is a per-device function attribute
+    bool &configured = configured_dev.get();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return cuda_fail(e, "gemm (fp16 operands) smem opt-in");

@@ -111,6 +111,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_dp4a_kernel(
     const int nb = IN / QBLK;
     if (ga.idx) {  // grouped experts: blockIdx.y = slot, one activation row against that slot's expert
         const int slot = blockIdx.y;
+        pdl_wait();   // the routing indices are written by an earlier kernel of the stream (router / top-k): wait first
         const int e = ga.idx[slot];
         if (e < 0 || e >= ga.num_experts) return;   // invalid id: the slot's output row is left untouched
         const int row = ga.x_per_slot ? slot : slot / ga.topk;
@@ -216,12 +217,13 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_dp4a_kernel(
 
 template <int MT, int U, typename ST, bool PEER>
 inline int launch_gemv_dp4a_p(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y,
-                              int IN, int OUT, int S, cudaStream_t st, const GroupedArgs &ga) {
+                              int IN, int OUT, int S, cudaStream_t st, const GroupedArgs &ga, const OutArgs &oa) {
     const int nb = IN / QBLK;
     const size_t smem = (size_t)MT * IN + (size_t)MT * nb * sizeof(float);
     auto kern = gemv_w4a8_dp4a_kernel<MT, U, ST, PEER>;
     if (smem > 48 * 1024) {
-        static size_t configured = 0;   // grow-only; single host thread per device (library convention)
+        static PerDevice<size_t> configured_dev;        // grow-only; the opt-in is a per-device function attribute
+        size_t &configured = configured_dev.get();
         if (smem > configured) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return cuda_fail(e, "gemv smem opt-in");
@@ -230,54 +232,59 @@ inline int launch_gemv_dp4a_p(const int8_t *xq, const float *xs, const uint8_t *
     }
     // Persistent: as many CTAs as are resident at once (fewer when there are not enough rows, or when grouped
     // slots already fill the GPU).  Residency is asked of the runtime once per kernel variant and smem size.
-    static size_t occ_smem = ~(size_t)0;
-    static int occ = 1;
-    if (occ_smem != smem) {
+    struct Occ { size_t smem_plus1; int occ; };          // per device: another GPU may answer differently
+    static PerDevice<Occ> occ_dev;
+    Occ &oc = occ_dev.get();
+    size_t occ_smem = oc.smem_plus1 - 1;
+    int occ = oc.occ > 0 ? oc.occ : 1;
+    if (oc.smem_plus1 == 0 || occ_smem != smem) {
         int n = 0;
         cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, GEMV_WARPS * 32, smem);
         if (e != cudaSuccess) return cuda_fail(e, "gemv occupancy query");
         occ = n > 0 ? n : 1;
-        occ_smem = smem;
+        oc.occ = occ;
+        oc.smem_plus1 = smem + 1;
     }
     long want = (OUT + GEMV_WARPS - 1) / GEMV_WARPS;
     long cap = (long)sm_count() * occ;
     if (ga.idx) cap = cap / ga.nslots > 1 ? cap / ga.nslots : 1;
     const dim3 grid((unsigned)(want < cap ? want : cap), (unsigned)(ga.idx ? ga.nslots : 1));
     // every expert's base stays 16-byte aligned when Wq is, because OUT*IN/2 is a multiple of 16
-    cudaError_t le = launch_pdl(kern, grid, dim3(GEMV_WARPS * 32), smem, st, xq, xs, Wq, sw, Y, IN, OUT, S, aligned(Wq, 16), ga, current_out());
+    cudaError_t le = launch_pdl(kern, grid, dim3(GEMV_WARPS * 32), smem, st, xq, xs, Wq, sw, Y, IN, OUT, S, aligned(Wq, 16), ga, oa);
     if (le != cudaSuccess) return cuda_fail(le, "gemv_w4a8 launch");
     return launch_status("gemv_w4a8");
 }
 
 template <int MT, int U, typename ST>
 inline int launch_gemv_dp4a_t(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y,
-                              int IN, int OUT, int S, cudaStream_t st, const GroupedArgs &ga) {
-    if (current_out().peers) return launch_gemv_dp4a_p<MT, U, ST, true>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga);
-    return launch_gemv_dp4a_p<MT, U, ST, false>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga);
+                              int IN, int OUT, int S, cudaStream_t st, const GroupedArgs &ga, const OutArgs &oa) {
+    if (oa.peers) return launch_gemv_dp4a_p<MT, U, ST, true>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga, oa);
+    return launch_gemv_dp4a_p<MT, U, ST, false>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga, oa);
 }
 
 template <int MT, typename ST>
 inline int launch_gemv_dp4a_u(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y,
-                              int IN, int OUT, int S, cudaStream_t st, const GroupedArgs &ga = GroupedArgs()) {
+                              int IN, int OUT, int S, cudaStream_t st, const GroupedArgs &ga = GroupedArgs(),
+                              const OutArgs &oa = OutArgs()) {
     const int nslots = (IN / QBLK + 31) / 32;
     // Loads in flight per lane: the whole row when it has at most 5 slots, else the divisor of the slot
     // count that wastes no predicated slot (5 for K = 15360), else 4.
     int u = nslots <= 5 ? nslots : (nslots % 5 == 0 ? 5 : (nslots % 3 == 0 ? 3 : 4));
     switch (u) {
-        case 1: return launch_gemv_dp4a_t<MT, 1, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga);
-        case 2: return launch_gemv_dp4a_t<MT, 2, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga);
-        case 3: return launch_gemv_dp4a_t<MT, 3, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga);
-        case 4: return launch_gemv_dp4a_t<MT, 4, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga);
-        default: return launch_gemv_dp4a_t<MT, 5, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga);
+        case 1: return launch_gemv_dp4a_t<MT, 1, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga, oa);
+        case 2: return launch_gemv_dp4a_t<MT, 2, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga, oa);
+        case 3: return launch_gemv_dp4a_t<MT, 3, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga, oa);
+        case 4: return launch_gemv_dp4a_t<MT, 4, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga, oa);
+        default: return launch_gemv_dp4a_t<MT, 5, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, ga, oa);
     }
 }
 
 template <typename ST>
 inline int launch_gemv_st(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y,
-                          int IN, int OUT, int S, cudaStream_t st) {
+                          int IN, int OUT, int S, cudaStream_t st, const OutArgs &oa_in) {
     const int nb = IN / QBLK;
     // Rows beyond GEMV_MT_MAX go in further passes over the weights (which then come from L2).
-    OutArgs &oa = current_out();
+    OutArgs oa = oa_in;
     const size_t y_off0 = oa.y_off;
     for (int s0 = 0; s0 < S; s0 += GEMV_MT_MAX) {
         const int s = S - s0 < GEMV_MT_MAX ? S - s0 : GEMV_MT_MAX;
@@ -287,14 +294,13 @@ inline int launch_gemv_st(const int8_t *xq, const float *xs, const uint8_t *Wq, 
         float *y_p = Y + (size_t)s0 * OUT;
         int rc;
         switch (s) {
-            case 1: rc = launch_gemv_dp4a_u<1, ST>(xq_p, xs_p, Wq, sw, y_p, IN, OUT, s, st); break;
-            case 2: rc = launch_gemv_dp4a_u<2, ST>(xq_p, xs_p, Wq, sw, y_p, IN, OUT, s, st); break;
-            case 3: rc = launch_gemv_dp4a_u<3, ST>(xq_p, xs_p, Wq, sw, y_p, IN, OUT, s, st); break;
-            default: rc = launch_gemv_dp4a_u<4, ST>(xq_p, xs_p, Wq, sw, y_p, IN, OUT, s, st); break;
+            case 1: rc = launch_gemv_dp4a_u<1, ST>(xq_p, xs_p, Wq, sw, y_p, IN, OUT, s, st, GroupedArgs(), oa); break;
+            case 2: rc = launch_gemv_dp4a_u<2, ST>(xq_p, xs_p, Wq, sw, y_p, IN, OUT, s, st, GroupedArgs(), oa); break;
+            case 3: rc = launch_gemv_dp4a_u<3, ST>(xq_p, xs_p, Wq, sw, y_p, IN, OUT, s, st, GroupedArgs(), oa); break;
+            default: rc = launch_gemv_dp4a_u<4, ST>(xq_p, xs_p, Wq, sw, y_p, IN, OUT, s, st, GroupedArgs(), oa); break;
         }
-        if (rc != W4A8_OK) { oa.y_off = y_off0; return rc; }
+        if (rc != W4A8_OK) return rc;
     }
-    oa.y_off = y_off0;
     return W4A8_OK;
 }
 
@@ -303,14 +309,14 @@ inline int launch_gemv_short(const int8_t *xq, const float *xs, const uint8_t *W
                              cudaStream_t st, const GroupedArgs &ga);
 
 inline int launch_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y,
-                       int IN, int OUT, int S, int scale_dtype, cudaStream_t st) {
+                       int IN, int OUT, int S, int scale_dtype, cudaStream_t st, const OutArgs &oa = OutArgs()) {
     if (S == 0 || OUT == 0) return W4A8_OK;
-    if (S == 1 && IN <= 32 * QBLK && !current_out().peers) {        // one short row: the R-rows-per-warp kernel (same bits)
+    if (S == 1 && IN <= 32 * QBLK && !oa.peers) {        // one short row: the R-rows-per-warp kernel (same bits)
         if (scale_dtype == 1) return launch_gemv_short<__half>(xq, xs, Wq, (const __half *)sw, Y, IN, OUT, st, GroupedArgs());
         return launch_gemv_short<float>(xq, xs, Wq, (const float *)sw, Y, IN, OUT, st, GroupedArgs());
     }
-    if (scale_dtype == 1) return launch_gemv_st<__half>(xq, xs, Wq, (const __half *)sw, Y, IN, OUT, S, st);
-    return launch_gemv_st<float>(xq, xs, Wq, (const float *)sw, Y, IN, OUT, S, st);
+    if (scale_dtype == 1) return launch_gemv_st<__half>(xq, xs, Wq, (const __half *)sw, Y, IN, OUT, S, st, oa);
+    return launch_gemv_st<float>(xq, xs, Wq, (const float *)sw, Y, IN, OUT, S, st, oa);
 }
 
 // ---- short rows (K <= 1024: at most one group per lane), one activation row, optional expert grouping -----------
@@ -326,6 +332,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_short_kernel(
     const int nb = IN / QBLK;                                       // <= 32
     if (ga.idx) {                                                   // blockIdx.y = slot (see the persistent kernel)
         const int slot = blockIdx.y;
+        pdl_wait();   // the routing indices are written by an earlier kernel of the stream: wait before reading them
         const int e = ga.idx[slot];
         if (e < 0 || e >= ga.num_experts) return;
         const int row = ga.x_per_slot ? slot : slot / ga.topk;
@@ -408,7 +415,8 @@ inline int launch_gemv_short(const int8_t *xq, const float *xs, const uint8_t *W
                              cudaStream_t st, const GroupedArgs &ga) {
     constexpr int R = 4;
     auto kern = gemv_w4a8_short_kernel<R, ST>;
-    static int occ = 0;
+    static PerDevice<int> occ_dev;
+    int &occ = occ_dev.get();
     if (occ == 0) {
         int n = 0;
         cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, GEMV_WARPS * 32, 0);
@@ -432,7 +440,7 @@ inline int launch_moe_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq,
     if (nslots > 65535) return fail(W4A8_ERR_UNSUPPORTED, "moe_gemv: at most 65535 slots per launch (got %d)", nslots);
     GroupedArgs ga;
     ga.idx = idx; ga.topk = topk; ga.x_per_slot = x_per_slot; ga.num_experts = num_experts; ga.nslots = nslots;
-    if (K <= 32 * QBLK && !current_out().peers) {                  // short rows: the R-rows-per-warp kernel
+    if (K <= 32 * QBLK) {                                           // short rows: the R-rows-per-warp kernel
         if (scale_dtype == 1) return launch_gemv_short<__half>(xq, xs, Wq, (const __half *)sw, Y, K, N, st, ga);
         return launch_gemv_short<float>(xq, xs, Wq, (const float *)sw, Y, K, N, st, ga);
     }

@@ -215,9 +215,10 @@ inline bool plan_for(const void *xq, const void *Wq, const void *sw, int IN, int
 }
 
 template <int NG, typename ST, bool PEER>
-inline int launch_p(const int8_t *xq, const float *xs, const Mats &mats_in, int IN, const Plan &p, cudaStream_t st) {
+inline int launch_p(const int8_t *xq, const float *xs, const Mats &mats_in, int IN, const Plan &p, cudaStream_t st, const OutArgs &oa) {
     auto kern = gemv_w4a8_bulk_kernel<NG, ST, PEER>;
-    static size_t configured = 0;   // grow-only; single host thread per device (library convention)
+    static PerDevice<size_t> configured_dev;            // grow-only; the opt-in is a per-device function attribute
+    size_t &configured = configured_dev.get();
     if (p.smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
         if (e != cudaSuccess) return cuda_fail(e, "gemv_bulk smem opt-in");
@@ -242,42 +243,43 @@ inline int launch_p(const int8_t *xq, const float *xs, const Mats &mats_in, int 
         m.cta0[i + 1] = (int)end;
     }
     m.cta0[m.count] = (int)grid;
-    cudaError_t le = launch_pdl(kern, dim3((unsigned)grid), dim3(THREADS), p.smem, st, xq, xs, m, IN, p.stages, current_out());
+    cudaError_t le = launch_pdl(kern, dim3((unsigned)grid), dim3(THREADS), p.smem, st, xq, xs, m, IN, p.stages, oa);
     if (le != cudaSuccess) return cuda_fail(le, "gemv_w4a8_bulk launch");
     return launch_status("gemv_w4a8_bulk");
 }
 
 template <int NG, typename ST>
-inline int launch_t(const int8_t *xq, const float *xs, const Mats &m, int IN, const Plan &p, cudaStream_t st) {
-    if (current_out().peers) return launch_p<NG, ST, true>(xq, xs, m, IN, p, st);
-    return launch_p<NG, ST, false>(xq, xs, m, IN, p, st);
+inline int launch_t(const int8_t *xq, const float *xs, const Mats &m, int IN, const Plan &p, cudaStream_t st, const OutArgs &oa) {
+    if (oa.peers) return launch_p<NG, ST, true>(xq, xs, m, IN, p, st, oa);
+    return launch_p<NG, ST, false>(xq, xs, m, IN, p, st, oa);
 }
 
 template <typename ST>
-inline int launch_st(const int8_t *xq, const float *xs, const Mats &m, int IN, const Plan &p, cudaStream_t st) {
+inline int launch_st(const int8_t *xq, const float *xs, const Mats &m, int IN, const Plan &p, cudaStream_t st, const OutArgs &oa) {
     switch (p.NG) {
-        case 1: return launch_t<1, ST>(xq, xs, m, IN, p, st);
-        case 2: return launch_t<2, ST>(xq, xs, m, IN, p, st);
-        case 3: return launch_t<3, ST>(xq, xs, m, IN, p, st);
-        case 4: return launch_t<4, ST>(xq, xs, m, IN, p, st);
-        case 5: return launch_t<5, ST>(xq, xs, m, IN, p, st);
-        case 6: return launch_t<6, ST>(xq, xs, m, IN, p, st);
-        case 7: return launch_t<7, ST>(xq, xs, m, IN, p, st);
-        case 8: return launch_t<8, ST>(xq, xs, m, IN, p, st);
+        case 1: return launch_t<1, ST>(xq, xs, m, IN, p, st, oa);
+        case 2: return launch_t<2, ST>(xq, xs, m, IN, p, st, oa);
+        case 3: return launch_t<3, ST>(xq, xs, m, IN, p, st, oa);
+        case 4: return launch_t<4, ST>(xq, xs, m, IN, p, st, oa);
+        case 5: return launch_t<5, ST>(xq, xs, m, IN, p, st, oa);
+        case 6: return launch_t<6, ST>(xq, xs, m, IN, p, st, oa);
+        case 7: return launch_t<7, ST>(xq, xs, m, IN, p, st, oa);
+        case 8: return launch_t<8, ST>(xq, xs, m, IN, p, st, oa);
     }
     return fail(W4A8_ERR_UNSUPPORTED, "gemv_bulk: no kernel for %d groups per lane", p.NG);
 }
 
-inline int launch_multi(const int8_t *xq, const float *xs, const Mats &m, int IN, int scale_dtype, const Plan &p, cudaStream_t st) {
-    if (scale_dtype == 1) return launch_st<__half>(xq, xs, m, IN, p, st);
-    return launch_st<float>(xq, xs, m, IN, p, st);
+inline int launch_multi(const int8_t *xq, const float *xs, const Mats &m, int IN, int scale_dtype, const Plan &p, cudaStream_t st,
+                        const OutArgs &oa = OutArgs()) {
+    if (scale_dtype == 1) return launch_st<__half>(xq, xs, m, IN, p, st, oa);
+    return launch_st<float>(xq, xs, m, IN, p, st, oa);
 }
 
 inline int launch(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int IN, int OUT,
-                  int scale_dtype, const Plan &p, cudaStream_t st) {
+                  int scale_dtype, const Plan &p, cudaStream_t st, const OutArgs &oa = OutArgs()) {
     Mats m = {};
     m.Wq[0] = Wq; m.sw[0] = sw; m.Y[0] = Y; m.OUT[0] = OUT; m.count = 1;
-    return launch_multi(xq, xs, m, IN, scale_dtype, p, st);
+    return launch_multi(xq, xs, m, IN, scale_dtype, p, st, oa);
 }
 
 }  // namespace gemv_bulk

@@ -416,11 +416,12 @@ inline bool plan_for(const void *Wq, const void *sw, int IN, int S, Plan *p) {
 
 template <int MH, int GS, int STAGES, typename ST, bool PEER>
 inline int launch_p(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int IN, int OUT, int S,
-                    cudaStream_t st) {
+                    cudaStream_t st, const OutArgs &oa) {
     const int nb = IN / QBLK;
     const size_t smem = smem_bytes(MH, S, nb, GS, STAGES);
     auto kern = gemv_w4a8_mma_kernel<MH, GS, STAGES, ST, PEER>;
-    static size_t configured = 0;
+    static PerDevice<size_t> configured_dev;            // grow-only; the opt-in is a per-device function attribute
+    size_t &configured = configured_dev.get();
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return cuda_fail(e, "gemv_mma smem opt-in");
@@ -430,23 +431,23 @@ inline int launch_p(const int8_t *xq, const float *xs, const uint8_t *Wq, const 
     long want = (units + 1) / 2;                         // at least one 16-row tile per CTA
     long cap = sm_count();                               // one persistent CTA per SM
     const dim3 grid((unsigned)(want < cap ? want : cap));
-    cudaError_t le = launch_pdl(kern, grid, dim3(WARPS * 32), smem, st, xq, xs, Wq, sw, Y, IN, OUT, S, current_out());
+    cudaError_t le = launch_pdl(kern, grid, dim3(WARPS * 32), smem, st, xq, xs, Wq, sw, Y, IN, OUT, S, oa);
     if (le != cudaSuccess) return cuda_fail(le, "gemv_w4a8_mma launch");
     return launch_status("gemv_w4a8_mma");
 }
 
 template <int MH, int GS, int STAGES, typename ST>
 inline int launch_t(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int IN, int OUT, int S,
-                    cudaStream_t st) {
-    if (current_out().peers) return launch_p<MH, GS, STAGES, ST, true>(xq, xs, Wq, sw, Y, IN, OUT, S, st);
-    return launch_p<MH, GS, STAGES, ST, false>(xq, xs, Wq, sw, Y, IN, OUT, S, st);
+                    cudaStream_t st, const OutArgs &oa) {
+    if (oa.peers) return launch_p<MH, GS, STAGES, ST, true>(xq, xs, Wq, sw, Y, IN, OUT, S, st, oa);
+    return launch_p<MH, GS, STAGES, ST, false>(xq, xs, Wq, sw, Y, IN, OUT, S, st, oa);
 }
 
 template <typename ST>
 inline int launch_st(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int IN, int OUT, int S,
-                     const Plan &p, cudaStream_t st) {
+                     const Plan &p, cudaStream_t st, const OutArgs &oa) {
 #define W4A8_MMA_CASE(MH_, GS_, ST_) \
-    if (p.MH == MH_ && p.GS == GS_ && p.STAGES == ST_) return launch_t<MH_, GS_, ST_, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st);
+    if (p.MH == MH_ && p.GS == GS_ && p.STAGES == ST_) return launch_t<MH_, GS_, ST_, ST>(xq, xs, Wq, sw, Y, IN, OUT, S, st, oa);
     W4A8_MMA_CASE(1, 16, 4) W4A8_MMA_CASE(1, 16, 3) W4A8_MMA_CASE(1, 16, 2) W4A8_MMA_CASE(1, 8, 8) W4A8_MMA_CASE(1, 8, 6) W4A8_MMA_CASE(1, 8, 3)
     W4A8_MMA_CASE(2, 16, 4) W4A8_MMA_CASE(2, 16, 3) W4A8_MMA_CASE(2, 16, 2) W4A8_MMA_CASE(2, 8, 8) W4A8_MMA_CASE(2, 8, 6) W4A8_MMA_CASE(2, 8, 3)
 #undef W4A8_MMA_CASE
@@ -454,9 +455,9 @@ inline int launch_st(const int8_t *xq, const float *xs, const uint8_t *Wq, const
 }
 
 inline int launch(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int IN, int OUT, int S,
-                  int scale_dtype, const Plan &p, cudaStream_t st) {
-    if (scale_dtype == 1) return launch_st<__half>(xq, xs, Wq, (const __half *)sw, Y, IN, OUT, S, p, st);
-    return launch_st<float>(xq, xs, Wq, (const float *)sw, Y, IN, OUT, S, p, st);
+                  int scale_dtype, const Plan &p, cudaStream_t st, const OutArgs &oa = OutArgs()) {
+    if (scale_dtype == 1) return launch_st<__half>(xq, xs, Wq, (const __half *)sw, Y, IN, OUT, S, p, st, oa);
+    return launch_st<float>(xq, xs, Wq, (const float *)sw, Y, IN, OUT, S, p, st, oa);
 }
 
 }  // namespace gemv_mma

@@ -32,9 +32,6 @@ struct OutArgs {                    // passed by value to the GEMV kernels; peer
     int local_only = 0;             // 1 (GEMM): store only into this rank's own arena; allgather_scatter_kernel sends the slice on
 };
 
-// Set by w4a8_gemv_allgather around its call into the ordinary launch path (single host thread per device).
-inline OutArgs &current_out() { static OutArgs o; return o; }
-
 // PEER is a template parameter of the GEMV kernels: the single-GPU instantiation carries none of this code.
 template <bool PEER>
 __device__ __forceinline__ void store_out(float *Y, const OutArgs &oa, int OUT, int m, int r, float v) {

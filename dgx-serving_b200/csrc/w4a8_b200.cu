@@ -14,6 +14,7 @@
 #include "gemv_w4a8.cuh"
 #include "gemv_w4a8_mma.cuh"
 #include "gemv_w4a8_bulk.cuh"
+#include "gemv_w4a8_tc.cuh"
 #include "gemm_w4a8_tc.cuh"
 #include "gemm_w4a8_tcf.cuh"
 
@@ -158,14 +159,14 @@ W4A8_API int w4a8_glu_quantize_x_q8(const float *G, const float *U, int act, flo
     return launch_glu_quantize(G, U, act, Y, xq, xs, xsum, IN, S, (cudaStream_t)stream);
 }
 
-// GEMV kernel policy: 0 auto (one activation row with fp32 scales -> dp4a kernel, else tensor-path kernel), 1 always dp4a,
-// 2 tensor path for every S it supports.  Initialised from the environment (W4A8_GEMV = dp4a | mma), changed at
-// run time with w4a8_config("gemv_kernel", v).
+// GEMV kernel policy: 0 auto, 1 always the dp4a kernel, 2 mma.sync tensor path for every S it supports, 3 bulk-copy
+// stream for every single row it supports, 5 tcgen05 tensor path for every S it supports.  Initialised from the
+// environment (W4A8_GEMV = dp4a | mma | bulk | tc), changed at run time with w4a8_config("gemv_kernel", v).
 static int g_gemv_policy = -1;
 static int gemv_policy() {
     if (g_gemv_policy < 0) {
         const char *e = getenv("W4A8_GEMV");
-        g_gemv_policy = !e ? 0 : (e[0] == 'm' ? 2 : (e[0] == 'd' ? 1 : (e[0] == 'b' ? 3 : 0)));
+        g_gemv_policy = !e ? 0 : (e[0] == 'm' ? 2 : (e[0] == 'd' ? 1 : (e[0] == 'b' ? 3 : (e[0] == 't' ? 5 : 0))));
     }
     return g_gemv_policy;
 }
@@ -177,9 +178,25 @@ static bool gemv_use_mma(int S, int scale_dtype) {
 }
 
 // The one place that decides which GEMV kernel runs and in how many launches.  count_only != nullptr: nothing is
-// launched, *count_only receives the number of kernel launches the call would make.
+// launched, *count_only receives the number of kernel launches the call would make.  `oa` carries the peer-store
+// epilogue of the fused all-gather (oa.peers == nullptr: ordinary Y); the count and the launch are decided by this one
+// function under the same arguments.
 static int gemv_dispatch(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int IN, int OUT, int S,
-                         int scale_dtype, cudaStream_t st, int *count_only) {
+                         int scale_dtype, cudaStream_t st, int *count_only, const OutArgs &oa_in = OutArgs()) {
+    const int pol = gemv_policy();
+    if (pol == 5 && gemv_tc::supported(xq, Wq, sw, IN, S < 16 ? S : 16, scale_dtype)) {
+        // tcgen05 path (opt-in): rows in passes of up to 16, MMQ order for every S
+        if (count_only) { *count_only = (S + 15) / 16; return W4A8_OK; }
+        for (int s0 = 0; s0 < S; s0 += 16) {
+            const int s = S - s0 < 16 ? S - s0 : 16;
+            OutArgs oa = oa_in;
+            if (oa.peers) oa.y_off += (size_t)s0 * oa.ld * sizeof(float);
+            int rc = gemv_tc::launch(xq + (size_t)s0 * IN, xs + (size_t)s0 * (IN / QBLK), Wq, sw, Y + (size_t)s0 * OUT, IN, OUT, s,
+                                     scale_dtype, st, oa);
+            if (rc != W4A8_OK) return rc;
+        }
+        return W4A8_OK;
+    }
     // One row.  The bulk-copy stream and the dp4a kernel give the same bits; which is faster depends on the matrix: the
     // bulk-copy stream has the higher steady rate (6.5-6.9 TB/s against 6.0) and the larger fixed cost per launch
     // (about 2.7 against 1.1 us), so auto takes it from 96 MB of weights up (K=5120: N >= 30k, an lm_head) and for
@@ -187,12 +204,12 @@ static int gemv_dispatch(const int8_t *xq, const float *xs, const uint8_t *Wq, c
     // (10.7 against 11.0 us).  Rows shorter than 2048 elements make the bulk copies too small.  With the peer-store
     // epilogue (a rank's slice of an N-sharded matrix) the dp4a kernel's smaller fixed cost wins as well.
     const size_t wbytes = (size_t)OUT * ((size_t)IN / 2 + (size_t)(IN / QBLK) * (scale_dtype == 1 ? 2 : 4));
-    const bool bulk_auto = IN >= 2048 && !current_out().peers && (scale_dtype == 1 || wbytes >= ((size_t)96 << 20));
-    if (S == 1 && (gemv_policy() == 3 || (gemv_policy() == 0 && bulk_auto))) {
+    const bool bulk_auto = IN >= 2048 && !oa_in.peers && (scale_dtype == 1 || wbytes >= ((size_t)96 << 20));
+    if (S == 1 && (pol == 3 || (pol == 0 && bulk_auto))) {
         gemv_bulk::Plan bp;
         if (gemv_bulk::plan_for(xq, Wq, sw, IN, scale_dtype, &bp)) {
             if (count_only) { *count_only = 1; return W4A8_OK; }
-            return gemv_bulk::launch(xq, xs, Wq, sw, Y, IN, OUT, scale_dtype, bp, st);
+            return gemv_bulk::launch(xq, xs, Wq, sw, Y, IN, OUT, scale_dtype, bp, st, oa_in);
         }
     }
     if (gemv_use_mma(S, scale_dtype)) {
@@ -203,23 +220,21 @@ static int gemv_dispatch(const int8_t *xq, const float *xs, const uint8_t *Wq, c
         if (!ok && per > 8) { per = 8; ok = gemv_mma::plan_for(Wq, sw, IN, per, &plan); }
         if (ok) {
             if (count_only) { *count_only = (S + per - 1) / per; return W4A8_OK; }
-            OutArgs &oa = current_out();
             for (int s0 = 0; s0 < S; s0 += per) {
                 const int s = S - s0 < per ? S - s0 : per;
                 gemv_mma::Plan pl = plan;
                 if (s <= 8 && pl.MH == 2) gemv_mma::plan_for(Wq, sw, IN, s, &pl);
-                const size_t y_off0 = oa.y_off;
-                if (oa.peers) oa.y_off = y_off0 + (size_t)s0 * oa.ld * sizeof(float);
+                OutArgs oa = oa_in;
+                if (oa.peers) oa.y_off += (size_t)s0 * oa.ld * sizeof(float);
                 int rc = gemv_mma::launch(xq + (size_t)s0 * IN, xs + (size_t)s0 * (IN / QBLK), Wq, sw, Y + (size_t)s0 * OUT, IN, OUT, s,
-                                          scale_dtype, pl, st);
-                oa.y_off = y_off0;
+                                          scale_dtype, pl, st, oa);
                 if (rc != W4A8_OK) return rc;
             }
             return W4A8_OK;
         }
     }
     if (count_only) { *count_only = (S + GEMV_MT_MAX - 1) / GEMV_MT_MAX; return W4A8_OK; }
-    return launch_gemv(xq, xs, Wq, sw, Y, IN, OUT, S, scale_dtype, st);
+    return launch_gemv(xq, xs, Wq, sw, Y, IN, OUT, S, scale_dtype, st, oa_in);
 }
 
 // GEMM kernel policy: 0 = fp16-operand tensor-core kernel (kind::f16, exact float group dots), 1 = int8-operand kernel
@@ -234,7 +249,7 @@ static int gemm_policy() {
 }
 static int gemm_launch(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int M, int N, int K,
                        int scale_dtype, int nsplit, int gsplit, cudaStream_t st) {
-    if (gemm_policy() == 1) return gemm::launch_tc(X, xs, Wq, sw, Y, M, N, K, scale_dtype, nsplit, gsplit, st);
+    if (gemm_policy() == 1) return gemm::launch_tc(X, xs, Wq, sw, Y, M, N, K, scale_dtype, nsplit, gsplit, st, OutArgs());
     return gemmf::launch(X, xs, Wq, sw, Y, M, N, K, scale_dtype, nsplit, gsplit, st);
 }
 
@@ -246,7 +261,8 @@ W4A8_API int w4a8_config(const char *key, int value) {
         return W4A8_OK;
     }
     if (!strcmp(key, "gemv_kernel")) {
-        if (value < 0 || value > 3) return fail(W4A8_ERR_ARG, "config: gemv_kernel = 0 (auto), 1 (dp4a), 2 (tensor path), 3 (bulk-copy stream for S = 1); got %d", value);
+        if (value < 0 || value > 5 || value == 4)
+            return fail(W4A8_ERR_ARG, "config: gemv_kernel = 0 (auto), 1 (dp4a), 2 (mma.sync tensor path), 3 (bulk-copy stream for S = 1), 5 (tcgen05 tensor path); got %d", value);
         g_gemv_policy = value;
         return W4A8_OK;
     }
@@ -276,7 +292,7 @@ W4A8_API int w4a8_gemv_multi(const int8_t *xq, const float *xs, int count, const
     if (!Wq || !sw || !Y || !OUT) return fail(W4A8_ERR_ARG, "gemv_multi: null array argument");
     // One launch when every matrix can take the bulk-copy stream (one row, the auto policy's conditions); else the
     // matrices go one after the other through w4a8_gemv.  Either way each output equals w4a8_gemv's, bit for bit.
-    bool one = S == 1 && !current_out().peers && (gemv_policy() == 3 || (gemv_policy() == 0 && IN >= 2048));
+    bool one = S == 1 && (gemv_policy() == 3 || (gemv_policy() == 0 && IN >= 2048));
     gemv_bulk::Plan bp;
     gemv_bulk::Mats m = {};
     for (int i = 0; i < count && one; i++) {
@@ -689,17 +705,22 @@ W4A8_API int w4a8_gemv_allgather(const int8_t *xq, const float *xs, const uint8_
     if (S > 0 && rows > 0) {
         int rc = check_common(xq, xs, Wq, sw, Ylocal, IN, scale_dtype, "gemv_allgather");
         if (rc != W4A8_OK) return rc;
-        rc = gemv_dispatch(xq, xs, Wq, sw, Ylocal, IN, rows, S, scale_dtype, st, &launches);
+        if (!aligned(xq, 4) || !aligned(Wq, 4)) return fail(W4A8_ERR_ALIGN, "gemv_allgather: xq and Wq must be 4-byte aligned");
+        rc = require_sm100();
         if (rc != W4A8_OK) return rc;
     } else {
         launches = 0;
     }
-    OutArgs &oa = current_out();
+    OutArgs oa;
     oa.peers = a->desc_dev; oa.y_off = y_offset; oa.ld = ldY; oa.col0 = row0; oa.epoch = epoch;
-    oa.publish = launches == 1 ? 1 : 0;
     int rc = W4A8_OK;
-    if (launches > 0) rc = w4a8_gemv(xq, xs, Wq, sw, Ylocal, IN, rows, S, scale_dtype, stream);
-    oa = OutArgs();
+    if (launches > 0) {
+        // how many launches, and which kernel, are decided by the same function under the same arguments
+        rc = gemv_dispatch(xq, xs, Wq, sw, Ylocal, IN, rows, S, scale_dtype, st, &launches, oa);
+        if (rc != W4A8_OK) return rc;
+        oa.publish = launches == 1 ? 1 : 0;
+        rc = gemv_dispatch(xq, xs, Wq, sw, Ylocal, IN, rows, S, scale_dtype, st, nullptr, oa);
+    }
     if (rc != W4A8_OK) return rc;
     if (launches != 1) {   // several passes (or nothing to compute): publish once they are all complete
         allgather_publish_kernel<<<1, 32, 0, st>>>(a->desc_dev, epoch);
@@ -730,11 +751,10 @@ W4A8_API int w4a8_gemm_allgather(const int8_t *X, const float *xs, const uint8_t
     // finished slice on with row-contiguous 16-byte stores; or (W4A8_GEMM_ALLGATHER=stores) the GEMM's epilogue stores
     // every tile into every arena itself, which overlaps with the compute but offers NVLink only 16-byte pieces.
     static const bool direct = [] { const char *e = getenv("W4A8_GEMM_ALLGATHER"); return e && e[0] == 's'; }();
-    OutArgs &oa = current_out();
+    OutArgs oa;
     oa.peers = a->desc_dev; oa.y_off = y_offset; oa.ld = ldY; oa.col0 = row0; oa.epoch = epoch;
     oa.publish = direct ? 1 : 0; oa.local_only = direct ? 0 : 1;
-    rc = gemm::launch_tc(X, xs, Wq, sw, Ylocal, M, rows, K, scale_dtype, 1, K / QBLK, st);   // the int8 kernel carries the peer epilogue
-    oa = OutArgs();
+    rc = gemm::launch_tc(X, xs, Wq, sw, Ylocal, M, rows, K, scale_dtype, 1, K / QBLK, st, oa);   // the int8 kernel carries the peer epilogue
     if (rc != W4A8_OK || direct) return rc;
     const long units = (long)M * ((((long)ldY | row0 | rows) & 3) == 0 ? rows / 4 : rows);
     long want = (units + 255) / 256, cap = (long)sm_count() * 4;

@@ -88,16 +88,22 @@ GEMV_SHAPES = [(1024, 256, 1), (1024, 2048, 1), (3584, 1024, 1), (1024, 4096, 5)
 def gemv_expected(oracle, xq, xs, Wq, sw, policy=0):
     """The documented fp32 order of w4a8_gemv.  A single row goes through the dp4a kernel or the bulk-copy stream, which
     share one chain order (auto picks by size and scale type; policy 3 forces the bulk-copy stream, 1 the dp4a kernel);
-    the tensor-path kernel (MMQ order) serves S >= 2, and S = 1 with fp16 scales when the bulk-copy stream does not
-    take the row (K outside 2048..8192), when K % 256 == 0; the dp4a kernel everything else."""
+    the mma.sync tensor-path kernel (MMQ order, kernels/gemm_mmq.cuh:104-105) serves S >= 2, and S = 1 with fp16 scales
+    when the bulk-copy stream does not take the row (K outside 2048..8192), when K % 256 == 0; the dp4a kernel everything
+    else.  Policy 5 = the tcgen05 tensor path (MMQ order for every S) where K % 128 == 0 (K % 256 == 0 with fp16
+    scales), else the dp4a kernel."""
     S, K = xq.shape
     fp16 = sw.dtype == np.float16
+    if policy == 5:
+        if K % (256 if fp16 else 128) == 0:
+            return oracle.gemm_mmq_w4a8(xq, xs, Wq, sw)
+        policy = 1
     bulk = S == 1 and K % (256 if fp16 else 128) == 0 and K <= 8192 and (policy == 3 or (policy == 0 and K >= 2048))
     mma = not bulk and K % 256 == 0 and (policy == 2 or (policy == 0 and (S >= 2 or fp16)))
     return oracle.gemm_mmq_w4a8(xq, xs, Wq, sw) if mma else oracle.gemv_b200_order(xq, xs, Wq, sw)
 
 
-@pytest.mark.parametrize("policy", [0, 1, 2, 3])
+@pytest.mark.parametrize("policy", [0, 1, 2, 3, 5])
 @pytest.mark.parametrize("scale_dtype", [0, 1])
 @pytest.mark.parametrize("IN,OUT,S", GEMV_SHAPES)
 def test_gemv_parity(w4a8, oracle, cuda, IN, OUT, S, scale_dtype, policy):
