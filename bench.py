@@ -33,9 +33,12 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 K_DIM, N_DIM = 5120, 17408
 L2_BYTES = 126 * 1024 * 1024
-NCU_TRAFFIC = {  # dram__bytes_read.sum + dram__bytes_write.sum per launch, from profiles/ (one ncu capture each)
-    "gemv_m1": 55.77e6,   # profiles/gemv_w4a8_dp4a_m1_k5120_n17408.md (dram read + written bytes of one launch)
+NCU_TRAFFIC = {  # dram__bytes_read.sum + dram__bytes_write.sum per launch, from one ncu capture of each kernel
+    "gemv_m1": 55.77e6,   # the dp4a streaming kernel, M=1, K=5120, N=17408
 }
+# One string for both arms (the driver compares the two arms' `config.workload`).
+WORKLOAD = "W4A8 decode GEMV M=1 K=5120 N=17408, int4 group-32 weights + fp32 scales (BASELINE configs[1])"
+MIN_TIMED_MS = 20.0       # every timed leg replays its steps until at least this much device time is covered
 
 
 def load_package():
@@ -64,6 +67,13 @@ def measured_peaks():
             d = json.load(f)
         return float(d["hbm_gbs"]), float(d["bf16_tflops_sustained"]), "measured"
     return 6650.0, 1400.0, "fallback"
+
+
+def host_cores():
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except (AttributeError, OSError):
+        return max(1, os.cpu_count() or 1)
 
 
 def gemv_bytes(M, N, K, scale_bytes=4):
@@ -121,7 +131,9 @@ def run_reference(args):
     if rank != 0:
         return
     O = load_oracle()
-    cores = O.max_threads()
+    # all the cores this process may run on: torch.distributed.run exports OMP_NUM_THREADS=1, which must not
+    # decide how many threads the CPU arm gets
+    cores = host_cores()
     O.set_threads(cores)
     Wq, sw = O.make_weights(N_DIM, K_DIM, seed=20260002)
     X = O.make_activations(1, K_DIM, seed=20260102)
@@ -140,8 +152,7 @@ def run_reference(args):
         "impl": "reference", "metric": "w4a8_gemv_m1_hbm_gbps", "value": gbps, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
-        "config": {"workload": "W4A8 decode GEMV M=1 K=5120 N=17408 (BASELINE configs[1])",
-                   "sample": "%d GEMVs per step" % per_step},
+        "config": {"workload": WORKLOAD, "sample": "%d GEMVs per step" % per_step},
         "cpu_baseline": {"value": gbps, "unit": "GB/s", "cores": cores, "kind": "port",
                          "sample": "%d scalar-C GEMVs of the full shape (oracle/w4a8_oracle.c, OpenMP)" % launches},
         "e2e": {"value": gbps, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -206,10 +217,14 @@ def run_ours(args):
             return float(t.item())
         return ms
 
-    def time_steps(step_fn, steps, warmup, graph, after_fn=None):
+    timing_log = {}
+
+    def time_steps(step_fn, steps, warmup, graph, after_fn=None, tag=None, min_ms=MIN_TIMED_MS):
         """step_fn(i, stream_handle) enqueues one step; after_fn(n, stream_handle), if given, is enqueued after every
-        block of n steps (eager warm-up block, and as the last node of the captured graph).  Returns ms for exactly
-        `steps` steps (max over ranks)."""
+        block of n steps (eager warm-up block, and as the last node of the captured graph).  One block = `steps` steps
+        (a CUDA graph of them, or an eager loop); blocks are replayed back to back, each between its own pair of CUDA
+        events on the launching stream, until at least `min_ms` of device time is covered.  Returns the MEDIAN block time
+        in ms (max over ranks); the minimum and the number of blocks go to timing_log[tag]."""
         s = torch.cuda.Stream()
         with torch.cuda.stream(s):
             nw = max(warmup, 3)
@@ -218,7 +233,7 @@ def run_ours(args):
             if after_fn:
                 after_fn(nw, s.cuda_stream)
             torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            gr = None
             if graph:
                 gr = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(gr, stream=s):
@@ -226,31 +241,50 @@ def run_ours(args):
                         step_fn(i, s.cuda_stream)
                     if after_fn:
                         after_fn(steps, s.cuda_stream)
-                gr.replay()          # one untimed replay: graph upload
-                barrier()
-                e0.record(s)
-                gr.replay()
-                e1.record(s)
-            else:
-                barrier()
-                e0.record(s)
-                for i in range(steps):
-                    step_fn(i, s.cuda_stream)
-                if after_fn:
-                    after_fn(steps, s.cuda_stream)
-                e1.record(s)
+
+            def block():
+                if gr is not None:
+                    gr.replay()
+                else:
+                    for i in range(steps):
+                        step_fn(i, s.cuda_stream)
+                    if after_fn:
+                        after_fn(steps, s.cuda_stream)
+            block()                  # one untimed block: graph upload, clocks up
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(s)
+            block()
+            e1.record(s)
+            torch.cuda.synchronize()
+            est = max_over_ranks(e0.elapsed_time(e1))
+            reps = int(min(400, max(3, np.ceil(min_ms / max(est, 1e-3)))))
+            barrier()
+            evs = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+            evs[0].record(s)
+            for r in range(reps):
+                block()
+                evs[r + 1].record(s)
             torch.cuda.synchronize()
             barrier()
-        return max_over_ranks(e0.elapsed_time(e1))
+        times = [evs[r].elapsed_time(evs[r + 1]) for r in range(reps)]
+        med, mn = max_over_ranks(float(np.median(times))), max_over_ranks(float(np.min(times)))
+        if tag:
+            timing_log[tag] = {"blocks": reps, "steps_per_block": steps, "ms_per_step_median": med / steps, "ms_per_step_min": mn / steps}
+        return med
 
     # ---- headline: GEMV M=1 (N-sharded + all-gather when world > 1) -------------------------------------
-    def gemv_case(M, steps, warmup, mode="fused"):
+    def gemv_case(M, steps, warmup, mode="fused", tag=None):
         """One step = the rank-local GEMV plus (world > 1) the exchange that leaves the whole Y[M, N] on every rank:
         mode "fused": peer stores from the GEMV epilogue + flag wait (w4a8_gemv_allgather / w4a8_allgather_wait);
         mode "nccl":  GEMV into a local slice, then an NCCL all-gather."""
         Xh, Xd, xq, xs, xsum = make_x(M)
         Yloc = torch.empty((M, rows), dtype=torch.float32, device=dev)
         after = None
+        check = None
+        # consecutive steps alternate between two Y buffers: a block of an odd number of steps is captured twice over, so
+        # that the last step of one replay and the first of the next never share a buffer
+        blk = steps if (steps % 2 == 0 or not (world > 1 and mode == "fused")) else 2 * steps
         if world > 1 and mode == "fused":
             ystride = (M * N * 4 + 255) // 256 * 256
             arena = w.Arena(2 * ystride, rank, world)
@@ -260,8 +294,8 @@ def run_ours(args):
             dist.barrier()
 
             def step(i, st):
-                arena.gemv_allgather(xq, xs, Wqs[i % nbuf], sws[i % nbuf], (i % 2) * ystride, K, rows, row0, N, M, 0, i + 1, st)
-                arena.wait(i + 1, 2000000, st)
+                # one call: the rank-local GEMV, the push of its slice to every peer, and the wait for every peer's slice
+                arena.gemv_allgather_sync(xq, xs, Wqs[i % nbuf], sws[i % nbuf], (i % 2) * ystride, K, rows, row0, N, M, 0, i + 1, 2000000, st)
 
             def after(n, st):
                 arena.advance_epoch(n, st)
@@ -270,44 +304,88 @@ def run_ours(args):
                 w.launch_gemv_w4a8_sb(xq, xs, Wqs[i % nbuf], sws[i % nbuf], Yloc, K, rows, M, 0, st)
                 if world > 1:
                     sharded.all_gather_columns(Yloc, plan)     # NCCL all-gather -> Y[M, N] on every rank
-        ms = time_steps(step, steps, warmup, graph=(world == 1 or mode == "fused"), after_fn=after)
+        ms = time_steps(step, blk, warmup, graph=(world == 1 or mode == "fused"), after_fn=after, tag=tag) * steps / blk
         if world > 1 and mode == "fused":
             w.device_status()
             barrier()
+            # outside the timed region: one more fused step, its gathered Y compared bit for bit with the NCCL path's
+            st0 = torch.cuda.current_stream().cuda_stream
+            arena.gemv_allgather_sync(xq, xs, Wqs[0], sws[0], 0, K, rows, row0, N, M, 0, 1, 2000000, st0)
+            arena.advance_epoch(1, st0)
+            w.launch_gemv_w4a8_sb(xq, xs, Wqs[0], sws[0], Yloc, K, rows, M, 0, st0)
+            Yn = sharded.all_gather_columns(Yloc, plan)
+            torch.cuda.synchronize()
+            w.device_status()
+            same = bool(torch.equal(arena.tensor(0, (M, N)), Yn.reshape(M, N)))
+            t = torch.tensor([1 if same else 0], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            check = "bitwise equal to the NCCL all-gather path on every rank" if int(t.item()) == 1 else "MISMATCH against the NCCL path"
+            barrier()
             arena.close()
         total_bytes = gemv_bytes(M, N, K)          # all ranks together stream the whole matrix once per step
-        return ms, total_bytes * steps / (ms * 1e-3) / 1e9, (Xh, Xd, xq, xs, xsum)
+        return ms, total_bytes * steps / (ms * 1e-3) / 1e9, (Xh, Xd, xq, xs, xsum), check
 
     sampler = ClockSampler(local) if rank == 0 else None
-    ms, gbps, xin = gemv_case(1, args.steps, args.warmup)
+    ms, gbps, xin, gather_check = gemv_case(1, args.steps, args.warmup, tag="headline")
     clocks = sampler.stop() if sampler else None
 
     # kernel-only time of this rank's GEMV (no collective), for the roofline of the dominant kernel
     Xh, Xd, xq, xs, xsum = xin
     Yloc = torch.empty((1, rows), dtype=torch.float32, device=dev)
     ms_k = time_steps(lambda i, st: w.launch_gemv_w4a8_sb(xq, xs, Wqs[i % nbuf], sws[i % nbuf], Yloc, K, rows, 1, 0, st),
-                      args.steps, args.warmup, graph=True)
+                      args.steps, args.warmup, graph=True, tag="kernel_only")
     per_launch_us = ms_k * 1e3 / args.steps
     achieved = gemv_bytes(1, rows, K) / (per_launch_us * 1e-6) / 1e9
 
     # ---- e2e: host fp32 activations in, host fp32 outputs back, through w4a8_linear ------------------------
-    Yh = torch.empty((1, rows), dtype=torch.float32).pin_memory()
     e2e_steps = max(10, min(args.steps, 200))
+    if world == 1:
+        Yh = torch.empty((1, rows), dtype=torch.float32).pin_memory()
 
-    def e2e_step(i, st):
-        # one C-ABI call: H2D of X, quantize_x + GEMV, D2H of Y, stream synchronise (the caller reads Y on the host)
-        w.linear_host(Xh, Yh, Xd, xq, xs, xsum, Yloc, Wqs[i % nbuf], sws[i % nbuf], 1, rows, K, 0, st)
-    ms_e = time_steps(e2e_step, e2e_steps, 3, graph=False)
+        def e2e_step(i, st):
+            # one C-ABI call: H2D of X, quantize_x + GEMV, D2H of Y, stream synchronise (the caller reads Y on the host)
+            w.linear_host(Xh, Yh, Xd, xq, xs, xsum, Yloc, Wqs[i % nbuf], sws[i % nbuf], 1, rows, K, 0, st)
+        ms_e = time_steps(e2e_step, e2e_steps, 3, graph=False, tag="e2e")
+        e2e_path = "w4a8_linear_host: pinned host X -> quantize_x + gemv -> pinned host Y, one C-ABI call per step"
+    else:
+        # sharded: host X in on every rank, quantize_x, the rank's GEMV with the fused exchange, and the WHOLE gathered
+        # Y[1, N] back to the host on every rank; stream synchronised every step
+        Yh = torch.empty((1, N), dtype=torch.float32).pin_memory()
+        estride = (N * 4 + 255) // 256 * 256
+        earena = w.Arena(2 * estride, rank, world)
+        ehandles = [None] * world
+        dist.all_gather_object(ehandles, earena.export_handle())
+        earena.connect_handles(ehandles)
+        dist.barrier()
+        ecount = [0]
+
+        def e2e_step(i, st):
+            ecount[0] += 1
+            ts = torch.cuda.current_stream()
+            Xd.copy_(Xh, non_blocking=True)
+            w.launch_quantize_x_q8(Xd, xq, xs, xsum, K, 1, st)
+            off = (ecount[0] % 2) * estride
+            earena.gemv_allgather_sync(xq, xs, Wqs[i % nbuf], sws[i % nbuf], off, K, rows, row0, N, 1, 0, ecount[0], 2000000, st)
+            Yh.copy_(earena.tensor(off, (1, N)), non_blocking=True)
+            ts.synchronize()
+        ms_e = time_steps(e2e_step, e2e_steps, 3, graph=False, tag="e2e")
+        w.device_status()
+        barrier()
+        earena.close()
+        e2e_path = ("pinned host X -> H2D -> quantize_x -> w4a8_gemv_allgather_sync (rank's rows, slice pushed to every peer, wait for "
+                    "every peer) -> D2H of the whole gathered Y[1, N] -> stream synchronise, on every rank")
     e2e_gbps = gemv_bytes(1, N, K) * e2e_steps / (ms_e * 1e-3) / 1e9
 
     extra = {}
     if world > 1:
-        ms_n, gb_n, _ = gemv_case(1, args.steps, args.warmup, mode="nccl")
+        ms_n, gb_n, _, _ = gemv_case(1, args.steps, args.warmup, mode="nccl")
         extra["nccl_allgather_path"] = {"ms_per_step": ms_n / args.steps, "gbps": gb_n}
+        extra["fused_allgather_check_m1"] = gather_check
+        extra["rank_local_kernel_us"] = per_launch_us
         sw_ = {}
         for M in (8, 16):
-            ms_m, gb_m, _ = gemv_case(M, max(20, args.steps // 2), 3)
-            sw_[str(M)] = {"us": ms_m * 1e3 / max(20, args.steps // 2), "gbps": gb_m}
+            ms_m, gb_m, _, chk = gemv_case(M, max(20, args.steps // 2), 3)
+            sw_[str(M)] = {"us": ms_m * 1e3 / max(20, args.steps // 2), "gbps": gb_m, "check": chk}
         extra["gemv_sweep_fused_allgather"] = sw_
         # ---- N-sharded prefill GEMM M=2048: quantize_x + GEMM on the rank's rows; Y[M, N] complete on every rank either by
         # peer stores from the GEMM epilogue + flag wait (w4a8_gemm_allgather) or by an NCCL all-gather of the slices ----------
@@ -325,8 +403,7 @@ def run_ours(args):
         def gemm_fused(i, st):
             gepoch[0] += 1
             w.launch_quantize_x_q8(Xd2, xq2, xs2, xsum2, K, Mg, st)
-            garena.gemm_allgather(xq2, xs2, Wqs[i % nbuf], sws[i % nbuf], (gepoch[0] % 2) * gstride, Mg, rows, row0, N, K, 0, gepoch[0], st)
-            garena.wait(gepoch[0], 5000000, st)
+            garena.gemm_allgather_sync(xq2, xs2, Wqs[i % nbuf], sws[i % nbuf], (gepoch[0] % 2) * gstride, Mg, rows, row0, N, K, 0, gepoch[0], 5000000, st)
 
         def gemm_nccl(i, st):
             w.linear(Xd2, xq2, xs2, xsum2, Wqs[i % nbuf], sws[i % nbuf], Yl2, Mg, rows, K, 0, 0, st)
@@ -351,16 +428,16 @@ def run_ours(args):
         sweep = {"1": {"us": per_launch_us, "gbps": achieved, "frac_of_measured_hbm": achieved / hbm_peak,
                        "frac_of_8tbs": achieved / 8000.0}}
         for M in (2, 4, 8, 16):
-            ms_m, gb_m, _ = gemv_case(M, max(20, args.steps // 2), 3)
+            ms_m, gb_m, _, _ = gemv_case(M, max(20, args.steps // 2), 3)
             us = ms_m * 1e3 / max(20, args.steps // 2)
             sweep[str(M)] = {"us": us, "gbps": gb_m, "frac_of_measured_hbm": gb_m / hbm_peak, "frac_of_8tbs": gb_m / 8000.0}
         extra["gemv_sweep_k5120_n17408"] = sweep
         # ---- prefill GEMM, quantize_x inside the timed region (BASELINE configs[3]) ------------------------
-        gemm = {}
-        for M in (512, 2048):
+        gemm, quant = {}, {}
+        for M in (512, 2048, 8192):
             Xh2, Xd2, xq2, xs2, xsum2 = make_x(M, outliers=True)
             Y2 = torch.empty((M, N), dtype=torch.float32, device=dev)
-            st_n = 5
+            st_n = 5 if M < 8192 else 3
             ms_g = time_steps(lambda i, st: w.linear(Xd2, xq2, xs2, xsum2, Wqs[i % nbuf], sws[i % nbuf], Y2, M, N, K, 0, 0, st),
                               st_n, 3, graph=False)
             w.device_status()
@@ -369,7 +446,18 @@ def run_ours(args):
             gemm[str(M)] = {"us": us, "int8_tops": tops, "frac_of_nominal_4500": tops / 4500.0,
                             "frac_of_2x_measured_bf16": tops / (2.0 * bf16_peak)}
             del Y2
+            if M >= 2048:
+                # ---- quantize_x alone (HBM-bound, 5.25 bytes per element): rotating inputs larger than L2 -------------
+                nx = max(2, int(np.ceil(1.5 * L2_BYTES / (M * K * 4.0))))
+                Xs_ = [Xd2] + [torch.randn(M, K, device=dev, generator=g) for _ in range(nx - 1)]
+                ms_q = time_steps(lambda i, st: w.launch_quantize_x_q8(Xs_[i % nx], xq2, xs2, xsum2, K, M, st), 20, 3, graph=True)
+                us_q = ms_q * 1e3 / 20
+                qb = 5.25 * M * K
+                quant[str(M)] = {"us": us_q, "gbps": qb / (us_q * 1e-6) / 1e9, "frac_of_measured_hbm": qb / (us_q * 1e-6) / 1e9 / hbm_peak,
+                                 "algorithmic_bytes": qb}
+                del Xs_
         extra["gemm_quantize_included_k5120_n17408"] = gemm
+        extra["quantize_x_k5120"] = quant
         # ---- fp16 weight scales (scale_dtype 1), M=1: 10 % fewer bytes per launch --------------------------------
         sws16 = [t.half() for t in sws]
         ms_h = time_steps(lambda i, st: w.launch_gemv_w4a8_sb(xq, xs, Wqs[i % nbuf], sws16[i % nbuf], Yloc, K, N, 1, 1, st),
@@ -456,6 +544,30 @@ def run_ours(args):
                 ref.ref_quantize_x_q8(P(Xd2), P(xq2), P(xs2), P(xsum2), K, 2048, ctypes.c_void_p(st))
                 ref.ref_gemm_mmq_w4a8(P(xq2), P(xs2), P(Wqs[i % nbuf]), P(sws[i % nbuf]), P(Y2), 2048, N, K, 0, ctypes.c_void_p(st))
             ms_rg = time_steps(ref_gemm, 3, 3, graph=False)
+            refk = {}
+            # the reference's batched decode kernels on the same buffers (a6: SB for 2..15 rows, a8: gemm_batch<16>)
+            for Mr in (2, 4, 8, 16):
+                Xr_, Xdr_, xqr, xsr, xsumr = make_x(Mr)
+                Yr = torch.empty((Mr, N), dtype=torch.float32, device=dev)
+                ms_sb = time_steps(lambda i, st: ref.ref_gemv_w4a8_sb(P(xqr), P(xsr), P(Wqs[i % nbuf]), P(sws[i % nbuf]), P(Yr), K, N, Mr, 0,
+                                                                      ctypes.c_void_p(st)), 20, 3, graph=True)
+                refk["gemv_w4a8_sb_m%d" % Mr] = {"us": ms_sb * 1e3 / 20}
+                if Mr == 16:
+                    ms_gb = time_steps(lambda i, st: ref.ref_gemm_batch_w4a8(P(xqr), P(xsr), P(Wqs[i % nbuf]), P(sws[i % nbuf]), P(Yr), K, N, 16, 0,
+                                                                             ctypes.c_void_p(st)), 20, 3, graph=True)
+                    refk["gemm_batch_w4a8_m16"] = {"us": ms_gb * 1e3 / 20}
+                del Yr
+            # the tile variants the graphs actually call for prefill (a11: 256x64 template, a12: raster order 1), kernel only
+            for nm, fn_ in (("gemm_mmq_tmpl_256x64_m2048", lambda i, st: ref.ref_gemm_mmq_256x64(P(xq2), P(xs2), P(Wqs[i % nbuf]), P(sws[i % nbuf]), P(Y2),
+                                                                                               2048, N, K, 0, ctypes.c_void_p(st))),
+                            ("gemm_mmq_raster1_m2048", lambda i, st: ref.ref_gemm_mmq_raster_w4a8(P(xq2), P(xs2), P(Wqs[i % nbuf]), P(sws[i % nbuf]), P(Y2),
+                                                                                                 2048, N, K, 0, 1, 8, ctypes.c_void_p(st))),
+                            ("gemm_mmq_128x128_m2048", lambda i, st: ref.ref_gemm_mmq_w4a8(P(xq2), P(xs2), P(Wqs[i % nbuf]), P(sws[i % nbuf]), P(Y2),
+                                                                                          2048, N, K, 0, ctypes.c_void_p(st)))):
+                ms_t = time_steps(fn_, 3, 3, graph=False)
+                refk[nm] = {"us": ms_t * 1e3 / 3, "int8_tops": 2.0 * 2048 * N * K / (ms_t / 3 * 1e-3) / 1e12}
+            ms_rq = time_steps(lambda i, st: ref.ref_quantize_x_q8(P(Xd2), P(xq2), P(xs2), P(xsum2), K, 2048, ctypes.c_void_p(st)), 20, 3, graph=True)
+            refk["quantize_x_q8_m2048"] = {"us": ms_rq * 1e3 / 20, "gbps": 5.25 * 2048 * K / (ms_rq / 20 * 1e-3) / 1e9}
             # ---- quantize_x fused into its producer, against the reference's two kernels (decode, one row) -----------
             ref.ref_rmsnorm.restype = ctypes.c_int
             ref.ref_glu.restype = ctypes.c_int
@@ -482,15 +594,15 @@ def run_ours(args):
                 us_t = time_steps(theirs, 100, 3, graph=True) * 1e3 / 100
                 fused[name] = {"us_fused": us_o, "us_reference_two_kernels": us_t}
             extra["fused_quantize_m1"] = fused
-            extra["reference_kernels_sm100a"] = {
-                "gemv_w4a8_mlp2_m1": {"us": us_r, "gbps": gemv_bytes(1, N, K) / (us_r * 1e-6) / 1e9},
-                "quantize+gemm_mmq_m2048": {"us": ms_rg * 1e3 / 3, "int8_tops": 2.0 * 2048 * N * K / (ms_rg / 3 * 1e-3) / 1e12}}
+            refk["gemv_w4a8_mlp2_m1"] = {"us": us_r, "gbps": gemv_bytes(1, N, K) / (us_r * 1e-6) / 1e9}
+            refk["quantize+gemm_mmq_m2048"] = {"us": ms_rg * 1e3 / 3, "int8_tops": 2.0 * 2048 * N * K / (ms_rg / 3 * 1e-3) / 1e12}
+            extra["reference_kernels_sm100a"] = refk
             del Y2
 
     cpu_baseline = None
     if world == 1:
         O = load_oracle()
-        cores = O.max_threads()
+        cores = host_cores()
         O.set_threads(cores)
         Wq_h, sw_h = Wqs[0].cpu().numpy(), sws[0].cpu().numpy()
         xq_h, xs_h = xq.cpu().numpy(), xs.cpu().numpy()
@@ -508,19 +620,21 @@ def run_ours(args):
             "metric": "w4a8_gemv_m1_hbm_gbps", "value": gbps, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "i8", "data": "synthetic",
-            "config": {"workload": "W4A8 decode GEMV M=1 K=5120 N=17408, int4 group-32 weights + fp32 scales (BASELINE configs[1])",
-                       "parallelism": ("n-shard x%d, all-gather fused into the GEMV epilogue (peer stores over NVLink + flag wait)" % world)
+            "config": {"workload": WORKLOAD,
+                       "parallelism": ("n-shard x%d, all-gather fused into the GEMV (last CTA pushes the slice to every peer over NVLink, flags, in-kernel wait)" % world)
                        if world > 1 else "single GPU",
                        "l2": "rotating %d distinct weight copies per rank (%.0f MB > 126 MB L2)" % (nbuf, nbuf * shard_bytes / 1e6),
-                       "launch": "CUDA graph of %d steps" % args.steps},
+                       "launch": "CUDA graph of %d steps, replayed %d times (>= %.0f ms timed); value from the median replay, min in `timing`"
+                                 % (timing_log["headline"]["steps_per_block"], timing_log["headline"]["blocks"], MIN_TIMED_MS)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": NCU_TRAFFIC["gemv_m1"] if world == 1 else None, "peak_kind": "of " + peak_kind,
                          "kernel": "gemv_w4a8_dp4a_kernel (w4a8_gemv, M=1, auto policy), rank-local slice of %d rows" % rows, "us_per_launch": per_launch_us,
                          "algorithmic_bytes_per_launch": gemv_bytes(1, rows, K), "frac_of_nominal_8tbs": achieved / 8000.0},
             "cpu_baseline": cpu_baseline,
-            "e2e": {"value": e2e_gbps, "unit": "GB/s", "h2d_bytes_per_step": K * 4, "d2h_bytes_per_step": rows * 4,
-                    "ms_per_step": ms_e / e2e_steps, "path": "w4a8_linear_host: pinned host X -> quantize_x + gemv -> pinned host Y, one C-ABI call per step"},
-            "gpu_launches": args.steps * (1 if world == 1 else 2),
+            "e2e": {"value": e2e_gbps, "unit": "GB/s", "h2d_bytes_per_step": K * 4, "d2h_bytes_per_step": (rows if world == 1 else N) * 4,
+                    "ms_per_step": ms_e / e2e_steps, "path": e2e_path},
+            "gpu_launches": args.steps,
+            "timing": {k: timing_log[k] for k in ("headline", "kernel_only", "e2e") if k in timing_log},
             "clocks": clocks,
             "extra": extra,
         }

@@ -68,6 +68,8 @@ _SIGNATURES = {
     "w4a8_gemv_allgather": (_I, [_P, _P, _P, _P, _P, _Z, _I, _I, _I, _I, _I, _I, ctypes.c_uint32, _P]),
     "w4a8_gemm_allgather": (_I, [_P, _P, _P, _P, _P, _Z, _I, _I, _I, _I, _I, _I, ctypes.c_uint32, _P]),
     "w4a8_allgather_wait": (_I, [_P, ctypes.c_uint32, _I, _P]),
+    "w4a8_gemv_allgather_sync": (_I, [_P, _P, _P, _P, _P, _Z, _I, _I, _I, _I, _I, _I, ctypes.c_uint32, _I, _P]),
+    "w4a8_gemm_allgather_sync": (_I, [_P, _P, _P, _P, _P, _Z, _I, _I, _I, _I, _I, _I, ctypes.c_uint32, _I, _P]),
     "w4a8_arena_advance_epoch": (_I, [_P, ctypes.c_uint32, _P]),
 }
 EXPORTS = tuple(_SIGNATURES)
@@ -288,6 +290,15 @@ class Arena:
     def gemm_allgather(self, X, xs, Wq, sw, y_offset, M, rows, row0, ldY, K, scale_dtype, epoch, stream=None):
         _check(lib().w4a8_gemm_allgather(_ptr(X), _ptr(xs), _ptr(Wq), _ptr(sw), self.handle, y_offset, M, rows, row0, ldY, K,
                                          scale_dtype, epoch, _stream(stream)))
+
+    def gemv_allgather_sync(self, xq, xs, Wq, sw, y_offset, IN, rows, row0, ldY, S, scale_dtype, epoch, timeout_us=1000000, stream=None):
+        """gemv_allgather with the wait folded into its last kernel: when that kernel completes, Y is complete here."""
+        _check(lib().w4a8_gemv_allgather_sync(_ptr(xq), _ptr(xs), _ptr(Wq), _ptr(sw), self.handle, y_offset, IN, rows, row0, ldY, S,
+                                              scale_dtype, epoch, timeout_us, _stream(stream)))
+
+    def gemm_allgather_sync(self, X, xs, Wq, sw, y_offset, M, rows, row0, ldY, K, scale_dtype, epoch, timeout_us=1000000, stream=None):
+        _check(lib().w4a8_gemm_allgather_sync(_ptr(X), _ptr(xs), _ptr(Wq), _ptr(sw), self.handle, y_offset, M, rows, row0, ldY, K,
+                                              scale_dtype, epoch, timeout_us, _stream(stream)))
 
     def wait(self, epoch, timeout_us=1000000, stream=None):
         _check(lib().w4a8_allgather_wait(self.handle, epoch, timeout_us, _stream(stream)))

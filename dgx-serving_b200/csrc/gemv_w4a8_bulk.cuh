@@ -34,7 +34,16 @@ constexpr int RPW = W4A8_BULK_RPW;      // rows per warp and stage, processed in
 constexpr int ROWS = CW * RPW;          // weight rows per ring stage
 constexpr int MAX_STAGES = 8;
 constexpr int BAR_BYTES = 256;          // full[MAX_STAGES], empty[MAX_STAGES], padding
-constexpr int THREADS = (CW + 1) * 32;
+// Consumer warps come in G groups of CW; group g takes the ring stages g, g + G, ...  A consumer warp needs about two
+// thousand cycles per row (shared-memory loads, the dp4a chain, the barrier hand-offs), longer than the copies need to
+// deliver a stage, so one group alone leaves HBM waiting for the consumers; two groups work on two stages at once.
+// The ring depth is a multiple of G, so a ring slot is always used by the same group, use after use (a parity wait
+// on an mbarrier may never be more than one phase ahead).
+#ifndef W4A8_BULK_GROUPS
+#define W4A8_BULK_GROUPS 2
+#endif
+constexpr int MAX_G = W4A8_BULK_GROUPS;
+constexpr int THREADS = (MAX_G * CW + 1) * 32;
 
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -64,7 +73,7 @@ struct Mats {
 // PEER: outputs go to every rank's arena and the last CTA publishes the step's epoch (peer_allgather.cuh); single matrix.
 template <int NG, typename ST, bool PEER>
 __global__ void __launch_bounds__(THREADS) gemv_w4a8_bulk_kernel(
-    const int8_t *__restrict__ xq, const float *__restrict__ xs, const Mats mats, int IN, int nstages, OutArgs oa) {
+    const int8_t *__restrict__ xq, const float *__restrict__ xs, const Mats mats, int IN, int nstages, int G, OutArgs oa) {
     int mi = 0;
     while (mi + 1 < mats.count && (int)blockIdx.x >= mats.cta0[mi + 1]) mi++;
     const uint8_t *__restrict__ Wq = mats.Wq[mi];
@@ -94,7 +103,7 @@ __global__ void __launch_bounds__(THREADS) gemv_w4a8_bulk_kernel(
     __syncthreads();
     pdl_launch_dependents();
 
-    if (warp == CW) {
+    if (warp == G * CW) {
         // ---------------- producer: one thread, weights and scales only (no dependency on the previous kernel) ----
         if (lane == 0) {
             Ring r(nstages);
@@ -140,10 +149,12 @@ __global__ void __launch_bounds__(THREADS) gemv_w4a8_bulk_kernel(
 #pragma unroll
             for (int i = 0; i < 4; i++) split_even_odd(v[2 * i], v[2 * i + 1], xe[j][i], xo[j][i]);
         }
-        Ring r(nstages);
-        for (int c = 0; c < nchunks; c++) {
+        const int grp = warp / CW, lw = warp - grp * CW;        // group and warp inside the group
+        for (int c = grp; c < nchunks; c += G) {
+            Ring r(nstages);
+            r.stage = c % nstages; r.phase = (uint32_t)(c / nstages) & 1u;
             if (!ptx::mbar_wait_warp(FULL(r.stage), r.phase)) { dev_set_error(0x400u | 2u); break; }
-            const int row = r0 + c * ROWS + warp;              // this warp's rows: row + CW * i
+            const int row = r0 + c * ROWS + lw;                // this warp's rows: row + CW * i
             if (row < r1) {
                 const unsigned char *stage_p = ring + (size_t)r.stage * stage_bytes;
                 float acc[RPW];
@@ -155,7 +166,7 @@ __global__ void __launch_bounds__(THREADS) gemv_w4a8_bulk_kernel(
                     if (b < nb) {
 #pragma unroll
                         for (int i = 0; i < RPW; i++) {
-                            const int lr = warp + CW * i;          // row inside the stage (rows past r1 hold stale bytes: never stored)
+                            const int lr = lw + CW * i;            // row inside the stage (rows past r1 hold stale bytes: never stored)
                             const uint4 wv = *reinterpret_cast<const uint4 *>(stage_p + (size_t)lr * wrow + (size_t)b * 16);
                             const float s = sval(reinterpret_cast<const ST *>(stage_p + (size_t)ROWS * wrow + (size_t)lr * srow)[b]);
                             uint32_t e0, o0, e1, o1, e2, o2, e3, o3;
@@ -186,13 +197,12 @@ __global__ void __launch_bounds__(THREADS) gemv_w4a8_bulk_kernel(
             }
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(EMPTY(r.stage));
-            r.advance();
         }
     }
-    publish_out<PEER>(oa, lane == 0 && warp < CW);
+    publish_out<PEER>(oa, lane == 0 && warp < G * CW);
 }
 
-struct Plan { int NG, stages, ctas_per_sm; size_t smem; };
+struct Plan { int NG, stages, ctas_per_sm, groups; size_t smem; };
 
 // Ring depth and residency for a row of IN elements, or false when the shape is not served here.
 inline bool plan_for(const void *xq, const void *Wq, const void *sw, int IN, int scale_dtype, Plan *p) {
@@ -210,7 +220,12 @@ inline bool plan_for(const void *xq, const void *Wq, const void *sw, int IN, int
     if (st > (occ == 1 ? 4 : MAX_STAGES)) st = occ == 1 ? 4 : MAX_STAGES;   // one CTA per SM: deeper than 4 stages measured slower
     if (want_st > 0 && want_st < st) st = want_st;
     if (st < 2) return false;
-    p->NG = (nb + 31) / 32; p->stages = st; p->ctas_per_sm = occ; p->smem = BAR_BYTES + (size_t)st * stage;
+    static const int want_g = [] { const char *e = getenv("W4A8_GEMV_BULK_GROUPS"); return e ? atoi(e) : MAX_G; }();
+    int g = want_g < 1 ? 1 : (want_g > MAX_G ? MAX_G : want_g);
+    if (occ == 2) g = 1;
+    while (g > 1 && st % g != 0) st--;                      // ring depth: a multiple of the group count
+    if (st < g) g = 1;
+    p->NG = (nb + 31) / 32; p->stages = st; p->ctas_per_sm = occ; p->groups = g; p->smem = BAR_BYTES + (size_t)st * stage;
     return true;
 }
 
@@ -243,7 +258,7 @@ inline int launch_p(const int8_t *xq, const float *xs, const Mats &mats_in, int 
         m.cta0[i + 1] = (int)end;
     }
     m.cta0[m.count] = (int)grid;
-    cudaError_t le = launch_pdl(kern, dim3((unsigned)grid), dim3(THREADS), p.smem, st, xq, xs, m, IN, p.stages, oa);
+    cudaError_t le = launch_pdl(kern, dim3((unsigned)grid), dim3((p.groups * CW + 1) * 32), p.smem, st, xq, xs, m, IN, p.stages, p.groups, oa);
     if (le != cudaSuccess) return cuda_fail(le, "gemv_w4a8_bulk launch");
     return launch_status("gemv_w4a8_bulk");
 }

@@ -692,53 +692,75 @@ W4A8_API int w4a8_ipc_close(void *dev_ptr) {
     return e == cudaSuccess ? W4A8_OK : cuda_fail(e, "cudaIpcCloseMemHandle");
 }
 
-W4A8_API int w4a8_gemv_allgather(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a, size_t y_offset,
-                                 int IN, int rows, int row0, int ldY, int S, int scale_dtype, uint32_t epoch, void *stream) {
+// Sends the finished slice on with the many-CTA copy kernel and publishes (and, wait_limit > 0, waits).
+static int launch_scatter(w4a8_arena *a, size_t y_offset, int M, int ldY, int row0, int rows, uint32_t epoch, long long wait_limit,
+                          cudaStream_t st) {
+    const long units = (long)M * ((((long)ldY | row0 | rows) & 3) == 0 ? rows / 4 : rows);
+    long want = (units + 255) / 256, cap = (long)sm_count() * 4;
+    const unsigned grid = (unsigned)(want < cap ? (want > 0 ? want : 1) : cap);
+    cudaError_t le = launch_pdl(allgather_scatter_kernel, dim3(grid), dim3(256), 0, st, (const PeerDesc *)a->desc_dev, y_offset, M, (long)ldY,
+                                (long)row0, rows, (unsigned int)epoch, wait_limit);
+    if (le != cudaSuccess) return cuda_fail(le, "allgather_scatter launch");
+    return launch_status("allgather_scatter");
+}
+static long long wait_cycles(int timeout_us) {
+    if (timeout_us <= 0) timeout_us = 1000000;
+    return (long long)timeout_us * 2000;                 // SM clock <= 2 GHz: at least timeout_us
+}
+
+static int gemv_allgather_impl(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a, size_t y_offset,
+                               int IN, int rows, int row0, int ldY, int S, int scale_dtype, uint32_t epoch, long long wait_limit,
+                               cudaStream_t st) {
     if (!a || !a->connected) return fail(W4A8_ERR_ARG, "gemv_allgather: arena not connected");
     if (S < 0 || rows < 0 || row0 < 0 || ldY < row0 + rows) return fail(W4A8_ERR_ARG, "gemv_allgather: bad shape S=%d rows=%d row0=%d ldY=%d", S, rows, row0, ldY);
     if (y_offset % 16 != 0 || y_offset + (size_t)S * ldY * sizeof(float) > a->bytes)
         return fail(W4A8_ERR_ARG, "gemv_allgather: Y[%d x %d] at offset %zu does not fit the %zu-byte arena", S, ldY, y_offset, a->bytes);
     if (IN <= 0) return fail(W4A8_ERR_ARG, "gemv_allgather: IN must be positive");
-    cudaStream_t st = (cudaStream_t)stream;
-    float *Ylocal = reinterpret_cast<float *>(a->base + y_offset);   // unused by the peer path; keeps the argument checks happy
-    int launches = 1;
-    if (S > 0 && rows > 0) {
-        int rc = check_common(xq, xs, Wq, sw, Ylocal, IN, scale_dtype, "gemv_allgather");
-        if (rc != W4A8_OK) return rc;
-        if (!aligned(xq, 4) || !aligned(Wq, 4)) return fail(W4A8_ERR_ALIGN, "gemv_allgather: xq and Wq must be 4-byte aligned");
-        rc = require_sm100();
-        if (rc != W4A8_OK) return rc;
-    } else {
-        launches = 0;
-    }
-    OutArgs oa;
-    oa.peers = a->desc_dev; oa.y_off = y_offset; oa.ld = ldY; oa.col0 = row0; oa.epoch = epoch;
-    int rc = W4A8_OK;
-    if (launches > 0) {
-        // how many launches, and which kernel, are decided by the same function under the same arguments
-        rc = gemv_dispatch(xq, xs, Wq, sw, Ylocal, IN, rows, S, scale_dtype, st, &launches, oa);
-        if (rc != W4A8_OK) return rc;
-        oa.publish = launches == 1 ? 1 : 0;
-        rc = gemv_dispatch(xq, xs, Wq, sw, Ylocal, IN, rows, S, scale_dtype, st, nullptr, oa);
-    }
-    if (rc != W4A8_OK) return rc;
-    if (launches != 1) {   // several passes (or nothing to compute): publish once they are all complete
-        allgather_publish_kernel<<<1, 32, 0, st>>>(a->desc_dev, epoch);
+    if (S == 0 || rows == 0) {                       // nothing to compute: this rank still has to publish the step
+        allgather_publish_kernel<<<1, 32, 0, st>>>(a->desc_dev, epoch, wait_limit);
         return launch_status("allgather_publish");
     }
-    return W4A8_OK;
+    float *Ylocal = reinterpret_cast<float *>(a->base + y_offset);   // unused by the peer path; keeps the argument checks happy
+    int rc = check_common(xq, xs, Wq, sw, Ylocal, IN, scale_dtype, "gemv_allgather");
+    if (rc != W4A8_OK) return rc;
+    if (!aligned(xq, 4) || !aligned(Wq, 4)) return fail(W4A8_ERR_ALIGN, "gemv_allgather: xq and Wq must be 4-byte aligned");
+    rc = require_sm100();
+    if (rc != W4A8_OK) return rc;
+    OutArgs oa;
+    oa.peers = a->desc_dev; oa.y_off = y_offset; oa.ld = ldY; oa.col0 = row0; oa.epoch = epoch;
+    oa.local_only = 1; oa.M = S; oa.cols = rows;
+    // how many launches, and which kernel, are decided by the same function under the same arguments
+    int launches = 1;
+    rc = gemv_dispatch(xq, xs, Wq, sw, Ylocal, IN, rows, S, scale_dtype, st, &launches, oa);
+    if (rc != W4A8_OK) return rc;
+    // One launch and a slice small enough for one CTA to send on: its last CTA pushes, publishes and (optionally) waits.
+    // Otherwise the launches only fill the rank's own arena and the many-CTA copy kernel does the rest.
+    const size_t push_total = (size_t)S * rows * sizeof(float) * (size_t)(a->world - 1);
+    const bool in_kernel = launches == 1 && push_total <= PUSH_MAX_BYTES;
+    if (in_kernel) { oa.publish = 1; oa.push = a->world > 1 ? 1 : 0; oa.wait_limit = wait_limit; }
+    rc = gemv_dispatch(xq, xs, Wq, sw, Ylocal, IN, rows, S, scale_dtype, st, nullptr, oa);
+    if (rc != W4A8_OK || in_kernel) return rc;
+    return launch_scatter(a, y_offset, S, ldY, row0, rows, epoch, wait_limit, st);
 }
 
-W4A8_API int w4a8_gemm_allgather(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a, size_t y_offset,
-                                 int M, int rows, int row0, int ldY, int K, int scale_dtype, uint32_t epoch, void *stream) {
+W4A8_API int w4a8_gemv_allgather(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a, size_t y_offset,
+                                 int IN, int rows, int row0, int ldY, int S, int scale_dtype, uint32_t epoch, void *stream) {
+    return gemv_allgather_impl(xq, xs, Wq, sw, a, y_offset, IN, rows, row0, ldY, S, scale_dtype, epoch, 0, (cudaStream_t)stream);
+}
+W4A8_API int w4a8_gemv_allgather_sync(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a, size_t y_offset,
+                                      int IN, int rows, int row0, int ldY, int S, int scale_dtype, uint32_t epoch, int timeout_us, void *stream) {
+    return gemv_allgather_impl(xq, xs, Wq, sw, a, y_offset, IN, rows, row0, ldY, S, scale_dtype, epoch, wait_cycles(timeout_us), (cudaStream_t)stream);
+}
+
+static int gemm_allgather_impl(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a, size_t y_offset,
+                               int M, int rows, int row0, int ldY, int K, int scale_dtype, uint32_t epoch, long long wait_limit, cudaStream_t st) {
     if (!a || !a->connected) return fail(W4A8_ERR_ARG, "gemm_allgather: arena not connected");
     if (M < 0 || rows < 0 || row0 < 0 || ldY < row0 + rows) return fail(W4A8_ERR_ARG, "gemm_allgather: bad shape M=%d rows=%d row0=%d ldY=%d", M, rows, row0, ldY);
     if (y_offset % 16 != 0 || y_offset + (size_t)M * ldY * sizeof(float) > a->bytes)
         return fail(W4A8_ERR_ARG, "gemm_allgather: Y[%d x %d] at offset %zu does not fit the %zu-byte arena", M, ldY, y_offset, a->bytes);
     if (K <= 0) return fail(W4A8_ERR_ARG, "gemm_allgather: K must be positive");
-    cudaStream_t st = (cudaStream_t)stream;
     if (M == 0 || rows == 0) {                       // nothing to compute: this rank still has to publish the step
-        allgather_publish_kernel<<<1, 32, 0, st>>>(a->desc_dev, epoch);
+        allgather_publish_kernel<<<1, 32, 0, st>>>(a->desc_dev, epoch, wait_limit);
         return launch_status("allgather_publish");
     }
     float *Ylocal = reinterpret_cast<float *>(a->base + y_offset);   // unused by the peer path; keeps the argument checks happy
@@ -754,18 +776,24 @@ W4A8_API int w4a8_gemm_allgather(const int8_t *X, const float *xs, const uint8_t
     OutArgs oa;
     oa.peers = a->desc_dev; oa.y_off = y_offset; oa.ld = ldY; oa.col0 = row0; oa.epoch = epoch;
     oa.publish = direct ? 1 : 0; oa.local_only = direct ? 0 : 1;
+    if (direct) oa.wait_limit = wait_limit;
     rc = gemm::launch_tc(X, xs, Wq, sw, Ylocal, M, rows, K, scale_dtype, 1, K / QBLK, st, oa);   // the int8 kernel carries the peer epilogue
     if (rc != W4A8_OK || direct) return rc;
-    const long units = (long)M * ((((long)ldY | row0 | rows) & 3) == 0 ? rows / 4 : rows);
-    long want = (units + 255) / 256, cap = (long)sm_count() * 4;
-    allgather_scatter_kernel<<<(unsigned)(want < cap ? (want > 0 ? want : 1) : cap), 256, 0, st>>>(a->desc_dev, y_offset, M, (long)ldY, (long)row0, rows, epoch);
-    return launch_status("allgather_scatter");
+    return launch_scatter(a, y_offset, M, ldY, row0, rows, epoch, wait_limit, st);
+}
+
+W4A8_API int w4a8_gemm_allgather(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a, size_t y_offset,
+                                 int M, int rows, int row0, int ldY, int K, int scale_dtype, uint32_t epoch, void *stream) {
+    return gemm_allgather_impl(X, xs, Wq, sw, a, y_offset, M, rows, row0, ldY, K, scale_dtype, epoch, 0, (cudaStream_t)stream);
+}
+W4A8_API int w4a8_gemm_allgather_sync(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a, size_t y_offset,
+                                      int M, int rows, int row0, int ldY, int K, int scale_dtype, uint32_t epoch, int timeout_us, void *stream) {
+    return gemm_allgather_impl(X, xs, Wq, sw, a, y_offset, M, rows, row0, ldY, K, scale_dtype, epoch, wait_cycles(timeout_us), (cudaStream_t)stream);
 }
 
 W4A8_API int w4a8_allgather_wait(w4a8_arena *a, uint32_t epoch, int timeout_us, void *stream) {
     if (!a || !a->connected) return fail(W4A8_ERR_ARG, "allgather_wait: arena not connected");
-    if (timeout_us <= 0) timeout_us = 1000000;
-    const long long limit = (long long)timeout_us * 2000;            // SM clock <= 2 GHz: at least timeout_us
+    const long long limit = wait_cycles(timeout_us);
     cudaError_t le = launch_pdl(allgather_wait_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, (const PeerDesc *)a->desc_dev, (unsigned int)epoch, limit);
     if (le != cudaSuccess) return cuda_fail(le, "allgather_wait launch");
     return launch_status("allgather_wait");

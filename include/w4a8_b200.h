@@ -229,9 +229,10 @@ int w4a8_free_qmat(w4a8_qmat *m);
  * New for multi-GPU; the reference is single-GPU and has nothing to replace here.  One process per GPU.
  * Every rank owns an ARENA: device memory that all ranks of the box map (CUDA IPC, or any other peer mapping the
  * caller has), holding the gathered outputs plus a small tail of flags.  w4a8_gemv_allgather runs the ordinary
- * GEMV on the rank's row shard, but its epilogue stores each result into EVERY rank's arena at the final address
- * of Y[M, ldY] (plain peer stores over NVLink; no collective, no TMA), and publishes `epoch` in a flag on every
- * rank when its stores are complete.  w4a8_allgather_wait enqueues a kernel that waits until all ranks' flags in
+ * GEMV on the rank's row shard into the rank's own arena at the final address of Y[M, ldY]; the last CTA of the
+ * launch to finish (or, for a large slice, a copy kernel many CTAs wide) then sends the finished slice to the same
+ * place in every other rank's arena with row-contiguous 16-byte peer stores over NVLink (no collective, no TMA), and
+ * publishes `epoch` in a flag on every rank behind one system-scope fence.  w4a8_allgather_wait enqueues a kernel that waits until all ranks' flags in
  * the local arena have reached `epoch`; work enqueued after it on the same stream sees the complete Y.
  * The wait is bounded: after timeout_us it records a device error (w4a8_device_status returns W4A8_ERR_DEVICE)
  * and returns, leaving the context usable.
@@ -262,6 +263,18 @@ int w4a8_gemm_allgather(const int8_t *X, const float *xs, const uint8_t *Wq, con
                         size_t y_offset, int M, int rows, int row0, int ldY, int K, int scale_dtype,
                         uint32_t epoch, void *stream);
 int w4a8_allgather_wait(w4a8_arena *a, uint32_t epoch, int timeout_us, void *stream);
+/* The same two products with the wait folded into their last kernel: the CTA that sends the rank's slice on and publishes
+ * the epoch also waits (at most timeout_us, then W4A8_ERR_DEVICE through w4a8_device_status) until every rank's flag has
+ * reached `epoch`, so when the call's last kernel completes, Y[M, ldY] is complete in this rank's arena and no separate
+ * wait kernel sits on the critical path of a decode step.  Every rank of the group must make the matching call: a rank
+ * whose peers never publish only returns after the time-out.  Not for several ranks driven one after the other on one
+ * GPU (use w4a8_gemv_allgather + w4a8_allgather_wait there). */
+int w4a8_gemv_allgather_sync(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a,
+                             size_t y_offset, int IN, int rows, int row0, int ldY, int S, int scale_dtype,
+                             uint32_t epoch, int timeout_us, void *stream);
+int w4a8_gemm_allgather_sync(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a,
+                             size_t y_offset, int M, int rows, int row0, int ldY, int K, int scale_dtype,
+                             uint32_t epoch, int timeout_us, void *stream);
 /* The epoch a kernel publishes / waits for is `epoch` plus a per-arena base kept in device memory (initially 0).
  * This enqueues base += delta.  A CUDA graph that captured steps with epochs 1..n ends with
  * w4a8_arena_advance_epoch(a, n, stream), so that every replay (on all ranks alike) uses fresh epochs. */

@@ -3,7 +3,7 @@
 One GPU: the two ranks are emulated in one process, one after the other on one stream — each "rank" owns an arena,
 both arenas are mapped into each other by plain pointers, rank 0's kernel runs, then rank 1's, then both waits — so no
 kernel ever waits for a kernel that is not already complete.  The bounded wait is exercised with a flag nothing sets:
-it must give up, report W4A8_ERR_DEVICE and leave the context usable.  Two GPUs (skipped on a one-GPU box): real ranks
+it must give up, report W4A8_ERR_DEVICE and leave the context usable.  Two, four or eight GPUs (skipped on a smaller box): real ranks
 as child processes with CUDA IPC mappings, NVLS off, checked against the oracle and against the NCCL all-gather path.
 """
 import os
@@ -111,6 +111,32 @@ def test_allgather_wait_gives_up_and_reports(w4a8, oracle, cuda):
             a.close()
 
 
+def test_in_kernel_wait_gives_up_and_reports(w4a8, oracle, cuda):
+    """The wait folded into the GEMV (w4a8_gemv_allgather_sync) is bounded too: rank 1 of the emulated pair never runs, so
+    rank 0's pushing CTA waits 2 ms for a flag nothing sets, records the error and returns; the outputs it computed are in
+    place, the context stays usable."""
+    S, N, K = 1, 520, 512
+    xq, xs, Wq, sw = make_case(oracle, S, N, K, seed=11)
+    arenas = [w4a8.Arena(8192, r, 2) for r in range(2)]
+    try:
+        for a in arenas:
+            a.connect_pointers([b.base for b in arenas])
+        row0, rows = w4a8.shard_rows(N, 0, 2)
+        arenas[0].gemv_allgather_sync(to_dev(xq, cuda), to_dev(xs, cuda), to_dev(Wq[row0:row0 + rows], cuda), to_dev(sw[row0:row0 + rows], cuda),
+                                      0, K, rows, row0, N, S, 0, 1, 2000)
+        with pytest.raises(w4a8.W4A8Error) as ei:
+            w4a8.device_status()
+        assert ei.value.code == w4a8.ERR_DEVICE and "0x20" in str(ei.value)
+        w4a8.device_status()                                      # cleared; the context still works
+        expect = gemv_expected(oracle, xq, xs, Wq, sw)
+        for a in arenas:                                          # rank 0's slice reached both arenas all the same
+            y = a.tensor(0, (S, N)).cpu().numpy()[:, row0:row0 + rows]
+            assert np.array_equal(y.view(np.uint32), expect[:, row0:row0 + rows].view(np.uint32))
+    finally:
+        for a in arenas:
+            a.close()
+
+
 _WORKER = r'''
 import os, sys
 sys.path.insert(0, os.path.join(ROOT, "tests")); sys.path.insert(0, os.path.join(ROOT, "oracle"))
@@ -137,13 +163,19 @@ for (S, N, K) in [(1, 17408, 5120), (8, 4096, 1024), (16, 1001, 512)]:
     dist.all_gather_object(handles, a.export_handle())
     a.connect_handles(handles)
     dist.barrier()
-    for epoch in range(1, 6):
+    for epoch in range(1, 9):
         off = (epoch % 2) * ystride
-        a.gemv_allgather(xq_d, xs_d, Wq_r, sw_r, off, K, rows, row0, N, S, 0, epoch)
-        a.wait(epoch, timeout_us=2000000)
+        if epoch <= 4:                                     # exchange and a wait kernel of its own
+            a.gemv_allgather(xq_d, xs_d, Wq_r, sw_r, off, K, rows, row0, N, S, 0, epoch)
+            a.wait(epoch, timeout_us=2000000)
+        else:                                              # the wait folded into the call's last kernel
+            a.gemv_allgather_sync(xq_d, xs_d, Wq_r, sw_r, off, K, rows, row0, N, S, 0, epoch, 2000000)
         w.device_status()
         y = a.tensor(off, (S, N)).cpu().numpy()
         assert np.array_equal(y.view(np.uint32), expect.view(np.uint32)), (S, N, K, epoch, rank)
+        a.tensor(off, (S, N)).fill_(float("nan"))
+        torch.cuda.synchronize()
+        dist.barrier()                                     # nobody refills a buffer a peer is still checking
     # the NCCL path gives the same bits
     Yloc = torch.empty((S, rows), dtype=torch.float32, device=dev)
     w.launch_gemv_w4a8_sb(xq_d, xs_d, Wq_r, sw_r, Yloc, K, rows, S)
@@ -164,13 +196,19 @@ for (M, N, K) in [(256, 1024, 1024), (130, 520, 512)]:
     dist.all_gather_object(handles, a.export_handle())
     a.connect_handles(handles)
     dist.barrier()
-    for epoch in range(1, 4):
+    for epoch in range(1, 6):
         off = (epoch % 2) * ystride
-        a.gemm_allgather(xq_d, xs_d, Wq_r, sw_r, off, M, rows, row0, N, K, 0, epoch)
-        a.wait(epoch, timeout_us=2000000)
+        if epoch <= 3:
+            a.gemm_allgather(xq_d, xs_d, Wq_r, sw_r, off, M, rows, row0, N, K, 0, epoch)
+            a.wait(epoch, timeout_us=2000000)
+        else:
+            a.gemm_allgather_sync(xq_d, xs_d, Wq_r, sw_r, off, M, rows, row0, N, K, 0, epoch, 2000000)
         w.device_status()
         y = a.tensor(off, (M, N)).cpu().numpy()
         assert np.array_equal(y.view(np.uint32), expect.view(np.uint32)), (M, N, K, epoch, rank)
+        a.tensor(off, (M, N)).fill_(float("nan"))
+        torch.cuda.synchronize()
+        dist.barrier()
     dist.barrier()
     a.close()
 dist.destroy_process_group()
@@ -178,17 +216,25 @@ print("rank", rank, "ok")
 '''
 
 
-def test_fused_allgather_two_gpus(tmp_path):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_allgather_real_gpus(tmp_path, world):
+    """Real ranks, one process per GPU (skipped when the box has fewer GPUs than `world`)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
     script = tmp_path / "worker.py"
     script.write_text("ROOT = %r\n" % ROOT + _WORKER)
     procs = []
-    for r in range(2):
-        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT="29733",
-                   NCCL_NVLS_ENABLE="0")
-        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
-    outs = [p.communicate(timeout=600)[0] for p in procs]
+    try:
+        for r in range(world):
+            env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                       MASTER_PORT=str(29733 + world), NCCL_NVLS_ENABLE="0")
+            procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+        outs = [p.communicate(timeout=600)[0] for p in procs]
+    finally:
+        for p in procs:                                    # never leave a rank behind in a barrier, holding a GPU
+            if p.poll() is None:
+                p.kill()
+                p.wait()
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, o[-3000:]
         assert "rank %d ok" % r in o
