@@ -620,7 +620,7 @@ W4A8_API int w4a8_free_qmat(w4a8_qmat *m) {
 
 // ---- arenas, IPC, fused GEMV + all-gather ---------------------------------------------------------------------
 struct w4a8_arena {
-    unsigned char *base = nullptr;      // local allocation: user bytes + PEER_TAIL
+    unsigned char *base = nullptr;      // local allocation: user bytes + PEER_TAIL + two slot buffers
     size_t bytes = 0;                   // user bytes
     int rank = 0, world = 1;
     PeerDesc *desc_dev = nullptr;       // device copy of the descriptor (valid after connect)
@@ -635,8 +635,9 @@ W4A8_API int w4a8_arena_create(size_t bytes, int rank, int world, w4a8_arena **o
     w4a8_arena *a = new w4a8_arena();
     a->bytes = (bytes + 255) & ~(size_t)255;
     a->rank = rank; a->world = world;
-    cudaError_t e = cudaMalloc((void **)&a->base, a->bytes + PEER_TAIL);
-    if (e == cudaSuccess) e = cudaMemset(a->base, 0, a->bytes + PEER_TAIL);
+    const size_t total = a->bytes + PEER_TAIL + 2 * LL_BUF_BYTES;
+    cudaError_t e = cudaMalloc((void **)&a->base, total);
+    if (e == cudaSuccess) e = cudaMemset(a->base, 0, total);
     if (e == cudaSuccess) e = cudaMalloc((void **)&a->desc_dev, sizeof(PeerDesc));
     if (e != cudaSuccess) { if (a->base) cudaFree(a->base); delete a; return cuda_fail(e, "arena_create"); }
     *out = a;
@@ -652,6 +653,7 @@ W4A8_API int w4a8_arena_connect(w4a8_arena *a, void *const *bases) {
         if (!d.base[r]) return fail(W4A8_ERR_ARG, "arena_connect: no mapping for rank %d", r);
     }
     d.flag_off = a->bytes;
+    d.ll_off = a->bytes + PEER_TAIL;
     d.counter = reinterpret_cast<unsigned int *>(a->base + a->bytes + PEER_MAX * sizeof(unsigned int));
     d.epoch_base = d.counter + 1;
     d.world = a->world; d.rank = a->rank;
@@ -716,28 +718,41 @@ static int gemv_allgather_impl(const int8_t *xq, const float *xs, const uint8_t 
     if (y_offset % 16 != 0 || y_offset + (size_t)S * ldY * sizeof(float) > a->bytes)
         return fail(W4A8_ERR_ARG, "gemv_allgather: Y[%d x %d] at offset %zu does not fit the %zu-byte arena", S, ldY, y_offset, a->bytes);
     if (IN <= 0) return fail(W4A8_ERR_ARG, "gemv_allgather: IN must be positive");
-    if (S == 0 || rows == 0) {                       // nothing to compute: this rank still has to publish the step
+    float *Ylocal = reinterpret_cast<float *>(a->base + y_offset);   // unused by the peer path; keeps the argument checks happy
+    static const int mode = [] { const char *e = getenv("W4A8_ALLGATHER"); return !e ? 0 : e[0] == 'p' ? 1 : e[0] == 'f' ? 2 : e[0] == 's' ? 3 : 0; }();
+    OutArgs oa;
+    oa.peers = a->desc_dev; oa.y_off = y_offset; oa.ld = ldY; oa.col0 = row0; oa.epoch = epoch;
+    oa.local_only = 1; oa.M = S; oa.cols = rows;
+    // how many launches, and which kernel, are decided by the same function under the same arguments (not by `rows`:
+    // every rank of the step comes to the same answer, its own slice empty or not)
+    int launches = 1;
+    int rc = S > 0 ? gemv_dispatch(xq, xs, Wq, sw, Ylocal, IN, rows, S, scale_dtype, st, &launches, oa) : W4A8_OK;
+    if (rc != W4A8_OK) return rc;
+    const bool tagged = launches == 1 && wait_limit > 0 && (size_t)S * ldY <= LL_MAX_SLOTS && mode == 0;
+    if (S == 0 || rows == 0) {                       // nothing to compute: this rank still takes part in the step
+        if (tagged && S > 0) {
+            oa.ll = 1; oa.wait_limit = wait_limit;
+            const long want = ((long)S * ldY + 255) / 256, cap = (long)sm_count() * 4;
+            cudaError_t le = launch_pdl(allgather_ll_gather_kernel, dim3((unsigned)(want < cap ? want : cap)), dim3(256), 0, st, oa);
+            if (le != cudaSuccess) return cuda_fail(le, "allgather_ll_gather launch");
+            return launch_status("allgather_ll_gather");
+        }
         allgather_publish_kernel<<<1, 32, 0, st>>>(a->desc_dev, epoch, wait_limit);
         return launch_status("allgather_publish");
     }
-    float *Ylocal = reinterpret_cast<float *>(a->base + y_offset);   // unused by the peer path; keeps the argument checks happy
-    int rc = check_common(xq, xs, Wq, sw, Ylocal, IN, scale_dtype, "gemv_allgather");
+    rc = check_common(xq, xs, Wq, sw, Ylocal, IN, scale_dtype, "gemv_allgather");
     if (rc != W4A8_OK) return rc;
     if (!aligned(xq, 4) || !aligned(Wq, 4)) return fail(W4A8_ERR_ALIGN, "gemv_allgather: xq and Wq must be 4-byte aligned");
     rc = require_sm100();
     if (rc != W4A8_OK) return rc;
-    OutArgs oa;
-    oa.peers = a->desc_dev; oa.y_off = y_offset; oa.ld = ldY; oa.col0 = row0; oa.epoch = epoch;
-    oa.local_only = 1; oa.M = S; oa.cols = rows;
-    // how many launches, and which kernel, are decided by the same function under the same arguments
-    int launches = 1;
-    rc = gemv_dispatch(xq, xs, Wq, sw, Ylocal, IN, rows, S, scale_dtype, st, &launches, oa);
-    if (rc != W4A8_OK) return rc;
-    // One launch and a slice small enough for one CTA to send on: its last CTA pushes, publishes and (optionally) waits.
-    // Otherwise the launches only fill the rank's own arena and the many-CTA copy kernel does the rest.
+    // One launch whose completion has to mean "Y is complete here" (wait_limit > 0) and a Y that fits a slot buffer:
+    // tagged slots, no fence and no flag.  One launch and a slice small enough: the computing threads store every
+    // output to every arena (W4A8_ALLGATHER=push: the last CTA copies the slice instead), and the last CTA publishes
+    // the flags.  Otherwise the launches only fill the rank's own arena and the many-CTA copy kernel does the rest.
     const size_t push_total = (size_t)S * rows * sizeof(float) * (size_t)(a->world - 1);
-    const bool in_kernel = launches == 1 && push_total <= PUSH_MAX_BYTES;
-    if (in_kernel) { oa.publish = 1; oa.push = a->world > 1 ? 1 : 0; oa.wait_limit = wait_limit; }
+    const bool in_kernel = tagged || (launches == 1 && push_total <= PUSH_MAX_BYTES && mode != 3);
+    if (tagged) { oa.ll = 1; oa.wait_limit = wait_limit; }
+    else if (in_kernel) { oa.publish = 1; oa.push = (a->world > 1 && mode == 1) ? 1 : 0; oa.local_only = mode == 1 ? 1 : 0; oa.wait_limit = wait_limit; }
     rc = gemv_dispatch(xq, xs, Wq, sw, Ylocal, IN, rows, S, scale_dtype, st, nullptr, oa);
     if (rc != W4A8_OK || in_kernel) return rc;
     return launch_scatter(a, y_offset, S, ldY, row0, rows, epoch, wait_limit, st);

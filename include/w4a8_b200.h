@@ -228,17 +228,21 @@ int w4a8_free_qmat(w4a8_qmat *m);
 /* ---- N-sharded GEMV with the all-gather fused into the epilogue ------------------------------------------
  * New for multi-GPU; the reference is single-GPU and has nothing to replace here.  One process per GPU.
  * Every rank owns an ARENA: device memory that all ranks of the box map (CUDA IPC, or any other peer mapping the
- * caller has), holding the gathered outputs plus a small tail of flags.  w4a8_gemv_allgather runs the ordinary
- * GEMV on the rank's row shard into the rank's own arena at the final address of Y[M, ldY]; the last CTA of the
- * launch to finish (or, for a large slice, a copy kernel many CTAs wide) then sends the finished slice to the same
- * place in every other rank's arena with row-contiguous 16-byte peer stores over NVLink (no collective, no TMA), and
- * publishes `epoch` in a flag on every rank behind one system-scope fence.  w4a8_allgather_wait enqueues a kernel that waits until all ranks' flags in
- * the local arena have reached `epoch`; work enqueued after it on the same stream sees the complete Y.
+ * caller has), holding the gathered outputs, a small tail of flags and two internal slot buffers (8 MiB together,
+ * allocated behind the `bytes` the caller asks for).  w4a8_gemv_allgather runs the ordinary GEMV on the rank's row
+ * shard into the rank's own arena at the final address of Y[M, ldY]; the slice reaches the same place in every
+ * other rank's arena through ordinary peer stores over NVLink (no collective, no TMA: from the computing threads
+ * for a small slice, from a copy kernel many CTAs wide with row-contiguous 16-byte stores for a large one), and
+ * the last CTA publishes `epoch` in a flag on every rank behind one system-scope fence.  w4a8_allgather_wait
+ * enqueues a kernel that waits until all ranks' flags in the local arena have reached `epoch`; work enqueued after
+ * it on the same stream sees the complete Y.
  * The wait is bounded: after timeout_us it records a device error (w4a8_device_status returns W4A8_ERR_DEVICE)
  * and returns, leaving the context usable.
- * Rules: epochs of successive steps must increase; a rank may start step e+1 only after its own wait for step e
- * (stream order does that), and Y buffers of consecutive steps must alternate between two offsets, because a
- * fast rank's step e+1 stores may land while a slow rank still reads step e.  At most 8 ranks. */
+ * Rules: epochs of successive steps must increase; a rank may start step e+1 only after step e is complete on its
+ * stream (w4a8_allgather_wait, or a `_sync` call, in stream order), and Y buffers of consecutive steps must
+ * alternate between two offsets, because a fast rank's step e+1 stores may land while a slow rank still reads
+ * step e.  Every rank passes the same S, IN, ldY and scale_dtype and equally aligned pointers.  At most 8 ranks.
+ * Environment W4A8_ALLGATHER = push | flags | scatter forces one exchange (measurement only). */
 typedef struct w4a8_arena w4a8_arena;
 int w4a8_arena_create(size_t bytes, int rank, int world, w4a8_arena **out);   /* cudaMalloc'd, zeroed */
 void *w4a8_arena_base(w4a8_arena *a);                                          /* local device pointer */
@@ -263,12 +267,16 @@ int w4a8_gemm_allgather(const int8_t *X, const float *xs, const uint8_t *Wq, con
                         size_t y_offset, int M, int rows, int row0, int ldY, int K, int scale_dtype,
                         uint32_t epoch, void *stream);
 int w4a8_allgather_wait(w4a8_arena *a, uint32_t epoch, int timeout_us, void *stream);
-/* The same two products with the wait folded into their last kernel: the CTA that sends the rank's slice on and publishes
- * the epoch also waits (at most timeout_us, then W4A8_ERR_DEVICE through w4a8_device_status) until every rank's flag has
- * reached `epoch`, so when the call's last kernel completes, Y[M, ldY] is complete in this rank's arena and no separate
- * wait kernel sits on the critical path of a decode step.  Every rank of the group must make the matching call: a rank
- * whose peers never publish only returns after the time-out.  Not for several ranks driven one after the other on one
- * GPU (use w4a8_gemv_allgather + w4a8_allgather_wait there). */
+/* The same two products with the wait folded into their last kernel: when the call's last kernel completes,
+ * Y[M, ldY] is complete in this rank's arena and no separate wait kernel sits on the critical path of a decode step.
+ * The GEMV with one launch and M*ldY <= 512 Ki outputs uses tagged slots instead of flags: every output also goes,
+ * as one 8-byte store {value, tag of the epoch}, into a slot buffer of every other arena, and every CTA, once its
+ * rows are done, polls its share of the slots the other ranks fill here and writes them into the local Y — no fence,
+ * no flag (such a step does not publish its epoch: do not call w4a8_allgather_wait for it).  Otherwise the CTA that
+ * publishes the epoch also waits for every rank's flag.  Either wait gives up after timeout_us (W4A8_ERR_DEVICE
+ * through w4a8_device_status).  Every rank of the group must make the matching call: a rank whose peers never
+ * arrive only returns after the time-out.  Not for several ranks driven one after the other on one GPU (use
+ * w4a8_gemv_allgather + w4a8_allgather_wait there). */
 int w4a8_gemv_allgather_sync(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, w4a8_arena *a,
                              size_t y_offset, int IN, int rows, int row0, int ldY, int S, int scale_dtype,
                              uint32_t epoch, int timeout_us, void *stream);
