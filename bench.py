@@ -529,6 +529,32 @@ def run_ours(args):
             by = touched * (n_ * k_ // 2 + n_ * (k_ // 32) * 4)
             moe[name] = {"us": ms_m * 1e3 / 50, "experts_touched": touched, "gbps_weights": by / (ms_m / 50 * 1e-3) / 1e9}
         extra["moe_128e_top8_m8"] = moe
+        # ---- the whole routed-expert block (quantize, gate|up, activation + quantize, down, combine) at M = 8 and 512 -----
+        H_, MI_ = 2048, 768
+        blk = {}
+        gu_w = [torch.randint(0, 256, (E, 2 * MI_, H_ // 2), dtype=torch.uint8, device=dev, generator=g) for _ in range(2)]
+        gu_s = [torch.randn(E, 2 * MI_, H_ // 32, device=dev, generator=g).abs() * (0.16 / 7.0) for _ in range(2)]
+        dn_w = [torch.randint(0, 256, (E, H_, MI_ // 2), dtype=torch.uint8, device=dev, generator=g) for _ in range(2)]
+        dn_s = [torch.randn(E, H_, MI_ // 32, device=dev, generator=g).abs() * (0.02 / 7.0) for _ in range(2)]
+        per_expert = 2 * MI_ * (H_ // 2 + (H_ // 32) * 4) + H_ * (MI_ // 2 + (MI_ // 32) * 4)     # 2,949,120 B: gate+up+down, fp32 scales
+        for tok_ in (8, 512):
+            n2_ = torch.randn(tok_, H_, device=dev, generator=g)
+            idx_ = torch.stack([torch.randperm(E, device=dev, generator=g)[:topk] for _ in range(tok_)]).reshape(-1).to(torch.int32)
+            dw_ = torch.rand(tok_ * topk, device=dev, generator=g)
+            out_ = torch.empty((tok_, H_), dtype=torch.float32, device=dev)
+            lay_ = w.moe_layout_for(tok_, topk, H_, MI_, E)
+            ws_ = torch.empty(lay_.bytes, dtype=torch.uint8, device=dev)
+            nst = 20 if tok_ <= 64 else 6
+            ms_b = time_steps(lambda i, st: w.moe_block(n2_, gu_w[i % 2], gu_s[i % 2], dn_w[i % 2], dn_s[i % 2], idx_, dw_, out_, tok_, topk, H_, MI_,
+                                                        E, ws_, 0, 0, st), nst, 3, graph=True)
+            us_b = ms_b * 1e3 / nst
+            touched = int(torch.unique(idx_).numel())
+            ops = 2.0 * tok_ * topk * (2 * MI_ * H_ + H_ * MI_)
+            blk["m%d" % tok_] = {"us": us_b, "experts_touched": touched, "weight_bytes": touched * per_expert,
+                                 "gbps_weights": touched * per_expert / (us_b * 1e-6) / 1e9, "int8_tops": ops / (us_b * 1e-6) / 1e12,
+                                 "kernel": "grouped GEMV per slot" if tok_ * topk <= 128 else "sorted grouped tcgen05 GEMM"}
+        extra["moe_block_128e_top8"] = blk
+        del gu_w, gu_s, dn_w, dn_s
         # ---- the reference's own kernels rebuilt for sm_100a, same buffers (not part of the library) -------
         refp = os.path.join(ROOT, "oracle", "_ref", "libref_kernels.so")
         if os.path.exists(refp):

@@ -35,6 +35,12 @@ class QMat(ctypes.Structure):
                 ("scale_dtype", ctypes.c_int)]
 
 
+class MoeLayout(ctypes.Structure):
+    """Mirror of w4a8_moe_layout: byte offsets of the routed-expert block's intermediates in the caller's workspace."""
+    _fields_ = [(n, ctypes.c_size_t) for n in ("perm", "pos", "offsets", "items", "num_items", "xq", "xs", "xq_g", "xs_g", "gu",
+                                               "xq_h", "xs_h", "sout", "bytes")]
+
+
 _P, _I, _Z, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t, ctypes.c_int64
 _SIGNATURES = {
     "w4a8_version": (_I, []),
@@ -54,6 +60,9 @@ _SIGNATURES = {
     "w4a8_linear": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "w4a8_linear_host": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "w4a8_moe_gemv": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P]),
+    "w4a8_moe_layout_for": (_I, [_I, _I, _I, _I, _I, ctypes.POINTER(MoeLayout)]),
+    "w4a8_moe_block": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _Z, _P]),
+    "w4a8_moe_block_shard": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _Z, _P, _Z, ctypes.c_uint32, _I, _I, _P]),
     "w4a8_shard_rows": (_I, [_L, _I, _I, ctypes.POINTER(_L), ctypes.POINTER(_L)]),
     "w4a8_load_qmat_shard": (_I, [ctypes.c_char_p, ctypes.c_char_p, _L, _L, _I, _I, _I, ctypes.POINTER(QMat)]),
     "w4a8_upload_qmat_shard": (_I, [_P, _P, _L, _L, _I, _I, _I, ctypes.POINTER(QMat)]),
@@ -216,6 +225,27 @@ def linear_host(X_host, Y_host, X_dev, xq, xs, xsum, Y_dev, Wq, sw, S, N, K, sca
 def moe_gemv(xq, xs, Wq, sw, idx, Y, nslots, topk, x_per_slot, N, K, num_experts, scale_dtype=0, stream=None):
     _check(lib().w4a8_moe_gemv(_ptr(xq), _ptr(xs), _ptr(Wq), _ptr(sw), _ptr(idx), _ptr(Y), nslots, topk, x_per_slot,
                                N, K, num_experts, scale_dtype, _stream(stream)))
+
+
+def moe_layout_for(S, topk, H, MI, experts):
+    l = MoeLayout()
+    _check(lib().w4a8_moe_layout_for(S, topk, H, MI, experts, ctypes.byref(l)))
+    return l
+
+
+def moe_block(n2, gu_wq, gu_sc, dn_wq, dn_sc, idx, dw, out, S, topk, H, MI, num_experts, workspace, scale_dtype=0, act=0, stream=None):
+    """The routed-expert block of models/moe_block.cuh:45-52 in W4A8 (w4a8_moe_block); workspace = a uint8 device tensor
+    of moe_layout_for(...).bytes bytes."""
+    _check(lib().w4a8_moe_block(_ptr(n2), _ptr(gu_wq), _ptr(gu_sc), _ptr(dn_wq), _ptr(dn_sc), _ptr(idx), _ptr(dw), _ptr(out), S, topk, H, MI,
+                                num_experts, scale_dtype, act, _ptr(workspace), workspace.numel() * workspace.element_size(), _stream(stream)))
+
+
+def moe_block_shard(n2, gu_wq, gu_sc, dn_wq, dn_sc, idx, dw, out, S, topk, H, MI, expert_base, experts_local, workspace, arena, sout_offset,
+                    epoch, scale_dtype=0, act=0, timeout_us=1000000, phase=0, stream=None):
+    """Expert-sharded routed-expert block (w4a8_moe_block_shard): this rank's experts only, down outputs exchanged through the arenas."""
+    _check(lib().w4a8_moe_block_shard(_ptr(n2), _ptr(gu_wq), _ptr(gu_sc), _ptr(dn_wq), _ptr(dn_sc), _ptr(idx), _ptr(dw), _ptr(out), S, topk, H, MI,
+                                      expert_base, experts_local, scale_dtype, act, _ptr(workspace),
+                                      workspace.numel() * workspace.element_size(), arena.handle, sout_offset, epoch, timeout_us, phase, _stream(stream)))
 
 
 def shard_rows(N, rank, world):

@@ -98,14 +98,17 @@ __device__ __forceinline__ float glu_value(float g, float u) {
 template <int ACT>
 __global__ void __launch_bounds__(256) glu_quantize_kernel(const float4 *__restrict__ G, const float4 *__restrict__ U, float4 *__restrict__ Y,
                                                            uint32_t *__restrict__ xq, float *__restrict__ xs, int32_t *__restrict__ xsum,
-                                                           long nvec /* = S*IN/4, a multiple of 8 */) {
+                                                           long nvec /* = S*IN/4, a multiple of 8 */, int row_vecs, long pitch_vecs) {
+    // row_vecs = IN/4; rows of G and U start pitch_vecs float4s apart (== row_vecs: dense; a fused gate|up tensor
+    // [S][2*IN] has pitch 2*IN/4 and U = G + IN)
     const long stride = (long)gridDim.x * blockDim.x;
     pdl_launch_dependents();
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i - (threadIdx.x & 31) < nvec; i += stride) {
         const bool live = i < nvec;
         float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
         if (live) {
-            const float4 g = G[i], u = U[i];
+            const long src = pitch_vecs == row_vecs ? i : (i / row_vecs) * pitch_vecs + (i % row_vecs);
+            const float4 g = G[src], u = U[src];
             y = make_float4(glu_value<ACT>(g.x, u.x), glu_value<ACT>(g.y, u.y), glu_value<ACT>(g.z, u.z), glu_value<ACT>(g.w, u.w));
             if (Y) Y[i] = y;
         }
@@ -125,15 +128,16 @@ inline int launch_rmsnorm_quantize(const float *X, const float *W, float eps, in
 }
 
 inline int launch_glu_quantize(const float *G, const float *U, int act, float *Y, int8_t *xq, float *xs, int32_t *xsum, int IN,
-                               int S, cudaStream_t st) {
+                               int S, cudaStream_t st, long pitch = 0 /* floats between rows of G / U; 0 = IN */) {
     const long nvec = (long)S * IN / 4;
     long want = (nvec + 255) / 256, cap = (long)sm_count() * 8;
     const unsigned grid = (unsigned)(want < cap ? want : cap);
     const float4 *g = reinterpret_cast<const float4 *>(G), *u = reinterpret_cast<const float4 *>(U);
     float4 *y = reinterpret_cast<float4 *>(Y);
     uint32_t *q = reinterpret_cast<uint32_t *>(xq);
-    if (act == 0) glu_quantize_kernel<0><<<grid, 256, 0, st>>>(g, u, y, q, xs, xsum, nvec);
-    else glu_quantize_kernel<1><<<grid, 256, 0, st>>>(g, u, y, q, xs, xsum, nvec);
+    const long pv = (pitch > 0 ? pitch : IN) / 4;
+    if (act == 0) glu_quantize_kernel<0><<<grid, 256, 0, st>>>(g, u, y, q, xs, xsum, nvec, IN / 4, pv);
+    else glu_quantize_kernel<1><<<grid, 256, 0, st>>>(g, u, y, q, xs, xsum, nvec, IN / 4, pv);
     return launch_status("glu_quantize_x_q8");
 }
 

@@ -170,17 +170,43 @@ __device__ __forceinline__ void epi_dump(const uint32_t (&d)[NC], int32_t *__res
     }
 }
 
+// Grouped experts (GROUPED instantiation): the activation rows are sorted by expert, item i of the list says
+// "expert x, sorted rows [y, y + z)" with z <= BM (one item per 128-row tile of an expert, written on the device by
+// moe_sort_kernel), the weights are the flat [experts * N][K/2] tensor of the reference (kernels/moe_fused.cuh:21-24:
+// expert e starts e * N rows in), and one unit of work is (item, 128-column tile of the expert's N outputs).
+struct GroupList {
+    const int4 *items = nullptr;
+    const int *num_items = nullptr;
+};
+
 // One unit of work = (output tile, K split).  Tiles are numbered M-fastest so that CTAs running at the
 // same time share weight tiles in L2; split s covers groups [s*gsplit, min(nb, (s+1)*gsplit)).
+// Rows [m0, mend) of the tile are live; wrow0 is added to a column index to get its row in the weight tensor.
 struct Work {
-    int m0, n0, g0, g1, nkt, split;
+    int m0, mend, n0, wrow0, g0, g1, nkt, split;
 };
-__device__ __forceinline__ Work decode_work(int w, int m_tiles, int num_tiles, int nb, int gsplit) {
+template <bool GROUPED>
+__device__ __forceinline__ Work decode_work(int w, int m_tiles, int num_tiles, int nb, int gsplit, int M, int N, int n_tiles,
+                                            const GroupList &gl) {
     Work k;
+    if (GROUPED) {
+        const int4 it = __ldg(gl.items + w / n_tiles);
+        k.split = 0;
+        k.m0 = it.y;
+        k.mend = it.y + it.z;
+        k.n0 = (w % n_tiles) * BN;      // consecutive units share an item: its activation tile stays in L2
+        k.wrow0 = it.x * N;
+        k.g0 = 0;
+        k.g1 = nb;
+        k.nkt = (nb + GPK - 1) / GPK;
+        return k;
+    }
     const int tile = w % num_tiles;
     k.split = w / num_tiles;
     k.m0 = (tile % m_tiles) * BM;
+    k.mend = M;
     k.n0 = (tile / m_tiles) * BN;
+    k.wrow0 = 0;
     k.g0 = k.split * gsplit;
     k.g1 = min(nb, k.g0 + gsplit);
     const int ng = max(0, k.g1 - k.g0);
@@ -191,11 +217,11 @@ __device__ __forceinline__ Work decode_work(int w, int m_tiles, int num_tiles, i
 // PEER (N-sharded weights, no split-K): every output tile is stored straight into EVERY rank's Y[M, ld] at its final
 // columns (oa.col0 + n: plain 16-byte peer stores over NVLink) and the last CTA publishes the step's epoch, so the
 // all-gather costs no extra pass over the outputs (peer_allgather.cuh).
-template <typename ST, bool DUMP, int EPI, bool PEER = false>
+template <typename ST, bool DUMP, int EPI, bool PEER = false, bool GROUPED = false>
 __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
     const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
     const float *__restrict__ xs, const ST *__restrict__ sw, float *__restrict__ Y, int32_t *__restrict__ Dout,
-    int M, int N, int K, int nsplit, int gsplit, const OutArgs oa) {
+    int M, int N, int K, int nsplit, int gsplit, const OutArgs oa, const GroupList gl) {
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t raw = ptx::smem_u32(smem_dyn);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -214,7 +240,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
     const bool scales_aligned = ((reinterpret_cast<uintptr_t>(xs) & 15) == 0) && ((reinterpret_cast<uintptr_t>(sw) & (4 * sizeof(ST) - 1)) == 0);
     const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
     const int num_tiles = m_tiles * n_tiles;
-    const int num_work = num_tiles * nsplit;
+    const int num_work = GROUPED ? *gl.num_items * n_tiles : num_tiles * nsplit;
 
     if (tid == 0) {
         for (int i = 0; i < SA; i++) { ptx::mbar_init(BAR(A_FULL + i), 1); ptx::mbar_init(BAR(A_EMPTY + i), 1); }
@@ -241,7 +267,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
             Ring ra(SA), rb(SB);
             bool ok = true;
             for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
-                const Work wk = decode_work(wi, m_tiles, num_tiles, nb, gsplit);
+                const Work wk = decode_work<GROUPED>(wi, m_tiles, num_tiles, nb, gsplit, M, N, n_tiles, gl);
                 const int m0 = wk.m0, n0 = wk.n0;
                 for (int kt = 0; kt < wk.nkt && ok; kt++) {
                     const int kbyte = (wk.g0 + kt * GPK) * QBLK;   // first K element of this K-tile (multiple of 32)
@@ -251,7 +277,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
                     ra.advance();
                     if (!ptx::mbar_wait(BAR(BP_EMPTY + rb.stage), rb.phase ^ 1u)) { dev_set_error(ERR_PRODUCER | 2); ok = false; break; }
                     ptx::mbar_arrive_expect_tx(BAR(BP_FULL + rb.stage), BP_STAGE);
-                    ptx::tma_load_2d(base + OFF_BP + rb.stage * BP_STAGE, &tmB, kbyte / 2, n0, BAR(BP_FULL + rb.stage));
+                    ptx::tma_load_2d(base + OFF_BP + rb.stage * BP_STAGE, &tmB, kbyte / 2, wk.wrow0 + n0, BAR(BP_FULL + rb.stage));
                     rb.advance();
                 }
             }
@@ -267,7 +293,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
             const uint32_t idesc = ptx::umma_idesc_s8(BM, BN);
             bool ok = true;
             for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
-                const Work wk = decode_work(wi, m_tiles, num_tiles, nb, gsplit);
+                const Work wk = decode_work<GROUPED>(wi, m_tiles, num_tiles, nb, gsplit, M, N, n_tiles, gl);
                 for (int kt = 0; kt < wk.nkt && ok; kt++) {
                     if (!ptx::mbar_wait(BAR(A_FULL + ra.stage), ra.phase)) { dev_set_error(ERR_MMA | 1); ok = false; break; }
                     if (!ptx::mbar_wait(BAR(B8_FULL + r8.stage), r8.phase)) { dev_set_error(ERR_MMA | 2); ok = false; break; }
@@ -296,7 +322,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
         Ring rb(SB), r8(S8), rs(SS);
         bool ok = true;
         for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
-            const Work wk = decode_work(wi, m_tiles, num_tiles, nb, gsplit);
+            const Work wk = decode_work<GROUPED>(wi, m_tiles, num_tiles, nb, gsplit, M, N, n_tiles, gl);
             const int n0 = wk.n0;
             for (int kt = 0; kt < wk.nkt && ok; kt++) {
                 // ---- this K-tile's scales: issue the loads first, they complete behind the expansion below.
@@ -312,11 +338,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
 #pragma unroll
                     for (int g = 0; g < GPK; g++) vw[r][g] = 0.f;
                     if (!DUMP && n < N) {
-                        if (vec) load_scales4(sw + (size_t)n * nb + b0, vw[r]);
+                        const ST *swrow = sw + (size_t)(wk.wrow0 + n) * nb;
+                        if (vec) load_scales4(swrow + b0, vw[r]);
                         else {
 #pragma unroll
                             for (int g = 0; g < GPK; g++)
-                                if (b0 + g < wk.g1) vw[r][g] = sval(sw[(size_t)n * nb + b0 + g]);
+                                if (b0 + g < wk.g1) vw[r][g] = sval(swrow[b0 + g]);
                         }
                     }
                 }
@@ -325,7 +352,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
                     const int m = wk.m0 + dt + r * DEQ_WARPS * 32;
 #pragma unroll
                     for (int g = 0; g < GPK; g++) vx[r][g] = 0.f;
-                    if (!DUMP && m < M) {
+                    if (!DUMP && m < wk.mend) {
                         if (vec) load_scales4(xs + (size_t)m * nb + b0, vx[r]);
                         else {
 #pragma unroll
@@ -392,11 +419,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
         Ring rs(SS), rt(TB);
         bool ok = true;
         for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
-            const Work wk = decode_work(wi, m_tiles, num_tiles, nb, gsplit);
+            const Work wk = decode_work<GROUPED>(wi, m_tiles, num_tiles, nb, gsplit, M, N, n_tiles, gl);
             const int m0 = wk.m0, n0 = wk.n0;
             const int m = m0 + quad * 32 + lane;
             // a warp whose 32 rows all lie beyond M only keeps the barriers moving
-            const bool rows_live = (m0 + quad * 32) < M;
+            const bool rows_live = (m0 + quad * 32) < wk.mend;
             float acc[EPI_COLS];
 #pragma unroll
             for (int j = 0; j < EPI_COLS; j++) acc[j] = 0.f;
@@ -431,7 +458,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
                 ptx::tmem_ld_wait();
                 if (rows_live) ptx::tmem_ld(tcur + EPI_CH, d1);
                 if (rows_live) {
-                    if (DUMP) epi_dump<EPI_CH>(d0, Dout, m, M, n0 + col0, N, nb, wk.g0 + gi);
+                    if (DUMP) epi_dump<EPI_CH>(d0, Dout, m, wk.mend, n0 + col0, N, nb, wk.g0 + gi);
                     else epi_chunk<EPI, EPI_CH>(d0, x, ssw + g * BN, acc);
                 }
                 // ---- second half: wait, release the accumulator buffer, start the next group's load
@@ -447,7 +474,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
                     if (rows_live) ptx::tmem_ld(tlane + rt.stage * BN, d0);
                 }
                 if (rows_live) {
-                    if (DUMP) epi_dump<EPI_CH>(d1, Dout, m, M, n0 + col0 + EPI_CH, N, nb, wk.g0 + gi);
+                    if (DUMP) epi_dump<EPI_CH>(d1, Dout, m, wk.mend, n0 + col0 + EPI_CH, N, nb, wk.g0 + gi);
                     else epi_chunk<EPI, EPI_CH>(d1, x, ssw + g * BN + EPI_CH, acc + EPI_CH);
                 }
                 if (g == GPK - 1 || gi + 1 == ngroups) {   // done with this K-tile's scales
@@ -457,7 +484,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
                 }
             }
             if (!ok) break;
-            if (!DUMP && ok && m < M) {
+            if (!DUMP && ok && m < wk.mend) {
                 const int nleft = N - (n0 + col0);
                 const int targets = PEER ? oa.peers->world : 1;
                 for (int k = 0; k < targets; k++) {
@@ -501,15 +528,18 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
 }
 
 // ---- host side ------------------------------------------------------------------------------------
-template <typename ST, bool DUMP, int EPI, bool PEER = false>
+// experts > 0: grouped launch (GROUPED instantiation): M = sorted activation rows, N = outputs per expert, Wq / sw the
+// flat tensors of `experts` experts, gl the item list; max_items bounds the list's length (grid size only).
+template <typename ST, bool DUMP, int EPI, bool PEER = false, bool GROUPED = false>
 inline int launch_tc_e(const int8_t *X, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int32_t *D,
-                       int M, int N, int K, int nsplit, int gsplit, cudaStream_t st, const OutArgs &oa) {
+                       int M, int N, int K, int nsplit, int gsplit, cudaStream_t st, const OutArgs &oa,
+                       const GroupList &gl = GroupList(), int experts = 0, int max_items = 0) {
     CUtensorMap tmA, tmB;
     int rc = make_tmap_u8(&tmA, X, (uint64_t)K, (uint64_t)M, KT, BM, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != W4A8_OK) return rc;
-    rc = make_tmap_u8(&tmB, Wq, (uint64_t)K / 2, (uint64_t)N, KT / 2, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
+    rc = make_tmap_u8(&tmB, Wq, (uint64_t)K / 2, (uint64_t)N * (GROUPED ? experts : 1), KT / 2, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != W4A8_OK) return rc;
-    auto kern = gemm_w4a8_tc_kernel<ST, DUMP, EPI, PEER>;
+    auto kern = gemm_w4a8_tc_kernel<ST, DUMP, EPI, PEER, GROUPED>;
     static PerDevice<bool> configured_dev;              // the opt-in is a per-device function attribute
     bool &configured = configured_dev.get();
     if (!configured) {
@@ -517,11 +547,20 @@ inline int launch_tc_e(const int8_t *X, const float *xs, const uint8_t *Wq, cons
         if (e != cudaSuccess) return cuda_fail(e, "gemm smem opt-in");
         configured = true;
     }
-    const long tiles = (long)((M + BM - 1) / BM) * ((N + BN - 1) / BN) * nsplit;
+    const long tiles = GROUPED ? (long)max_items * ((N + BN - 1) / BN) : (long)((M + BM - 1) / BM) * ((N + BN - 1) / BN) * nsplit;
     const int sms = sm_count();
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, xs, sw, Y, D, M, N, K, nsplit, gsplit, PEER ? oa : OutArgs());
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, xs, sw, Y, D, M, N, K, nsplit, gsplit, PEER ? oa : OutArgs(), gl);
     return launch_status("gemm_w4a8_tc");
+}
+
+// Grouped experts: Y[sorted row, n] for the rows and experts the item list names (rows of experts without an item,
+// and rows no item covers, are not written).  Same arithmetic per (row, expert) as launch_tc.
+inline int launch_tc_grouped(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int rows, int N, int K,
+                             int scale_dtype, int experts, const GroupList &gl, int max_items, cudaStream_t st) {
+    if (scale_dtype == 1)
+        return launch_tc_e<__half, false, 2, false, true>(X, xs, Wq, (const __half *)sw, Y, nullptr, rows, N, K, 1, K / QBLK, st, OutArgs(), gl, experts, max_items);
+    return launch_tc_e<float, false, 2, false, true>(X, xs, Wq, (const float *)sw, Y, nullptr, rows, N, K, 1, K / QBLK, st, OutArgs(), gl, experts, max_items);
 }
 
 // Needs X and Wq 16-byte aligned (TMA global address rule); the caller checks.

@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tcf_kernel(
             Ring ra(SR), rb(SR);
             bool ok = true;
             for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
-                const Work wk = decode_work(wi, m_tiles, num_tiles, nb, gsplit);
+                const Work wk = decode_work<false>(wi, m_tiles, num_tiles, nb, gsplit, M, N, n_tiles, gemm::GroupList());
                 for (int kt = 0; kt < wk.nkt && ok; kt++) {
                     const int kel = (wk.g0 + kt * GPK) * QBLK;
                     if (!ptx::mbar_wait(BAR(AR_EMPTY + ra.stage), ra.phase ^ 1u)) { dev_set_error(gemm::ERR_PRODUCER | 1); ok = false; break; }
@@ -218,7 +218,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tcf_kernel(
             const uint32_t idesc = umma_idesc_f16(BM, BN);
             bool ok = true;
             for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
-                const Work wk = decode_work(wi, m_tiles, num_tiles, nb, gsplit);
+                const Work wk = decode_work<false>(wi, m_tiles, num_tiles, nb, gsplit, M, N, n_tiles, gemm::GroupList());
                 for (int kt = 0; kt < wk.nkt && ok; kt++) {
                     if (!ptx::mbar_wait(BAR(OP_FULL + ro.stage), ro.phase)) { dev_set_error(gemm::ERR_MMA | 1); ok = false; break; }
                     ptx::tc_fence_after_sync();
@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tcf_kernel(
         Ring ra(SR), rb(SR), ro(SO), rs(SS);
         bool ok = true;
         for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
-            const Work wk = decode_work(wi, m_tiles, num_tiles, nb, gsplit);
+            const Work wk = decode_work<false>(wi, m_tiles, num_tiles, nb, gsplit, M, N, n_tiles, gemm::GroupList());
             const int n0 = wk.n0;
             for (int kt = 0; kt < wk.nkt && ok; kt++) {
                 bool w = ptx::mbar_wait_warp(BAR(AR_FULL + ra.stage), ra.phase) && ptx::mbar_wait_warp(BAR(BR_FULL + rb.stage), rb.phase) &&
@@ -307,7 +307,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tcf_kernel(
         Ring rs(SS), rt(TB);
         bool ok = true;
         for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
-            const Work wk = decode_work(wi, m_tiles, num_tiles, nb, gsplit);
+            const Work wk = decode_work<false>(wi, m_tiles, num_tiles, nb, gsplit, M, N, n_tiles, gemm::GroupList());
             const int m0 = wk.m0, n0 = wk.n0;
             const int m = m0 + quad * 32 + lane;
             const bool rows_live = (m0 + quad * 32) < M;

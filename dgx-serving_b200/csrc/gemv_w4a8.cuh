@@ -29,6 +29,7 @@ constexpr int GEMV_MT_MAX = 4;     // activation rows handled per pass of the dp
 struct GroupedArgs {
     const int32_t *idx = nullptr;
     int topk = 1, x_per_slot = 0, num_experts = 0, nslots = 1;
+    int expert_base = 0;   // experts [expert_base, expert_base + num_experts) live in this Wq / sw (an expert shard)
 };
 
 __device__ __forceinline__ uint4 ldg_w16(const uint8_t *p, bool a16) {
@@ -112,8 +113,8 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_dp4a_kernel(
     if (ga.idx) {  // grouped experts: blockIdx.y = slot, one activation row against that slot's expert
         const int slot = blockIdx.y;
         pdl_wait();   // the routing indices are written by an earlier kernel of the stream (router / top-k): wait first
-        const int e = ga.idx[slot];
-        if (e < 0 || e >= ga.num_experts) return;   // invalid id: the slot's output row is left untouched
+        const int e = ga.idx[slot] - ga.expert_base;
+        if (e < 0 || e >= ga.num_experts) return;   // invalid id, or another rank's expert: the slot's output row is left untouched
         const int row = ga.x_per_slot ? slot : slot / ga.topk;
         xq += (size_t)row * IN;
         xs += (size_t)row * nb;
@@ -333,7 +334,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_short_kernel(
     if (ga.idx) {                                                   // blockIdx.y = slot (see the persistent kernel)
         const int slot = blockIdx.y;
         pdl_wait();   // the routing indices are written by an earlier kernel of the stream: wait before reading them
-        const int e = ga.idx[slot];
+        const int e = ga.idx[slot] - ga.expert_base;
         if (e < 0 || e >= ga.num_experts) return;
         const int row = ga.x_per_slot ? slot : slot / ga.topk;
         xq += (size_t)row * IN;
@@ -435,11 +436,12 @@ inline int launch_gemv_short(const int8_t *xq, const float *xs, const uint8_t *W
 // Grouped experts: one launch, grid.y = slots, each slot one activation row against its expert.
 inline int launch_moe_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, const int32_t *idx,
                            float *Y, int nslots, int topk, int x_per_slot, int N, int K, int num_experts,
-                           int scale_dtype, cudaStream_t st) {
+                           int scale_dtype, cudaStream_t st, int expert_base = 0) {
     if (nslots == 0 || N == 0) return W4A8_OK;
     if (nslots > 65535) return fail(W4A8_ERR_UNSUPPORTED, "moe_gemv: at most 65535 slots per launch (got %d)", nslots);
     GroupedArgs ga;
     ga.idx = idx; ga.topk = topk; ga.x_per_slot = x_per_slot; ga.num_experts = num_experts; ga.nslots = nslots;
+    ga.expert_base = expert_base;
     if (K <= 32 * QBLK) {                                           // short rows: the R-rows-per-warp kernel
         if (scale_dtype == 1) return launch_gemv_short<__half>(xq, xs, Wq, (const __half *)sw, Y, K, N, st, ga);
         return launch_gemv_short<float>(xq, xs, Wq, (const float *)sw, Y, K, N, st, ga);

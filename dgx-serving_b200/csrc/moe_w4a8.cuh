@@ -1,0 +1,288 @@
+// Routed-expert MLP block in W4A8: the four launches of the reference's fused MoE path (models/moe_block.cuh:45-52:
+// grouped gate_up, swiglu, grouped down, fixed-order reduce — kernels/moe_fused.cuh:14-76) with the expert products
+// done in W4A8 arithmetic (activations quantized per 32-element block like every other matmul on this path; the
+// reference's own expert kernels are W4A32).  Kept from the reference: the flat expert tensors
+// experts_gate_up[E][2*MI][H] (rows [0,MI) gate, [MI,2*MI) up, kernels/moe_fused.cuh:40-42) and experts_down[E][H][MI]
+// (runtime/weights_qwen.cu:62-63), slot = token*topk + k with the expert id idx[slot] read on the device, the router
+// weight applied to the slot's down output, and the combine in ascending k without atomics (kernels/moe_fused.cuh:68-76).
+//
+// Few slots (decode): one grouped GEMV launch per projection, one CTA column per slot.  Many slots (prefill): the slots
+// are sorted by expert on the device and both projections run as grouped GEMMs on the tensor cores — work unit =
+// (expert, tile of up to 128 of its rows) x 128 output columns, every expert's weights streamed once.
+// An expert shard (experts [expert_base, expert_base + experts) on this rank) computes only the slots routed to its
+// experts; the slots' down outputs are then sent to every rank's arena (moe_push_rows_kernel) and every rank combines.
+#pragma once
+#include "common.cuh"
+#include "fused_quantize.cuh"
+#include "gemm_w4a8_tc.cuh"
+#include "gemv_w4a8.cuh"
+#include "peer_allgather.cuh"
+#include "quantize_x.cuh"
+
+namespace w4a8 {
+namespace moe {
+
+constexpr int MAX_EXPERTS = 1024;
+constexpr int TILE_ROWS = gemm::BM;
+
+// Byte offsets of the block's intermediates inside the caller's workspace (all 256-byte aligned).
+struct Layout {
+    size_t perm, pos, offsets, items, num_items;   // sort: sorted row -> slot, slot -> sorted row (-1: not on this rank),
+                                                   // first sorted row of every local expert [experts + 1], item list, its length
+    size_t xq, xs;                                 // quantized tokens [S][H], [S][H/32]
+    size_t xq_g, xs_g;                             // the same rows gathered per sorted row [nslots][H] (GEMM path)
+    size_t gu;                                     // gate|up outputs [nslots][2*MI] fp32 (GEMM path: sorted rows; GEMV path: slots)
+    size_t xq_h, xs_h;                             // quantized hidden activations [nslots][MI], [nslots][MI/32] (same row order)
+    size_t sout;                                   // down outputs [nslots][H] fp32 (same row order), router weight not applied yet
+    size_t bytes;
+    int max_items;
+};
+inline Layout layout_for(int S, int topk, int H, int MI, int experts) {
+    Layout l;
+    const size_t nslots = (size_t)S * topk;
+    size_t o = 0;
+    auto take = [&](size_t n) { const size_t at = o; o += (n + 255) & ~(size_t)255; return at; };
+    l.max_items = experts + (int)(nslots / TILE_ROWS) + 1;
+    l.perm = take(nslots * 4);
+    l.pos = take(nslots * 4);
+    l.offsets = take(((size_t)experts + 1) * 4);
+    l.items = take((size_t)l.max_items * 16);
+    l.num_items = take(4);
+    l.xq = take((size_t)S * H);
+    l.xs = take((size_t)S * (H / QBLK) * 4);
+    l.xq_g = take(nslots * H);
+    l.xs_g = take(nslots * (H / QBLK) * 4);
+    l.gu = take(nslots * 2 * MI * 4);
+    l.xq_h = take(nslots * MI);
+    l.xs_h = take(nslots * (MI / QBLK) * 4);
+    l.sout = take(nslots * H * 4);
+    l.bytes = o;
+    return l;
+}
+
+// One CTA.  Stable counting sort of the slots by local expert id (idx[slot] - expert_base; ids outside
+// [0, experts) belong to another rank or are invalid and get pos = -1), and the item list of the grouped GEMM.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int32_t *__restrict__ idx, int nslots, int expert_base, int experts,
+                                                        int *__restrict__ perm, int *__restrict__ pos, int *__restrict__ offsets,
+                                                        int4 *__restrict__ items, int *__restrict__ num_items) {
+    __shared__ int cnt[MAX_EXPERTS];
+    __shared__ int off[MAX_EXPERTS + 1];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    for (int e = tid; e < experts; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int s = tid; s < nslots; s += blockDim.x) {
+        const int e = idx[s] - expert_base;
+        if (e >= 0 && e < experts) atomicAdd(&cnt[e], 1);
+        else pos[s] = -1;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0, n = 0;
+        for (int e = 0; e < experts; e++) {
+            off[e] = run;
+            offsets[e] = run;
+            for (int t = 0; t < cnt[e]; t += TILE_ROWS) items[n++] = make_int4(e, run + t, min(TILE_ROWS, cnt[e] - t), 0);
+            run += cnt[e];
+        }
+        off[experts] = run;
+        offsets[experts] = run;
+        *num_items = n;
+    }
+    __syncthreads();
+    // placement: a warp takes an expert and walks the slots 32 at a time, so an expert's rows keep the slots' order
+    for (int e = warp; e < experts; e += nwarps) {
+        if (cnt[e] == 0) continue;
+        int placed = 0;
+        for (int s0 = 0; s0 < nslots; s0 += 32) {
+            const int s = s0 + lane;
+            const bool mine = s < nslots && idx[s] - expert_base == e;
+            const unsigned m = __ballot_sync(0xffffffffu, mine);
+            if (mine) {
+                const int p = off[e] + placed + __popc(m & ((1u << lane) - 1u));
+                perm[p] = s;
+                pos[s] = p;
+            }
+            placed += __popc(m);
+        }
+    }
+}
+
+// Sorted row p < offsets[experts] gets the quantized activations of its token perm[p] / topk.
+__global__ void __launch_bounds__(128) moe_gather_rows_kernel(const int8_t *__restrict__ xq, const float *__restrict__ xs,
+                                                              const int *__restrict__ perm, const int *__restrict__ count, int topk, int K,
+                                                              int8_t *__restrict__ xq_g, float *__restrict__ xs_g) {
+    const int n = *count, nb = K / QBLK;
+    for (int p = blockIdx.x; p < n; p += gridDim.x) {
+        const int tok = perm[p] / topk;
+        const uint4 *src = reinterpret_cast<const uint4 *>(xq + (size_t)tok * K);
+        uint4 *dst = reinterpret_cast<uint4 *>(xq_g + (size_t)p * K);
+        for (int i = threadIdx.x; i < K / 16; i += blockDim.x) dst[i] = src[i];
+        for (int i = threadIdx.x; i < nb; i += blockDim.x) xs_g[(size_t)p * nb + i] = xs[(size_t)tok * nb + i];
+    }
+}
+
+// out[b, o] = sum over k ascending of dw[b*topk + k] * Sout[row(b*topk + k), o], starting from 0: the values and the
+// order of kernels/moe_fused.cuh:64 (router weight times the slot's down output, one rounding) and :68-76.
+// pos != nullptr: Sout is in sorted-row order, row(slot) = pos[slot] (slots with pos < 0 contribute nothing);
+// pos == nullptr: Sout is in slot order.  H a multiple of 4.
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float4 *__restrict__ Sout, const int *__restrict__ pos, const float *__restrict__ dw,
+                                                          float4 *__restrict__ out, int H4, int topk, long total /* = S * H4 */) {
+    const long stride = (long)gridDim.x * blockDim.x;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long b = i / H4;
+        const int o = (int)(i - b * H4);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < topk; k++) {
+            const long slot = b * topk + k;
+            const long row = pos ? pos[slot] : slot;
+            if (row < 0) continue;
+            const float w = dw[slot];
+            const float4 v = Sout[row * H4 + o];
+            acc.x = __fadd_rn(acc.x, __fmul_rn(w, v.x));
+            acc.y = __fadd_rn(acc.y, __fmul_rn(w, v.y));
+            acc.z = __fadd_rn(acc.z, __fmul_rn(w, v.z));
+            acc.w = __fadd_rn(acc.w, __fmul_rn(w, v.w));
+        }
+        out[i] = acc;
+    }
+}
+
+// Expert shard: the down outputs of this rank's slots (rows p < *count of `src`; src row = p when sorted != 0, else the
+// slot) go to row perm[p] of the slot-ordered buffer at y_off in EVERY rank's arena, 16-byte stores, consecutive lanes
+// on consecutive pieces of a row; then one system fence per CTA, the last CTA publishes `epoch` and (wait_limit > 0)
+// waits for every rank's flag.
+__global__ void __launch_bounds__(256) moe_push_rows_kernel(const PeerDesc *p, const float4 *__restrict__ src, int sorted,
+                                                            const int *__restrict__ perm, const int *__restrict__ count, int H4, size_t y_off,
+                                                            unsigned int epoch, long long wait_limit) {
+    const int n = *count, world = p->world;
+    for (int r = blockIdx.x; r < n; r += gridDim.x) {
+        const int slot = perm[r];
+        const float4 *s = src + (size_t)(sorted ? r : slot) * H4;
+        for (int i = threadIdx.x; i < H4; i += blockDim.x) {
+            const float4 v = s[i];
+            for (int k = 0; k < world; k++) reinterpret_cast<float4 *>(p->base[k] + y_off)[(size_t)slot * H4 + i] = v;
+        }
+    }
+    __syncthreads();
+    __shared__ unsigned int s_last;
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        s_last = (atomicAdd(p->counter, 1u) == gridDim.x - 1) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    if (threadIdx.x == 0) {
+        *p->counter = 0u;
+        publish_flags(p, epoch);
+    }
+    if (wait_limit > 0 && threadIdx.x < 32) wait_flags(p, epoch, wait_limit);
+}
+
+struct BlockArgs {
+    const float *n2 = nullptr;                                   // [S][H] fp32 (post-attention norm output)
+    const uint8_t *gu_wq = nullptr, *dn_wq = nullptr;            // this rank's experts: [experts][2*MI][H/2], [experts][H][MI/2]
+    const void *gu_sc = nullptr, *dn_sc = nullptr;
+    const int32_t *idx = nullptr;                                // [S*topk] global expert ids (device)
+    const float *dw = nullptr;                                   // [S*topk] router weights (device)
+    float *out = nullptr;                                        // [S][H]
+    int S = 0, topk = 0, H = 0, MI = 0, expert_base = 0, experts = 0, scale_dtype = 0, act = 0;
+    int kernel = 0;                                              // 0 auto, 1 grouped GEMV, 2 grouped GEMM
+    unsigned char *ws = nullptr;
+    const PeerDesc *peers = nullptr;                             // expert shard: every arena's slot-ordered Sout at sout_off
+    unsigned char *arena_base = nullptr;
+    size_t sout_off = 0;
+    unsigned int epoch = 0;
+    long long wait_limit = 0;
+    int phase = 0;                                               // expert shard: 0 whole block, 1 up to the publish (no wait, no combine),
+                                                                 //               2 wait + combine only
+};
+
+constexpr int GEMV_MAX_SLOTS = 128;   // auto: up to this many slots one CTA column per slot, above it the sorted GEMM
+
+struct Buffers {
+    int *perm, *pos, *offsets, *num_items;
+    int4 *items;
+    int8_t *xq, *xq_g, *xq_h;
+    float *xs, *xs_g, *xs_h, *gu, *sout;
+    int max_items;
+};
+inline Buffers buffers_of(const BlockArgs &a) {
+    const Layout l = layout_for(a.S, a.topk, a.H, a.MI, a.experts);
+    unsigned char *ws = a.ws;
+    Buffers b;
+    b.perm = reinterpret_cast<int *>(ws + l.perm); b.pos = reinterpret_cast<int *>(ws + l.pos);
+    b.offsets = reinterpret_cast<int *>(ws + l.offsets); b.num_items = reinterpret_cast<int *>(ws + l.num_items);
+    b.items = reinterpret_cast<int4 *>(ws + l.items);
+    b.xq = reinterpret_cast<int8_t *>(ws + l.xq); b.xq_g = reinterpret_cast<int8_t *>(ws + l.xq_g); b.xq_h = reinterpret_cast<int8_t *>(ws + l.xq_h);
+    b.xs = reinterpret_cast<float *>(ws + l.xs); b.xs_g = reinterpret_cast<float *>(ws + l.xs_g); b.xs_h = reinterpret_cast<float *>(ws + l.xs_h);
+    b.gu = reinterpret_cast<float *>(ws + l.gu); b.sout = reinterpret_cast<float *>(ws + l.sout);
+    b.max_items = l.max_items;
+    return b;
+}
+
+// quantize, (sort, gather,) gate|up, activation + quantize, down; with peers: send this rank's rows on and publish
+// (wait_limit > 0: and wait for every rank).
+inline int launch_experts(const BlockArgs &a, const Buffers &b, bool use_gemm, long long wait_limit, cudaStream_t st) {
+    const int nslots = a.S * a.topk, sms = sm_count();
+    int rc = launch_quantize_x(a.n2, b.xq, b.xs, nullptr, a.H, a.S, st);
+    if (rc != W4A8_OK) return rc;
+    if (use_gemm || a.peers) {
+        moe_sort_kernel<<<1, 1024, 0, st>>>(a.idx, nslots, a.expert_base, a.experts, b.perm, b.pos, b.offsets, b.items, b.num_items);
+        rc = launch_status("moe_sort");
+        if (rc != W4A8_OK) return rc;
+    }
+    if (use_gemm) {
+        const unsigned gg = (unsigned)(nslots < sms * 8 ? nslots : sms * 8);
+        moe_gather_rows_kernel<<<gg, 128, 0, st>>>(b.xq, b.xs, b.perm, b.offsets + a.experts, a.topk, a.H, b.xq_g, b.xs_g);
+        rc = launch_status("moe_gather_rows");
+        if (rc != W4A8_OK) return rc;
+        gemm::GroupList gl;
+        gl.items = b.items; gl.num_items = b.num_items;
+        rc = gemm::launch_tc_grouped(b.xq_g, b.xs_g, a.gu_wq, a.gu_sc, b.gu, nslots, 2 * a.MI, a.H, a.scale_dtype, a.experts, gl, b.max_items, st);
+        if (rc != W4A8_OK) return rc;
+        rc = launch_glu_quantize(b.gu, b.gu + a.MI, a.act, nullptr, b.xq_h, b.xs_h, nullptr, a.MI, nslots, st, 2L * a.MI);
+        if (rc != W4A8_OK) return rc;
+        rc = gemm::launch_tc_grouped(b.xq_h, b.xs_h, a.dn_wq, a.dn_sc, b.sout, nslots, a.H, a.MI, a.scale_dtype, a.experts, gl, b.max_items, st);
+        if (rc != W4A8_OK) return rc;
+    } else {
+        rc = launch_moe_gemv(b.xq, b.xs, a.gu_wq, a.gu_sc, a.idx, b.gu, nslots, a.topk, 0, 2 * a.MI, a.H, a.experts, a.scale_dtype, st, a.expert_base);
+        if (rc != W4A8_OK) return rc;
+        rc = launch_glu_quantize(b.gu, b.gu + a.MI, a.act, nullptr, b.xq_h, b.xs_h, nullptr, a.MI, nslots, st, 2L * a.MI);
+        if (rc != W4A8_OK) return rc;
+        rc = launch_moe_gemv(b.xq_h, b.xs_h, a.dn_wq, a.dn_sc, a.idx, b.sout, nslots, a.topk, 1, a.H, a.MI, a.experts, a.scale_dtype, st, a.expert_base);
+        if (rc != W4A8_OK) return rc;
+    }
+    if (a.peers) {
+        const unsigned pg = (unsigned)(nslots < sms * 4 ? nslots : sms * 4);
+        moe_push_rows_kernel<<<pg, 256, 0, st>>>(a.peers, reinterpret_cast<const float4 *>(b.sout), use_gemm ? 1 : 0, b.perm, b.offsets + a.experts,
+                                                  a.H / 4, a.sout_off, a.epoch, wait_limit);
+        rc = launch_status("moe_push_rows");
+    }
+    return rc;
+}
+
+inline int launch_block(const BlockArgs &a, cudaStream_t st) {
+    const int nslots = a.S * a.topk, sms = sm_count();
+    const Buffers b = buffers_of(a);
+    const bool use_gemm = a.kernel == 2 || (a.kernel == 0 && nslots > GEMV_MAX_SLOTS);
+    int rc = W4A8_OK;
+    if (a.peers && a.phase == 2) {
+        allgather_wait_kernel<<<1, 32, 0, st>>>(a.peers, a.epoch, a.wait_limit);
+        rc = launch_status("allgather_wait");
+    } else {
+        rc = launch_experts(a, b, use_gemm, a.phase == 1 ? 0 : a.wait_limit, st);
+    }
+    if (rc != W4A8_OK || (a.peers && a.phase == 1)) return rc;
+    // one GPU: the down outputs as computed (sorted rows through pos, or slot order); expert shard: the slot-ordered
+    // buffer of this rank's arena, complete once every rank's flag has arrived
+    const float4 *src = a.peers ? reinterpret_cast<const float4 *>(a.arena_base + a.sout_off) : reinterpret_cast<const float4 *>(b.sout);
+    const int *pos = (!a.peers && use_gemm) ? b.pos : nullptr;
+    const long total = (long)a.S * (a.H / 4);
+    const long want = (total + 255) / 256;
+    const unsigned cg = (unsigned)(want < (long)sms * 8 ? (want > 0 ? want : 1) : (long)sms * 8);
+    moe_combine_kernel<<<cg, 256, 0, st>>>(src, pos, a.dw, reinterpret_cast<float4 *>(a.out), a.H / 4, a.topk, total);
+    return launch_status("moe_combine");
+}
+
+}  // namespace moe
+}  // namespace w4a8

@@ -17,6 +17,7 @@
 #include "gemv_w4a8_tc.cuh"
 #include "gemm_w4a8_tc.cuh"
 #include "gemm_w4a8_tcf.cuh"
+#include "moe_w4a8.cuh"
 
 namespace w4a8 {
 
@@ -253,6 +254,8 @@ static int gemm_launch(const int8_t *X, const float *xs, const uint8_t *Wq, cons
     return gemmf::launch(X, xs, Wq, sw, Y, M, N, K, scale_dtype, nsplit, gsplit, st);
 }
 
+static int g_moe_policy = 0;   // w4a8_moe_block: 0 auto (by slot count), 1 grouped GEMV, 2 sorted grouped GEMM
+
 W4A8_API int w4a8_config(const char *key, int value) {
     if (!key) return fail(W4A8_ERR_ARG, "config: null key");
     if (!strcmp(key, "gemm_kernel")) {
@@ -264,6 +267,11 @@ W4A8_API int w4a8_config(const char *key, int value) {
         if (value < 0 || value > 5 || value == 4)
             return fail(W4A8_ERR_ARG, "config: gemv_kernel = 0 (auto), 1 (dp4a), 2 (mma.sync tensor path), 3 (bulk-copy stream for S = 1), 5 (tcgen05 tensor path); got %d", value);
         g_gemv_policy = value;
+        return W4A8_OK;
+    }
+    if (!strcmp(key, "moe_kernel")) {
+        if (value < 0 || value > 2) return fail(W4A8_ERR_ARG, "config: moe_kernel = 0 (auto), 1 (grouped GEMV), 2 (sorted grouped GEMM); got %d", value);
+        g_moe_policy = value;
         return W4A8_OK;
     }
     return fail(W4A8_ERR_ARG, "config: unknown key '%s'", key);
@@ -335,6 +343,7 @@ W4A8_API int w4a8_gemm(const int8_t *X, const float *xs, const uint8_t *Wq, cons
 
 // Split count and groups per split.  Boundaries follow the reference: K-tiles of 64 (2 groups), ranges of
 // ceil(niter/splitk) K-tiles (kernels/gemm_mmq.cuh:138-139), default split count ~96 CTAs clamp 1..8 (:209-210).
+constexpr int SPLITK_MAX = 4096;   // explicit split counts above this are refused (K = 131072 has 2048 K-tiles of 64)
 static void splitk_plan(int N, int K, int splitk_in, int *nsplit, int *gsplit) {
     const int nb = K / QBLK;
     const int niter = (nb + 1) / 2;
@@ -350,7 +359,7 @@ static void splitk_plan(int N, int K, int splitk_in, int *nsplit, int *gsplit) {
 }
 
 W4A8_API size_t w4a8_gemm_splitk_workspace_bytes(int M, int N, int K, int splitk) {
-    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (M <= 0 || N <= 0 || K <= 0 || splitk > SPLITK_MAX) return 0;
     int ns, gs;
     splitk_plan(N, K, splitk, &ns, &gs);
     return ns > 1 ? (size_t)ns * M * N * sizeof(float) : 0;
@@ -359,6 +368,7 @@ W4A8_API size_t w4a8_gemm_splitk_workspace_bytes(int M, int N, int K, int splitk
 W4A8_API int w4a8_gemm_splitk(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int M, int N,
                               int K, int scale_dtype, int splitk, void *workspace, size_t workspace_bytes, void *stream) {
     if (M < 0 || N < 0) return fail(W4A8_ERR_ARG, "gemm_splitk: negative size M=%d N=%d", M, N);
+    if (splitk > SPLITK_MAX) return fail(W4A8_ERR_ARG, "gemm_splitk: splitk=%d (0 = automatic, at most %d)", splitk, SPLITK_MAX);
     if (M == 0 || N == 0) return W4A8_OK;
     int rc = check_common(X, xs, Wq, sw, Y, K, scale_dtype, "gemm_splitk");
     if (rc != W4A8_OK) return rc;
@@ -387,8 +397,10 @@ W4A8_API int w4a8_gemm_splitk(const int8_t *X, const float *xs, const uint8_t *W
 // In host code this name is only a handle for cudaGetSymbolAddress, never a usable pointer.
 static __device__ __align__(256) float g_splitk_static_scratch[W4A8_SPLITK_STATIC_BYTES / sizeof(float)];
 
-// Device address of the buffer on the current device; queried once per device and cached.
-static int splitk_static_ptr(float **out) {
+// Device address of the buffer on the current device; queried once per device and cached.  The query itself is not a
+// stream operation, but the first call on a device also loads the module and configures the kernels, which a stream
+// capture in progress does not allow: that case is refused with a message instead of failing somewhere inside.
+static int splitk_static_ptr(float **out, cudaStream_t st) {
     constexpr int MAX_DEV = 64;
     static float *cached[MAX_DEV] = {nullptr};
     int dev = 0;
@@ -396,6 +408,12 @@ static int splitk_static_ptr(float **out) {
     if (e != cudaSuccess) return cuda_fail(e, "gemm_splitk_static: cudaGetDevice");
     if (dev < 0 || dev >= MAX_DEV) return fail(W4A8_ERR_UNSUPPORTED, "gemm_splitk_static: device index %d out of range", dev);
     if (!cached[dev]) {
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        e = cudaStreamIsCapturing(st, &cs);
+        if (e != cudaSuccess) return cuda_fail(e, "gemm_splitk_static: cudaStreamIsCapturing");
+        if (cs != cudaStreamCaptureStatusNone)
+            return fail(W4A8_ERR_UNSUPPORTED, "gemm_splitk_static: the first call on a device must not be made while the stream is "
+                                              "being captured (it looks up the built-in buffer); call it once outside the capture first");
         float *p = nullptr;
         e = cudaGetSymbolAddress((void **)&p, g_splitk_static_scratch);
         if (e != cudaSuccess || !p) return cuda_fail(e, "gemm_splitk_static: cudaGetSymbolAddress");
@@ -408,6 +426,7 @@ static int splitk_static_ptr(float **out) {
 W4A8_API int w4a8_gemm_splitk_static(const int8_t *X, const float *xs, const uint8_t *Wq, const void *sw, float *Y, int M, int N,
                                      int K, int scale_dtype, int splitk, void *stream) {
     if (M < 0 || N < 0) return fail(W4A8_ERR_ARG, "gemm_splitk_static: negative size M=%d N=%d", M, N);
+    if (splitk > SPLITK_MAX) return fail(W4A8_ERR_ARG, "gemm_splitk_static: splitk=%d (0 = automatic, at most %d)", splitk, SPLITK_MAX);
     if (M == 0 || N == 0) return W4A8_OK;
     int rc = check_common(X, xs, Wq, sw, Y, K, scale_dtype, "gemm_splitk_static");
     if (rc != W4A8_OK) return rc;
@@ -426,7 +445,7 @@ W4A8_API int w4a8_gemm_splitk_static(const int8_t *X, const float *xs, const uin
     cudaStream_t st = (cudaStream_t)stream;
     if (ns == 1) return gemm_launch(X, xs, Wq, sw, Y, M, N, K, scale_dtype, 1, K / QBLK, st);
     float *scratch = nullptr;
-    rc = splitk_static_ptr(&scratch);
+    rc = splitk_static_ptr(&scratch, st);
     if (rc != W4A8_OK) return rc;
     // kernel 1 writes every partial sum [split][m][n], m < M, n < N (an empty K range writes zeros), kernel 2 reads
     // exactly those: nothing left over from an earlier call is ever read, so nothing needs clearing.
@@ -818,4 +837,76 @@ W4A8_API int w4a8_arena_advance_epoch(w4a8_arena *a, uint32_t delta, void *strea
     if (!a || !a->connected) return fail(W4A8_ERR_ARG, "arena_advance_epoch: arena not connected");
     allgather_advance_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(a->desc_dev, delta);
     return launch_status("allgather_advance");
+}
+
+// ---- routed-expert block ---------------------------------------------------------------------------------
+W4A8_API int w4a8_moe_layout_for(int S, int topk, int H, int MI, int experts, w4a8_moe_layout *out) {
+    if (!out || S < 0 || topk <= 0 || H <= 0 || MI <= 0 || experts <= 0 || experts > moe::MAX_EXPERTS || (long)S * topk > (1L << 24))
+        return fail(W4A8_ERR_ARG, "moe_layout_for: S=%d topk=%d H=%d MI=%d experts=%d (1..%d experts)", S, topk, H, MI, experts, moe::MAX_EXPERTS);
+    const moe::Layout l = moe::layout_for(S, topk, H, MI, experts);
+    out->perm = l.perm; out->pos = l.pos; out->offsets = l.offsets; out->items = l.items; out->num_items = l.num_items;
+    out->xq = l.xq; out->xs = l.xs; out->xq_g = l.xq_g; out->xs_g = l.xs_g; out->gu = l.gu; out->xq_h = l.xq_h; out->xs_h = l.xs_h;
+    out->sout = l.sout; out->bytes = l.bytes;
+    return W4A8_OK;
+}
+
+static int moe_block_impl(const float *n2, const uint8_t *gu_wq, const void *gu_sc, const uint8_t *dn_wq, const void *dn_sc,
+                          const int32_t *idx, const float *dw, float *out, int S, int topk, int H, int MI, int expert_base, int experts,
+                          int scale_dtype, int act, void *workspace, size_t workspace_bytes, w4a8_arena *a, size_t sout_offset,
+                          uint32_t epoch, int timeout_us, int phase, cudaStream_t st, const char *who) {
+    if (phase < 0 || phase > 2) return fail(W4A8_ERR_ARG, "%s: phase=%d (0 whole block, 1 compute + publish, 2 wait + combine)", who, phase);
+    if (S < 0 || topk <= 0 || experts <= 0 || experts > moe::MAX_EXPERTS || expert_base < 0)
+        return fail(W4A8_ERR_ARG, "%s: bad sizes S=%d topk=%d experts=%d expert_base=%d", who, S, topk, experts, expert_base);
+    if (H <= 0 || MI <= 0 || H % QBLK != 0 || MI % QBLK != 0)
+        return fail(W4A8_ERR_ARG, "%s: H=%d and MI=%d must be positive multiples of %d", who, H, MI, QBLK);
+    if (scale_dtype < 0 || scale_dtype > 1) return fail(W4A8_ERR_ARG, "%s: scale_dtype=%d (0 fp32, 1 fp16)", who, scale_dtype);
+    if (act < 0 || act > 1) return fail(W4A8_ERR_ARG, "%s: act=%d (0 SwiGLU, 1 GeGLU)", who, act);
+    const long nslots = (long)S * topk;
+    if (nslots > (1L << 24)) return fail(W4A8_ERR_UNSUPPORTED, "%s: at most 2^24 slots (got %ld)", who, nslots);
+    if (a && !a->connected) return fail(W4A8_ERR_ARG, "%s: arena not connected", who);
+    if (a && (sout_offset % 256 != 0 || sout_offset + (size_t)nslots * H * sizeof(float) > a->bytes))
+        return fail(W4A8_ERR_ARG, "%s: Sout[%ld x %d] at offset %zu does not fit the %zu-byte arena", who, nslots, H, sout_offset, a->bytes);
+    if (S == 0) {
+        if (!a) return W4A8_OK;
+        allgather_publish_kernel<<<1, 32, 0, st>>>(a->desc_dev, epoch, wait_cycles(timeout_us));   // still takes part in the step
+        return launch_status("allgather_publish");
+    }
+    if (!n2 || !gu_wq || !gu_sc || !dn_wq || !dn_sc || !idx || !dw || !out || !workspace)
+        return fail(W4A8_ERR_ARG, "%s: null pointer argument", who);
+    if (!aligned(n2, 16) || !aligned(out, 16) || !aligned(gu_wq, 16) || !aligned(dn_wq, 16) || !aligned(gu_sc, 16) || !aligned(dn_sc, 16) ||
+        !aligned(workspace, 256))
+        return fail(W4A8_ERR_ALIGN, "%s: n2, out, the weight and scale tensors must be 16-byte aligned, the workspace 256-byte aligned", who);
+    const moe::Layout l = moe::layout_for(S, topk, H, MI, experts);
+    if (workspace_bytes < l.bytes) return fail(W4A8_ERR_ARG, "%s: workspace of %zu bytes, %zu needed (w4a8_moe_layout_for)", who, workspace_bytes, l.bytes);
+    int rc = require_sm100();
+    if (rc != W4A8_OK) return rc;
+    const bool use_gemm = g_moe_policy == 2 || (g_moe_policy == 0 && nslots > moe::GEMV_MAX_SLOTS);
+    if (!use_gemm && nslots > 65535) return fail(W4A8_ERR_UNSUPPORTED, "%s: the grouped GEMV takes at most 65535 slots (got %ld)", who, nslots);
+    if (use_gemm && (H % 32 != 0 || MI % 32 != 0)) return fail(W4A8_ERR_UNSUPPORTED, "%s: the grouped GEMM needs H and MI multiples of 32", who);
+    moe::BlockArgs b;
+    b.n2 = n2; b.gu_wq = gu_wq; b.gu_sc = gu_sc; b.dn_wq = dn_wq; b.dn_sc = dn_sc; b.idx = idx; b.dw = dw; b.out = out;
+    b.S = S; b.topk = topk; b.H = H; b.MI = MI; b.expert_base = expert_base; b.experts = experts; b.scale_dtype = scale_dtype; b.act = act;
+    b.kernel = use_gemm ? 2 : 1;
+    b.ws = static_cast<unsigned char *>(workspace);
+    if (a) {
+        b.peers = a->desc_dev; b.arena_base = a->base; b.sout_off = sout_offset; b.epoch = epoch; b.wait_limit = wait_cycles(timeout_us);
+        b.phase = phase;
+    }
+    return moe::launch_block(b, st);
+}
+
+W4A8_API int w4a8_moe_block(const float *n2, const uint8_t *gu_wq, const void *gu_sc, const uint8_t *dn_wq, const void *dn_sc,
+                            const int32_t *idx, const float *dw, float *out, int S, int topk, int H, int MI, int num_experts,
+                            int scale_dtype, int act, void *workspace, size_t workspace_bytes, void *stream) {
+    return moe_block_impl(n2, gu_wq, gu_sc, dn_wq, dn_sc, idx, dw, out, S, topk, H, MI, 0, num_experts, scale_dtype, act, workspace,
+                          workspace_bytes, nullptr, 0, 0, 0, 0, (cudaStream_t)stream, "moe_block");
+}
+
+W4A8_API int w4a8_moe_block_shard(const float *n2, const uint8_t *gu_wq, const void *gu_sc, const uint8_t *dn_wq, const void *dn_sc,
+                                  const int32_t *idx, const float *dw, float *out, int S, int topk, int H, int MI, int expert_base,
+                                  int experts_local, int scale_dtype, int act, void *workspace, size_t workspace_bytes, w4a8_arena *a,
+                                  size_t sout_offset, uint32_t epoch, int timeout_us, int phase, void *stream) {
+    if (!a) return fail(W4A8_ERR_ARG, "moe_block_shard: null arena");
+    return moe_block_impl(n2, gu_wq, gu_sc, dn_wq, dn_sc, idx, dw, out, S, topk, H, MI, expert_base, experts_local, scale_dtype, act,
+                          workspace, workspace_bytes, a, sout_offset, epoch, timeout_us, phase, (cudaStream_t)stream, "moe_block_shard");
 }

@@ -7,6 +7,16 @@
 #include "qscale.cuh"
 #include "reduce.cuh"
 
+#ifdef __CUDACC__
+// Device helper other files of the reference borrow from its header (kernels/gemv_w4a8.cuh:16-21; tools/probe_*.cu):
+// two packed bytes = four 4-bit codes (low nibble first) -> four signed bytes (code - 8), the dp4a operand.
+static __device__ __forceinline__ int w4a8_pk(int lo_byte, int hi_byte) {
+    const unsigned v = (unsigned)(lo_byte & 0x0F) | ((unsigned)(lo_byte & 0xF0) << 4) | ((unsigned)(hi_byte & 0x0F) << 16) |
+                       ((unsigned)(hi_byte & 0xF0) << 20);       // one code per byte
+    return (int)__vsub4(v, 0x08080808u);                         // minus 8 in every byte
+}
+#endif
+
 static inline void launch_gemv_w4a8(const int8_t *xq, const float *xs, const int32_t * /*xsum*/, const uint8_t *Wq,
                                     const void *sw, float *Y, int IN, int OUT, int S, int scale_dtype = 0,
                                     cudaStream_t st = 0) {

@@ -193,12 +193,59 @@ int w4a8_linear_host(const float *X_host, float *Y_host, float *X_dev, int8_t *x
 /* ---- grouped experts (W4A8 semantics per expert) ----------------------------------------------------
  * The reference's expert kernels take fp32 activations (kernels/moe_fused.cuh:14-33); this keeps their
  * weight indexing — expert e starts e*(N*K/2) bytes into Wq and e*(N*K/32) scales into sw
- * (kernels/moe_fused.cuh:21-24), slot = token*topk + k, expert id idx[slot] read on the device — and
- * applies the dense W4A8 product per slot.  Y[nslots,N].  x_per_slot = 0: activations are per token
+ * (kernels/moe_fused.cuh:21-24), slot = token*topk + k, expert id idx[slot] read on the device (idx may be
+ * written by an earlier kernel of the same stream: the kernels wait for that dependency before their first read of
+ * it) — and applies the dense W4A8 product per slot.  Y[nslots,N].  x_per_slot = 0: activations are per token
  * (row slot/topk; gate/up projection); 1: per slot (down projection). */
 int w4a8_moe_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, const int32_t *idx,
                   float *Y, int nslots, int topk, int x_per_slot, int N, int K, int num_experts,
                   int scale_dtype, void *stream);
+
+/* ---- routed-expert MLP block (W4A8) ------------------------------------------------------------------
+ * Replaces the four launches of the reference's fused expert path at its call site (models/moe_block.cuh:45-52:
+ * launch_moe_fused_gu, _swiglu, _down, _reduce; kernels/moe_fused.cuh:14-76) — same tensors, same slot order, same
+ * fixed-order combine — with the expert products in W4A8 arithmetic (the reference's are W4A32):
+ *   xq, xs      = quantize_x_q8(n2)                                   per token, H elements
+ *   gu[slot]    = W4A8 product of token slot/topk with experts_gate_up[idx[slot]]      [2*MI] (gate rows, then up rows)
+ *   hid[slot]   = act(gu[slot][0:MI]) * gu[slot][MI:2*MI], quantized per 32-element block
+ *   so[slot]    = W4A8 product of hid[slot] with experts_down[idx[slot]]               [H]
+ *   out[b]      = sum over k ascending, from 0, of dw[b*topk+k] * so[b*topk+k]         (each product rounded once)
+ * gu_wq / gu_sc: flat [E][2*MI][H/2] bytes and [E][2*MI][H/32] scales; dn_wq / dn_sc: [E][H][MI/2], [E][H][MI/32]
+ * (runtime/weights_qwen.cu:62-63).  idx (global expert ids) and dw (router weights) are device arrays of S*topk
+ * entries written by earlier work of the stream; every id must name an existing expert.
+ * Up to 128 slots run as one grouped GEMV launch per projection; above that the slots are sorted by expert on the
+ * device and both projections run as grouped tensor-core GEMMs whose work units are (expert, up to 128 of its
+ * rows) x 128 outputs (w4a8_config("moe_kernel", 1 | 2) forces one).  Nothing is allocated: the intermediates live
+ * in the caller's workspace at the offsets w4a8_moe_layout_for reports (256-byte aligned device memory of
+ * layout.bytes bytes).  H and MI multiples of 32, at most 1024 experts. */
+typedef struct {
+    size_t perm, pos, offsets, items, num_items;  /* sort: sorted row -> slot; slot -> sorted row (-1: another rank's);
+                                                     first sorted row per local expert [experts+1]; int4 item list; its length */
+    size_t xq, xs;                                /* quantized tokens [S][H] int8, [S][H/32] fp32 */
+    size_t xq_g, xs_g;                            /* the same, gathered per sorted row [S*topk][H] (GEMM path) */
+    size_t gu;                                    /* [S*topk][2*MI] fp32; rows in sorted order (GEMM path) or slot order (GEMV path) */
+    size_t xq_h, xs_h;                            /* quantized hidden [S*topk][MI] int8, [S*topk][MI/32] fp32, same row order */
+    size_t sout;                                  /* down outputs [S*topk][H] fp32, same row order, router weight not applied */
+    size_t bytes;
+} w4a8_moe_layout;
+int w4a8_moe_layout_for(int S, int topk, int H, int MI, int experts, w4a8_moe_layout *out);
+int w4a8_moe_block(const float *n2, const uint8_t *gu_wq, const void *gu_sc, const uint8_t *dn_wq, const void *dn_sc,
+                   const int32_t *idx, const float *dw, float *out, int S, int topk, int H, int MI, int num_experts,
+                   int scale_dtype, int act, void *workspace, size_t workspace_bytes, void *stream);
+/* Expert-sharded form (new for multi-GPU; nothing in the reference): this rank holds experts
+ * [expert_base, expert_base + experts_local) — gu_wq etc. point at ITS experts — and n2, idx, dw are replicated.
+ * The rank computes only the slots routed to its experts, stores their down outputs into row `slot` of a
+ * slot-ordered buffer Sout[S*topk][H] at sout_offset in EVERY rank's arena (16-byte peer stores), publishes `epoch`,
+ * waits (bounded by timeout_us) for every rank's flag and then combines: every rank ends with the whole out[S][H],
+ * bit-identical to w4a8_moe_block with all experts on one GPU.  Arena rules as for w4a8_gemv_allgather (alternate
+ * sout_offset between consecutive steps); workspace from w4a8_moe_layout_for(S, topk, H, MI, experts_local).
+ * phase 0: the whole block.  phase 1: everything up to and including the publish (no wait, no combine) and
+ * phase 2: wait + combine only — for a caller that puts other work between the two, and for several ranks driven
+ * one after the other on one GPU, where a kernel must not wait for a rank that has not been launched yet. */
+int w4a8_moe_block_shard(const float *n2, const uint8_t *gu_wq, const void *gu_sc, const uint8_t *dn_wq, const void *dn_sc,
+                         const int32_t *idx, const float *dw, float *out, int S, int topk, int H, int MI, int expert_base,
+                         int experts_local, int scale_dtype, int act, void *workspace, size_t workspace_bytes,
+                         struct w4a8_arena *a, size_t sout_offset, uint32_t epoch, int timeout_us, int phase, void *stream);
 
 /* ---- a15: N-sharded weight upload --------------------------------------------------------------------
  * Replaces QMat + load_dev()/mat() (runtime/weights_qwen.h:8, runtime/weights_qwen.cu:12-36,

@@ -17,6 +17,8 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "liboracle.so")
 _REF_PATH = os.path.join(_HERE, "_ref", "libref_kernels.so")
+# the reference checkout: W4A8_REFERENCE_DIR, else a directory "reference" beside this repository
+_REF_TREE = os.environ.get("W4A8_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
 QBLK = 32
 _lib = None
 
@@ -25,9 +27,9 @@ def build(force=False):
     """Compiles liboracle.so (and, when the reference tree is present, _ref/libref_kernels.so)."""
     src = os.path.join(_HERE, "w4a8_oracle.c")
     stale = force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src)
-    if stale or (os.path.isdir("/root/reference/kernels") and not os.path.exists(_REF_PATH)):
+    if stale or (os.path.isdir(os.path.join(_REF_TREE, "kernels")) and not os.path.exists(_REF_PATH)):
         if os.path.exists("/usr/bin/make") and os.path.exists("/usr/bin/gcc"):
-            subprocess.run(["make", "-C", _HERE] + (["-B"] if force else []), check=True, capture_output=True)
+            subprocess.run(["make", "-C", _HERE, "REF=" + _REF_TREE] + (["-B"] if force else []), check=True, capture_output=True)
     return _LIB_PATH
 
 
@@ -166,6 +168,35 @@ def moe_w4a8(xq, xs, Wq, sw, idx, topk, x_per_slot, N, K):
                           _p(np.ascontiguousarray(sw)), _p(np.ascontiguousarray(idx, dtype=np.int32)), _p(Y),
                           nslots, topk, int(x_per_slot), N, K, _sd(sw))
     return Y
+
+
+def moe_combine(so, dw, topk):
+    """out[b] = sum_k (ascending, from 0) dw[b*topk+k] * so[b*topk+k]; so [nslots, H] float32, dw [nslots] float32."""
+    so = np.ascontiguousarray(so, dtype=np.float32)
+    dw = np.ascontiguousarray(dw, dtype=np.float32)
+    nslots, H = so.shape
+    S = nslots // topk
+    out = np.empty((S, H), dtype=np.float32)
+    lib().oracle_moe_combine(_p(so), _p(dw), _p(out), S, topk, H)
+    return out
+
+
+def moe_block_w4a8(n2, gu_wq, gu_sc, dn_wq, dn_sc, idx, dw, topk, act=0):
+    """The routed-expert block in W4A8, stage by stage (models/moe_block.cuh:45-52 with the expert products in W4A8):
+    quantize the tokens, gate|up product per slot against experts_gate_up[idx[slot]] ([E][2*MI][H], gate rows first,
+    kernels/moe_fused.cuh:40-42), act(gate)*up, quantize, down product per slot against experts_down[idx[slot]]
+    ([E][H][MI]), router weight and fixed-order combine (kernels/moe_fused.cuh:64,68-76).  Returns every stage."""
+    n2 = np.ascontiguousarray(n2, dtype=np.float32)
+    S, H = n2.shape
+    E, MI2 = gu_wq.shape[0], gu_wq.shape[1]
+    MI = MI2 // 2
+    xq, xs, _ = quantize_x_q8(n2)
+    gu = moe_w4a8(xq, xs, gu_wq.reshape(E * MI2, H // 2), gu_sc.reshape(E * MI2, H // QBLK), idx, topk, 0, MI2, H)
+    hid = glu(gu[:, :MI], gu[:, MI:], act)
+    xq_h, xs_h, _ = quantize_x_q8(hid)
+    so = moe_w4a8(xq_h, xs_h, dn_wq.reshape(E * H, MI // 2), dn_sc.reshape(E * H, MI // QBLK), idx, topk, 1, H, MI)
+    out = moe_combine(so, dw, topk)
+    return {"xq": xq, "xs": xs, "gu": gu, "hid": hid, "xq_h": xq_h, "xs_h": xs_h, "so": so, "out": out}
 
 
 def gemv_b200_order(xq, xs, Wq, sw):

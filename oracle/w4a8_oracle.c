@@ -417,3 +417,21 @@ API void oracle_moe_w4a8(const int8_t *xq, const float *xs, const uint8_t *Wq, c
         Y[sn] = acc;
     }
 }
+
+/* Combine of the routed-expert block: out[b][o] = sum over k ascending, from 0, of dw[b*topk+k] * so[b*topk+k][o],
+ * the product rounded to fp32 before it is added: the values of kernels/moe_fused.cuh:64 (Sout = dw * acc) summed in
+ * the fixed order of kernels/moe_fused.cuh:68-76.  Built with -ffp-contract=off, so no fused multiply-add. */
+API void oracle_moe_combine(const float *so, const float *dw, float *out, int S, int topk, int H) {
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < (long)S * H; i++) {
+        long b = i / H;
+        int o = (int)(i % H);
+        float acc = 0.0f;
+        for (int k = 0; k < topk; k++) {
+            long slot = b * topk + k;
+            float t = dw[slot] * so[slot * H + o];
+            acc = acc + t;
+        }
+        out[i] = acc;
+    }
+}

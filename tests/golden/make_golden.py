@@ -16,12 +16,14 @@ from pathlib import Path
 
 import numpy as np
 
-ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+here = os.path.dirname(os.path.abspath(__file__))
+# the reference checkout: first argument, else W4A8_REFERENCE_DIR, else a directory "reference" beside this repository
+ref = sys.argv[1] if len(sys.argv) > 1 else (os.environ.get("W4A8_REFERENCE_DIR") or
+                                             os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(here))), "reference"))
 sys.path.insert(0, os.path.join(ref, "tools"))
 import extract_weights as ew          # noqa: E402
 import qat_golden_loader as qgl       # noqa: E402
 
-here = os.path.dirname(os.path.abspath(__file__))
 rng = np.random.default_rng(31)
 w = rng.normal(size=(12, 160)).astype(np.float32) * 0.05
 w[0, :32] = 0.0                       # an all-zero block: scale 1e-8, nibbles 8

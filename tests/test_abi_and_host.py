@@ -142,7 +142,9 @@ _SHIM_TU = r'''
 #include "kernels/gemm_mmq_tmpl.cuh"
 #include "kernels/gemm_mmq_raster.cuh"
 #include "kernels/gemm_mmq_ms.cuh"
+#include "kernels/moe_w4a8.cuh"
 #include "runtime/weights_shard.h"
+__global__ void helpers(int *o) { o[0] = w4a8_pk(0x21, 0x43); o[1] = mmq_unpack4v(0x4321u); }   // device helpers other reference files borrow
 // every launcher of the reference's W4A8 path, called with the reference's argument lists and defaults
 void all(const float *X, int8_t *xq, float *xs, int32_t *xsum, const uint8_t *Wq, const void *sw, float *Y, cudaStream_t st) {
     launch_quantize_x_q8(X, xq, xs, xsum, 64, 1);
@@ -162,6 +164,8 @@ void all(const float *X, int8_t *xq, float *xs, int32_t *xsum, const uint8_t *Wq
     launch_gemm_mmq_raster_w4a8(xq, xs, Wq, sw, Y, 128, 8, 64, 0, 1, 1);
     launch_gemm_mmq_ms<128, 128, 64, 2, 4, 3>(xq, xs, Wq, sw, Y, 128, 8, 64);
     launch_gemm_bm16_splitk(xq, xs, Wq, sw, Y, 16, 8, 64);
+    // the W4A8 form of the fused routed-expert path at models/moe_block.cuh:45-52 (tensor names as there)
+    launch_moe_w4a8_block(X, Wq, sw, Wq, sw, (const int *)xsum, X, Y, /*S=*/4, /*H=*/64, /*MI=*/32, /*E=*/8, /*K=*/2, 0);
     QMatShard m = mat_shard("dir", "L0_mlp.gate_proj", 8, 64, 0, 0, 1);
     (void)m;
 }

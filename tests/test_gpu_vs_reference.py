@@ -139,3 +139,32 @@ def test_reference_unit_test_runs_against_the_dropin_library(oracle):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "[test_w4a8] PASS" in r.stdout and "FAIL" not in r.stdout
     assert r.stdout.count("xq_mis=0 xsum_mis=0") == 4
+
+
+@pytest.mark.parametrize("name,verdict", [("gemm_mmq", "[test_gemm_mmq] PASS"), ("gemm_mma", "[test_gemm_mma] PASS"),
+                                          ("mmq_tmpl", "[test_mmq_tmpl] PASS")])
+def test_reference_gemm_tests_run_against_the_dropin_library(oracle, name, verdict):
+    """The reference's own tests/test_gemm_mmq.cu, test_gemm_mma.cu and test_mmq_tmpl.cu, compiled unmodified with this
+    repository's headers standing in for kernels/*.cuh (oracle/Makefile, rule $(REFTESTS)).  Their gates: GEMM against
+    launch_gemv_w4a8 within 1e-5 of the output rms, 30 runs bitwise identical, and the template launcher bitwise equal
+    to launch_gemm_mmq_w4a8_kt (tests/test_gemm_mmq.cu:28-34, tests/test_mmq_tmpl.cu:60-67)."""
+    import os
+    import subprocess
+    exe = os.path.join(os.path.dirname(oracle.__file__), "_ref", "reftest_" + name)
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/reftest_%s not built (needs the reference tree at build time)" % name)
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert verdict in r.stdout and "FAIL" not in r.stdout
+
+
+def test_dropin_device_helpers(oracle):
+    """w4a8_pk and mmq_unpack4v of the drop-in headers (kernels/gemv_w4a8.cuh:16-21, kernels/gemm_mmq.cuh:25-28 in the
+    reference) over all 65536 inputs (oracle/reftest_unpack.cu)."""
+    import os
+    import subprocess
+    exe = os.path.join(os.path.dirname(oracle.__file__), "_ref", "reftest_unpack")
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/reftest_unpack not built")
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "[reftest_unpack] PASS" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
