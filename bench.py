@@ -423,6 +423,47 @@ def run_ours(args):
                                          "ms_per_step_nccl_allgather": ms_g, "int8_tops_whole_job_nccl_allgather": tops(ms_g),
                                          "ms_rank_local_quantize_gemm": ms_gl, "int8_tops_without_allgather": tops(ms_gl)}
         del Yl2
+        # ---- BASELINE configs[4] split over the ranks: 128 experts, 128 / world per GPU, top-8, M = 8 and 512 tokens; every
+        # rank computes the slots routed to its experts, the slots' down outputs are exchanged through the arenas and every
+        # rank combines (w4a8_moe_block_shard).  Timed without a graph: the step's epoch is an argument of the call. ----------
+        if 128 % world == 0:
+            E_, topk_, H_, MI_ = 128, 8, 2048, 768
+            per_ = E_ // world
+            gm = torch.Generator(device=dev); gm.manual_seed(77)                     # same routing and activations on every rank
+            gu_w = torch.randint(0, 256, (per_, 2 * MI_, H_ // 2), dtype=torch.uint8, device=dev, generator=g)
+            gu_s = torch.randn(per_, 2 * MI_, H_ // 32, device=dev, generator=g).abs() * (0.16 / 7.0)
+            dn_w = torch.randint(0, 256, (per_, H_, MI_ // 2), dtype=torch.uint8, device=dev, generator=g)
+            dn_s = torch.randn(per_, H_, MI_ // 32, device=dev, generator=g).abs() * (0.02 / 7.0)
+            shard = {}
+            for tok_ in (8, 512):
+                n2_ = torch.randn(tok_, H_, device=dev, generator=gm)
+                idx_ = torch.stack([torch.randperm(E_, device=dev, generator=gm)[:topk_] for _ in range(tok_)]).reshape(-1).to(torch.int32)
+                dw_ = torch.rand(tok_ * topk_, device=dev, generator=gm)
+                out_ = torch.empty((tok_, H_), dtype=torch.float32, device=dev)
+                lay_ = w.moe_layout_for(tok_, topk_, H_, MI_, per_)
+                ws_ = torch.empty(lay_.bytes, dtype=torch.uint8, device=dev)
+                sstride = (tok_ * topk_ * H_ * 4 + 255) // 256 * 256
+                marena = w.Arena(2 * sstride, rank, world)
+                mh = [None] * world
+                dist.all_gather_object(mh, marena.export_handle())
+                marena.connect_handles(mh)
+                dist.barrier()
+                mep = [0]
+
+                def moe_step(i, st):
+                    mep[0] += 1
+                    w.moe_block_shard(n2_, gu_w, gu_s, dn_w, dn_s, idx_, dw_, out_, tok_, topk_, H_, MI_, rank * per_, per_, ws_, marena,
+                                      (mep[0] % 2) * sstride, mep[0], 0, 0, 5000000, 0, st)
+                nst = 10
+                ms_ms = time_steps(moe_step, nst, 3, graph=False) / nst
+                w.device_status()
+                barrier()
+                marena.close()
+                ops = 2.0 * tok_ * topk_ * (2 * MI_ * H_ + H_ * MI_)
+                shard["m%d" % tok_] = {"us_per_block": ms_ms * 1e3, "experts_per_gpu": per_, "int8_tops_whole_job": ops / (ms_ms * 1e-3) / 1e12,
+                                       "exchange_bytes_per_rank": tok_ * topk_ * H_ * 4 // world * (world - 1)}
+            extra["moe_block_128e_top8_expert_sharded"] = shard
+            del gu_w, gu_s, dn_w, dn_s
     if world == 1:
         # ---- sweep M = 2..16 on the same shape ------------------------------------------------------------
         sweep = {"1": {"us": per_launch_us, "gbps": achieved, "frac_of_measured_hbm": achieved / hbm_peak,
@@ -670,9 +711,10 @@ def run_ours(args):
 
 
 def run_kernel_case(args):
-    """Small single-kernel run for profiler captures: `--kernel-case gemv_m1 | gemv_m8 | gemv_m16 | gemm_m512` launches that
-    kernel `--steps` times (eagerly, no graph) over 3 rotating copies of the K=5120 x N=17408 weights (167 MB, larger
-    than L2, well under 1 GB on the device) and prints its CUDA-event time.  Not a bench line."""
+    """Small single-kernel run for profiler captures: `--kernel-case gemv_m1 | gemv_m8 | gemv_m16 | gemm_m512 | quantize_m2048 |
+    moe_m512 | moe_m8` launches that kernel (moe: the routed-expert block of BASELINE configs[4], all of its kernels)
+    `--steps` times (eagerly, no graph) over 3 rotating copies of the K=5120 x N=17408 weights (167 MB, larger than L2,
+    well under 1 GB on the device; moe: one 378 MB set of 128 experts) and prints its CUDA-event time.  Not a bench line."""
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device")
@@ -696,9 +738,25 @@ def run_kernel_case(args):
     Y = torch.empty((M, N), dtype=torch.float32, device=dev)
     s = torch.cuda.Stream()
     steps = max(1, min(args.steps, 20))
+    if kind == "moe":
+        del Wqs, sws
+        E, topk, H_, MI_ = 128, 8, 2048, 768
+        gu_w = torch.randint(0, 256, (E, 2 * MI_, H_ // 2), dtype=torch.uint8, device=dev, generator=g)
+        gu_s = torch.randn(E, 2 * MI_, H_ // 32, device=dev, generator=g).abs() * (0.16 / 7.0)
+        dn_w = torch.randint(0, 256, (E, H_, MI_ // 2), dtype=torch.uint8, device=dev, generator=g)
+        dn_s = torch.randn(E, H_, MI_ // 32, device=dev, generator=g).abs() * (0.02 / 7.0)
+        n2 = torch.randn(M, H_, device=dev, generator=g)
+        idx = torch.stack([torch.randperm(E, device=dev, generator=g)[:topk] for _ in range(M)]).reshape(-1).to(torch.int32)
+        dw = torch.rand(M * topk, device=dev, generator=g)
+        out = torch.empty((M, H_), dtype=torch.float32, device=dev)
+        ws = torch.empty(w.moe_layout_for(M, topk, H_, MI_, E).bytes, dtype=torch.uint8, device=dev)
 
     def launch(i):
-        if kind == "gemv":
+        if kind == "moe":
+            w.moe_block(n2, gu_w, gu_s, dn_w, dn_s, idx, dw, out, M, topk, H_, MI_, E, ws, 0, 0, s.cuda_stream)
+        elif kind == "quantize":
+            w.launch_quantize_x_q8(X, xq, xs, xsum, K, M, s.cuda_stream)
+        elif kind == "gemv":
             w.launch_gemv_w4a8_sb(xq, xs, Wqs[i % 3], sws[i % 3], Y, K, N, M, 0, s.cuda_stream)
         elif kind == "gemm":
             w.launch_gemm_mmq_w4a8(xq, xs, Wqs[i % 3], sws[i % 3], Y, M, N, K, 0, s.cuda_stream)

@@ -58,3 +58,39 @@ class NShardedLinear:
 
     def __call__(self, X):
         return all_gather_columns(self.compute(X, self.row0, self.rows), self.plan, self.group)
+
+
+def expert_range(num_experts, rank, world):
+    """Experts [base, base + count) of rank `rank`: equal contiguous blocks (num_experts must divide by world), the
+    split w4a8_moe_block_shard expects (expert e's tensors start e - base experts into the rank's flat tensors)."""
+    if num_experts % world != 0:
+        raise ValueError("num_experts=%d is not a multiple of world=%d" % (num_experts, world))
+    count = num_experts // world
+    return rank * count, count
+
+
+class ExpertShardedBlock:
+    """Plain (collective) form of the expert-sharded routed-expert block, for comparison with the fused peer-store
+    exchange of w4a8_moe_block_shard and for the CPU tests of the partition.
+
+    `compute(n2, idx, base, count) -> so[nslots, H]` is the rank-local part: the down outputs of the slots whose expert
+    lies in [base, base + count), zeros in every other row (on a GPU: the library's block on the rank's experts; the CPU
+    tests inject the oracle).  Every row has exactly one owner, so an all-reduce(sum) of the zero-padded buffers IS the
+    gather of the rows (x + 0 = x exactly); the combine then runs on every rank in the reference's fixed order
+    (kernels/moe_fused.cuh:64,68-76): out[b] = sum over k ascending of dw[b,k] * so[b,k], each product rounded once."""
+
+    def __init__(self, num_experts, topk, rank, world, compute, group=None):
+        self.topk, self.group, self.compute = topk, group, compute
+        self.base, self.count = expert_range(num_experts, rank, world)
+
+    def __call__(self, n2, idx, dw):
+        so = self.compute(n2, idx, self.base, self.count)
+        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            dist.all_reduce(so, op=dist.ReduceOp.SUM, group=self.group)
+        S, H = n2.shape[0], so.shape[1]
+        so = so.view(S, self.topk, H)
+        w = dw.view(S, self.topk, 1).to(so.dtype)
+        out = torch.zeros((S, H), dtype=so.dtype, device=so.device)
+        for k in range(self.topk):
+            out = out + w[:, k] * so[:, k]
+        return out

@@ -55,6 +55,33 @@ def test_argument_validation_before_any_device_work(w4a8):
     assert lib.w4a8_moe_gemv(p, p, p, p, None, p, 4, 2, 0, 8, 64, 4, 0, None) == w4a8.ERR_ARG
     assert lib.w4a8_gemm_splitk_workspace_bytes(16, 256, 1024, 4) == 4 * 16 * 256 * 4
     assert lib.w4a8_gemm_splitk_workspace_bytes(16, 17408, 5120, 0) == 0                           # 136 tiles: no split
+    assert lib.w4a8_gemm_splitk_workspace_bytes(16, 256, 1024, 2 ** 31 - 1) == 0                   # absurd split count
+    assert lib.w4a8_gemm_splitk(p, p, p, p, p, 16, 256, 1024, 0, 2 ** 31 - 1, p, 1 << 20, None) == w4a8.ERR_ARG
+    assert lib.w4a8_gemm_splitk_static(p, p, p, p, p, 16, 256, 1024, 0, 2 ** 31 - 1, None) == w4a8.ERR_ARG
+    # routed-expert block: shapes and workspace are checked before any device work
+    z = ctypes.c_size_t(1 << 30)
+    assert lib.w4a8_moe_block(p, p, p, p, p, p, p, p, 4, 2, 48, 32, 4, 0, 0, p, z, None) == w4a8.ERR_ARG      # H % 32
+    assert lib.w4a8_moe_block(p, p, p, p, p, p, p, p, 4, 2, 64, 32, 4, 0, 3, p, z, None) == w4a8.ERR_ARG      # activation
+    assert lib.w4a8_moe_block(p, p, p, p, p, p, p, p, 4, 2, 64, 32, 4000, 0, 0, p, z, None) == w4a8.ERR_ARG   # experts > 1024
+    assert lib.w4a8_moe_block(p, p, p, p, p, None, p, p, 4, 2, 64, 32, 4, 0, 0, p, z, None) == w4a8.ERR_ARG   # no routing indices
+    assert lib.w4a8_moe_block(p, p, p, p, p, p, p, p, 4, 2, 64, 32, 4, 0, 0, p, ctypes.c_size_t(64), None) == w4a8.ERR_ARG
+    assert b"workspace" in lib.w4a8_last_error()
+    assert lib.w4a8_moe_block(p, p, p, p, p, p, p, p, 0, 2, 64, 32, 4, 0, 0, p, z, None) == w4a8.OK           # no tokens
+
+
+def test_moe_layout_is_disjoint_and_aligned(w4a8):
+    S, topk, H, MI, E = 512, 8, 2048, 768, 128
+    lay = w4a8.moe_layout_for(S, topk, H, MI, E)
+    n = S * topk
+    sizes = {"perm": n * 4, "pos": n * 4, "offsets": (E + 1) * 4, "items": (E + n // 128 + 1) * 16, "num_items": 4, "xq": S * H,
+             "xs": S * (H // 32) * 4, "xq_g": n * H, "xs_g": n * (H // 32) * 4, "gu": n * 2 * MI * 4, "xq_h": n * MI, "xs_h": n * (MI // 32) * 4,
+             "sout": n * H * 4}
+    spans = sorted((getattr(lay, k), getattr(lay, k) + v) for k, v in sizes.items())
+    assert all(a % 256 == 0 for a, _ in spans)
+    assert all(spans[i][1] <= spans[i + 1][0] for i in range(len(spans) - 1))
+    assert spans[-1][1] <= lay.bytes
+    with pytest.raises(w4a8.W4A8Error):
+        w4a8.moe_layout_for(4, 2, 64, 32, 5000)
 
 
 def test_no_cpu_fallback_without_a_device(w4a8):
@@ -115,6 +142,26 @@ for (M, N, K) in [(1, 64, 128), (5, 64, 128), (3, 37, 96)]:
     xq, xs, _ = O.quantize_x_q8(X)
     full = O.gemm_mmq_w4a8(xq, xs, Wq, sw)
     assert Y.shape == (M, N) and np.array_equal(Y.numpy().view(np.uint32), full.view(np.uint32)), (M, N, K, rank)
+# expert shards: each rank computes the down outputs of the slots routed to its experts, the rows are exchanged, every
+# rank combines in the fixed order; equal, bit for bit, to the whole block on one rank
+S, topk, E, H, MI = 6, 2, 4, 64, 32
+rng = np.random.default_rng(11)
+n2 = O.make_activations(S, H, seed=3)
+gu_wq, gu_sc = O.make_weights(E * 2 * MI, H, seed=4); dn_wq, dn_sc = O.make_weights(E * H, MI, seed=5)
+gu_wq, gu_sc = gu_wq.reshape(E, 2 * MI, -1), (gu_sc * 8).reshape(E, 2 * MI, -1)
+dn_wq, dn_sc = dn_wq.reshape(E, H, -1), dn_sc.reshape(E, H, -1)
+idx = np.stack([rng.permutation(E)[:topk] for _ in range(S)]).astype(np.int32).reshape(-1)
+dw = rng.random(S * topk).astype(np.float32)
+whole = O.moe_block_w4a8(n2, gu_wq, gu_sc, dn_wq, dn_sc, idx, dw, topk)
+def compute(n2t, idxt, base, count):
+    so = whole["so"].copy()                                   # a slot's row depends only on its own expert ...
+    mine = (idxt.numpy() >= base) & (idxt.numpy() < base + count)
+    so[~mine] = 0.0                                           # ... and a rank produces only its experts' slots
+    return torch.from_numpy(so)
+blk = sharded.ExpertShardedBlock(E, topk, rank, world, compute)
+out = blk(torch.from_numpy(n2), torch.from_numpy(idx), torch.from_numpy(dw))
+assert np.array_equal(out.numpy().view(np.uint32), whole["out"].view(np.uint32)), rank
+assert sharded.expert_range(E, rank, world) == (rank * (E // world), E // world)
 dist.destroy_process_group()
 print("rank", rank, "ok")
 '''

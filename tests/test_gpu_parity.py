@@ -319,7 +319,7 @@ def test_config3_gemma_layer_shapes_m8(w4a8, oracle, cuda, K, N):
     assert np.array_equal(Y.cpu().numpy().view(np.uint32), gemv_expected(oracle, xq, xs, Wq, sw).view(np.uint32))
 
 
-@pytest.mark.parametrize("M", [1, 16])
+@pytest.mark.parametrize("M", [1, 2, 4, 8, 16])
 def test_config2_decode_sweep_full_shape(w4a8, oracle, cuda, M):
     K, N = 5120, 17408
     xq, xs, Wq, sw = make_case(oracle, M, N, K, seed=20260002 + M)
@@ -331,11 +331,13 @@ def test_config2_decode_sweep_full_shape(w4a8, oracle, cuda, M):
     assert rel_err(y, oracle.w4a8_f64(xq, xs, Wq, sw)) < REL_TOL
 
 
-def test_config4_prefill_gemm_full_shape_sampled_rows(w4a8, oracle, cuda):
-    """M=2048, K=5120, N=17408 with 1 % outliers x20, quantize_x on the device.  The oracle cannot do the whole product
-    in seconds, so: xq/xs/xsum of all rows exact; a sample of output rows bit-exact (rows are independent of M in the
-    reference, tools/probe_mmq_rowdep.cu, so a row equals the M=1 product of that row); a second run bitwise equal."""
-    M, K, N = 2048, 5120, 17408
+@pytest.mark.parametrize("M", [512, 2048, 8192])
+def test_config4_prefill_gemm_full_shape_sampled_rows(w4a8, oracle, cuda, M):
+    """M = 512, 2048, 8192 (the reference bench's sizes, tools/bench_mmq_tune.cu:30), K=5120, N=17408 with 1 % outliers
+    x20, quantize_x on the device.  The oracle cannot do the whole product in seconds, so: xq/xs/xsum of all rows exact;
+    a sample of output rows bit-exact (rows are independent of M in the reference, tools/probe_mmq_rowdep.cu, so a row
+    equals the M=1 product of that row); a second run bitwise equal."""
+    K, N = 5120, 17408
     X = oracle.make_activations(M, K, seed=20260004, outliers=True)
     Wq, sw = oracle.make_weights(N, K, seed=20260005)
     xq_o, xs_o, xsum_o = oracle.quantize_x_q8(X)
@@ -346,7 +348,7 @@ def test_config4_prefill_gemm_full_shape_sampled_rows(w4a8, oracle, cuda):
     Y = torch.empty((M, N), dtype=torch.float32, device=cuda)
     w4a8.launch_gemm_mmq_w4a8(xq, xs, Wq_d, sw_d, Y, M, N, K)
     w4a8.device_status()
-    rows = np.array([0, 1, 127, 128, 777, 1023, 1024, 2046, 2047])
+    rows = np.unique(np.array([0, 1, 127, 128, 777 % M, M // 2 - 1, M // 2, M - 2, M - 1]))
     ref = oracle.gemm_mmq_w4a8(xq_o[rows], xs_o[rows], Wq, sw)
     assert np.array_equal(Y[torch.from_numpy(rows).to(cuda)].cpu().numpy().view(np.uint32), ref.view(np.uint32))
     Y2 = torch.empty((M, N), dtype=torch.float32, device=cuda)
