@@ -591,7 +591,24 @@ def run_ours(args):
             us_b = ms_b * 1e3 / nst
             touched = int(torch.unique(idx_).numel())
             ops = 2.0 * tok_ * topk * (2 * MI_ * H_ + H_ * MI_)
-            blk["m%d" % tok_] = {"us": us_b, "experts_touched": touched, "weight_bytes": touched * per_expert,
+            refp_ = os.path.join(ROOT, "oracle", "_ref", "libref_kernels.so")
+            us_ref = None
+            if os.path.exists(refp_):       # the reference's own fused expert path (W4A32 arithmetic: the nearest reference code)
+                rk = ctypes.CDLL(refp_)
+                if hasattr(rk, "ref_moe_fused_block"):
+                    P_ = lambda t: ctypes.c_void_p(t.data_ptr())
+                    nsl = tok_ * topk
+                    fgu = torch.empty((nsl, 2 * MI_), dtype=torch.float32, device=dev)
+                    fhid = torch.empty((nsl, MI_), dtype=torch.float32, device=dev)
+                    fso = torch.empty((nsl, H_), dtype=torch.float32, device=dev)
+                    nr = 10 if tok_ <= 64 else 2
+                    ms_r = time_steps(lambda i, st: rk.ref_moe_fused_block(P_(n2_), P_(gu_w[i % 2]), P_(gu_s[i % 2]), P_(dn_w[i % 2]), P_(dn_s[i % 2]),
+                                                                           P_(idx_), P_(dw_), P_(fgu), P_(fhid), P_(fso), P_(out_), tok_, H_, MI_, topk,
+                                                                           0, ctypes.c_void_p(st)), nr, 3, graph=True, min_ms=5.0)
+                    us_ref = ms_r * 1e3 / nr
+                    del fgu, fhid, fso
+            blk["m%d" % tok_] = {"us": us_b, "reference_w4a32_fused_path_sm100a_us": us_ref,
+                                 "experts_touched": touched, "weight_bytes": touched * per_expert,
                                  "gbps_weights": touched * per_expert / (us_b * 1e-6) / 1e9, "int8_tops": ops / (us_b * 1e-6) / 1e12,
                                  "kernel": "grouped GEMV per slot" if tok_ * topk <= 128 else "sorted grouped tcgen05 GEMM"}
         extra["moe_block_128e_top8"] = blk
@@ -688,7 +705,7 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "i8", "data": "synthetic",
             "config": {"workload": WORKLOAD,
-                       "parallelism": ("n-shard x%d, all-gather fused into the GEMV (last CTA pushes the slice to every peer over NVLink, flags, in-kernel wait)" % world)
+                       "parallelism": ("n-shard x%d, all-gather fused into the GEMV (every output also goes to every peer as an 8-byte {value, epoch tag} store over NVLink; the same launch polls the peers' slots)" % world)
                        if world > 1 else "single GPU",
                        "l2": "rotating %d distinct weight copies per rank (%.0f MB > 126 MB L2)" % (nbuf, nbuf * shard_bytes / 1e6),
                        "launch": "CUDA graph of %d steps, replayed %d times (>= %.0f ms timed); value from the median replay, min in `timing`"

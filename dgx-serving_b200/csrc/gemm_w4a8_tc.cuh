@@ -34,9 +34,16 @@ namespace w4a8 {
 namespace gemm {
 
 constexpr int BM = 128, BN = 128, KT = 128;
+static_assert(BM == BN, "the grouped (transposed) instantiation exchanges the operands' roles");
 constexpr int GPK = KT / QBLK;  // groups (MMAs) per K-tile = 4
-constexpr int SA = 4;           // activation stages
-constexpr int SB = 4;           // packed-weight stages
+#ifndef W4A8_GEMM_SA
+#define W4A8_GEMM_SA 4
+#endif
+#ifndef W4A8_GEMM_SB
+#define W4A8_GEMM_SB 4
+#endif
+constexpr int SA = W4A8_GEMM_SA;  // activation stages
+constexpr int SB = W4A8_GEMM_SB;  // packed-weight stages
 constexpr int S8 = 3;           // expanded-weight stages
 constexpr int SS = 4;           // weight-scale stages
 constexpr int TB = 4;           // TMEM accumulator buffers (TB * BN = 512 columns = all of tensor memory)
@@ -63,7 +70,8 @@ constexpr int OFF_B8 = OFF_A + SA * A_STAGE;
 constexpr int OFF_BP = OFF_B8 + S8 * B8_STAGE;
 constexpr int OFF_SW = OFF_BP + SB * BP_STAGE;
 constexpr int OFF_BAR = OFF_SW + SS * SW_STAGE;
-constexpr int NUM_BARS = 2 * (SA + SB + S8 + SS + TB);
+constexpr int KD = 12;           // K-tile-done ring (GROUPED): a multiple of SA and S8, deeper than any role can lag
+constexpr int NUM_BARS = 2 * (SA + SB + S8 + SS + TB) + KD;
 constexpr int OFF_TMEM = OFF_BAR + NUM_BARS * 8;
 constexpr int SMEM_BYTES = OFF_TMEM + 16 + 1024;  // + slack to align the base to 1024 B
 
@@ -143,6 +151,28 @@ __device__ __forceinline__ void epi_chunk(const uint32_t (&d)[NC], float x, cons
             acc[j + 1] = fmaf(t1, s4.y, acc[j + 1]);
             acc[j + 2] = fmaf(t2, s4.z, acc[j + 2]);
             acc[j + 3] = fmaf(t3, s4.w, acc[j + 3]);
+        }
+    }
+}
+// The same arithmetic with the roles of the two scales exchanged (grouped experts: lane = weight row, column = token):
+// xs[j] belongs to column j, sw16 to the lane.  t = (float)d * xs (rounded), acc = fma(t, sw16, acc): the same operations
+// on the same values as epi_chunk, so the same bits.
+template <int NC>
+__device__ __forceinline__ void epi_chunk_t(const uint32_t (&d)[NC], const float *__restrict__ xs, float sw16, float *__restrict__ acc) {
+    const uint64_t ss = pack_f32x2(sw16, sw16);
+#pragma unroll
+    for (int j4 = 0; j4 < NC / 4; j4++) {
+        const float4 x4 = *reinterpret_cast<const float4 *>(xs + j4 * 4);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int j = j4 * 4 + 2 * h;
+            const uint64_t f2 = pack_f32x2(__int2float_rn((int)d[j]), __int2float_rn((int)d[j + 1]));
+            const uint64_t x2 = h == 0 ? pack_f32x2(x4.x, x4.y) : pack_f32x2(x4.z, x4.w);
+            uint64_t a2 = pack_f32x2(acc[j], acc[j + 1]);
+            uint64_t t2;
+            asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(t2) : "l"(f2), "l"(x2));
+            asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(a2) : "l"(t2), "l"(ss));
+            unpack_f32x2(a2, acc[j], acc[j + 1]);
         }
     }
 }
@@ -232,7 +262,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
     // barrier index map
     constexpr int A_FULL = 0, A_EMPTY = A_FULL + SA, BP_FULL = A_EMPTY + SA, BP_EMPTY = BP_FULL + SB,
                   B8_FULL = BP_EMPTY + SB, B8_EMPTY = B8_FULL + S8, SW_FULL = B8_EMPTY + S8, SW_EMPTY = SW_FULL + SS,
-                  TM_FULL = SW_EMPTY + SS, TM_EMPTY = TM_FULL + TB;
+                  TM_FULL = SW_EMPTY + SS, TM_EMPTY = TM_FULL + TB, KT_DONE = TM_EMPTY + TB;
+    // GROUPED: ONE tcgen05.commit per K-tile instead of six (accumulator ready x 4, activation stage free, operand stage
+    // free).  K-tile j of the CTA (counted across work units, the same in every role) commits to KT_DONE[j % KD]; whoever
+    // needs "the MMAs of K-tile j have completed" waits for parity (j / KD) & 1 — the epilogue for its accumulators, the
+    // producer and the expansion warps for the stages K-tile j read.  The epilogue then fetches all of a K-tile's live
+    // columns in one go and hands the four accumulator buffers back together (MoE block at M = 512: 555 -> 530 us).
+    constexpr bool KT_COMMIT = GROUPED;
+    auto kt_done_wait = [&](int j) { return ptx::mbar_wait(BAR(KT_DONE + j % KD), (uint32_t)(j / KD) & 1u); };
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + OFF_TMEM);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -248,6 +285,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
         for (int i = 0; i < S8; i++) { ptx::mbar_init(BAR(B8_FULL + i), DEQ_WARPS); ptx::mbar_init(BAR(B8_EMPTY + i), 1); }
         for (int i = 0; i < SS; i++) { ptx::mbar_init(BAR(SW_FULL + i), DEQ_WARPS); ptx::mbar_init(BAR(SW_EMPTY + i), EPI_WARPS); }
         for (int i = 0; i < TB; i++) { ptx::mbar_init(BAR(TM_FULL + i), 1); ptx::mbar_init(BAR(TM_EMPTY + i), EPI_WARPS); }
+        for (int i = 0; i < KD; i++) ptx::mbar_init(BAR(KT_DONE + i), 1);
         ptx::mbar_fence_init();
         ptx::tma_prefetch_desc(&tmA);
         ptx::tma_prefetch_desc(&tmB);
@@ -266,12 +304,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
         if (lane == 0) {
             Ring ra(SA), rb(SB);
             bool ok = true;
+            int kc = 0;
             for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
                 const Work wk = decode_work<GROUPED>(wi, m_tiles, num_tiles, nb, gsplit, M, N, n_tiles, gl);
                 const int m0 = wk.m0, n0 = wk.n0;
-                for (int kt = 0; kt < wk.nkt && ok; kt++) {
+                for (int kt = 0; kt < wk.nkt && ok; kt++, kc++) {
                     const int kbyte = (wk.g0 + kt * GPK) * QBLK;   // first K element of this K-tile (multiple of 32)
-                    if (!ptx::mbar_wait(BAR(A_EMPTY + ra.stage), ra.phase ^ 1u)) { dev_set_error(ERR_PRODUCER | 1); ok = false; break; }
+                    if (KT_COMMIT ? (kc >= SA && !kt_done_wait(kc - SA)) : !ptx::mbar_wait(BAR(A_EMPTY + ra.stage), ra.phase ^ 1u)) { dev_set_error(ERR_PRODUCER | 1); ok = false; break; }
                     ptx::mbar_arrive_expect_tx(BAR(A_FULL + ra.stage), A_STAGE);
                     ptx::tma_load_2d(base + OFF_A + ra.stage * A_STAGE, &tmA, kbyte, m0, BAR(A_FULL + ra.stage));
                     ra.advance();
@@ -292,15 +331,37 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
             Ring ra(SA), r8(S8), rt(TB);
             const uint32_t idesc = ptx::umma_idesc_s8(BM, BN);
             bool ok = true;
+            int kc = 0;
             for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
                 const Work wk = decode_work<GROUPED>(wi, m_tiles, num_tiles, nb, gsplit, M, N, n_tiles, gl);
-                for (int kt = 0; kt < wk.nkt && ok; kt++) {
+                for (int kt = 0; kt < wk.nkt && ok; kt++, kc++) {
                     if (!ptx::mbar_wait(BAR(A_FULL + ra.stage), ra.phase)) { dev_set_error(ERR_MMA | 1); ok = false; break; }
                     if (!ptx::mbar_wait(BAR(B8_FULL + r8.stage), r8.phase)) { dev_set_error(ERR_MMA | 2); ok = false; break; }
                     ptx::tc_fence_after_sync();
                     const uint64_t adesc = ptx::umma_desc_k_sw128(base + OFF_A + ra.stage * A_STAGE);
                     const uint64_t bdesc = ptx::umma_desc_k_sw128(base + OFF_B8 + r8.stage * B8_STAGE);
                     const int ng = min(GPK, wk.g1 - (wk.g0 + kt * GPK));
+                    if (KT_COMMIT) {
+                        // all of the K-tile's accumulator buffers free, its MMAs back to back, one commit
+                        int st = rt.stage; uint32_t ph = rt.phase;
+                        for (int g = 0; g < ng && ok; g++) {
+                            if (!ptx::mbar_wait(BAR(TM_EMPTY + st), ph ^ 1u)) { dev_set_error(ERR_MMA | 3); ok = false; }
+                            if (++st == TB) { st = 0; ph ^= 1u; }
+                        }
+                        if (!ok) break;
+                        ptx::tc_fence_after_sync();
+                        for (int g = 0; g < ng; g++) {
+                            // the expanded weights are the MMA's A operand (accumulator lanes = weight rows), the activations
+                            // its B operand (columns = tokens): an expert's tile has few live tokens, and the epilogue's work
+                            // follows the live COLUMNS while all 128 lanes stay busy
+                            ptx::umma_i8(tmem_base + rt.stage * BN, bdesc + (uint64_t)(g * 2), adesc + (uint64_t)(g * 2), idesc, 0u);
+                            rt.advance();
+                        }
+                        ptx::umma_commit(BAR(KT_DONE + kc % KD));
+                        ra.advance();
+                        r8.advance();
+                        continue;
+                    }
                     for (int g = 0; g < ng; g++) {
                         if (!ptx::mbar_wait(BAR(TM_EMPTY + rt.stage), rt.phase ^ 1u)) { dev_set_error(ERR_MMA | 3); ok = false; break; }
                         ptx::tc_fence_after_sync();
@@ -321,10 +382,26 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
         const int dt = tid - 64;  // 0..DEQ_WARPS*32-1
         Ring rb(SB), r8(S8), rs(SS);
         bool ok = true;
+        int kc = 0;
         for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
             const Work wk = decode_work<GROUPED>(wi, m_tiles, num_tiles, nb, gsplit, M, N, n_tiles, gl);
             const int n0 = wk.n0;
-            for (int kt = 0; kt < wk.nkt && ok; kt++) {
+            if (GROUPED && dt == 0 && scales_aligned) {
+                // An expert's scales are touched by this CTA only, so every K-tile's scale loads would wait for HBM (with
+                // dense weights another CTA has usually brought them into L2).  The scale rows of a unit are one contiguous
+                // block each: ask for the NEXT unit's blocks now (and for this CTA's first unit at its start).
+                auto prefetch_unit = [&](const Work &u) {
+                    const int nrows = min(BN, N - u.n0), mrows = u.mend - u.m0;
+                    const uint32_t wbytes = (uint32_t)((size_t)nrows * nb * sizeof(ST)) & ~15u, xbytes = (uint32_t)((size_t)mrows * nb * 4) & ~15u;
+                    const ST *wp = sw + (size_t)(u.wrow0 + u.n0) * nb;
+                    const float *xp = xs + (size_t)u.m0 * nb;
+                    if (wbytes && (reinterpret_cast<uintptr_t>(wp) & 15) == 0) ptx::prefetch_l2_bulk(wp, wbytes);
+                    if (xbytes && (reinterpret_cast<uintptr_t>(xp) & 15) == 0) ptx::prefetch_l2_bulk(xp, xbytes);
+                };
+                if (wi == (int)blockIdx.x) prefetch_unit(wk);
+                if (wi + (int)gridDim.x < num_work) prefetch_unit(decode_work<GROUPED>(wi + gridDim.x, m_tiles, num_tiles, nb, gsplit, M, N, n_tiles, gl));
+            }
+            for (int kt = 0; kt < wk.nkt && ok; kt++, kc++) {
                 // ---- this K-tile's scales: issue the loads first, they complete behind the expansion below.
                 // A row's GPK scales are contiguous in memory: one 16-byte (fp32) or 8-byte (fp16) load per row
                 // when the K-tile is complete and the addresses line up, else element by element.
@@ -363,7 +440,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
                 }
 
                 // ---- expansion of the packed stage into the operand stage
-                bool w = ptx::mbar_wait_warp(BAR(BP_FULL + rb.stage), rb.phase) && ptx::mbar_wait_warp(BAR(B8_EMPTY + r8.stage), r8.phase ^ 1u);
+                bool w = ptx::mbar_wait_warp(BAR(BP_FULL + rb.stage), rb.phase) && (KT_COMMIT ? (kc < S8 || ptx::mbar_wait_warp(BAR(KT_DONE + (kc - S8) % KD), (uint32_t)((kc - S8) / KD) & 1u))
+                                                                                                   : ptx::mbar_wait_warp(BAR(B8_EMPTY + r8.stage), r8.phase ^ 1u));
                 if (!w) { dev_set_error(ERR_DEQUANT | 1); ok = false; break; }
                 const unsigned char *src = base_ptr + OFF_BP + rb.stage * BP_STAGE;
                 unsigned char *dst = base_ptr + OFF_B8 + r8.stage * B8_STAGE;
@@ -418,7 +496,94 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
         const int col0 = (ew >> 2) * EPI_COLS;  // this warp's accumulator columns [col0, col0 + EPI_COLS)
         Ring rs(SS), rt(TB);
         bool ok = true;
-        for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
+        if (GROUPED) {
+            // Transposed accumulator: lanes are weight rows (all 128 live), columns are the item's tokens (z <= 128 live,
+            // 32 on average).  The 4 warps that share a quad of lanes deal the live columns out in chunks of CW: warp
+            // group cg takes chunks cg, cg + 4, ... so that at z = 32 every one of the 16 warps converts and scales
+            // 8 columns per group instead of 4 warps doing 32 each.  The accumulator buffer is released as soon as the
+            // chunks are in registers.
+            constexpr int CW = 8, CK = BM / (4 * CW);      // 4 chunks of 8 columns per warp at most
+            const int cg = ew >> 2;
+            int kce = 0;                                   // kce: K-tiles of this CTA so far (the index every role counts)
+            for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
+                const Work wk = decode_work<GROUPED>(wi, m_tiles, num_tiles, nb, gsplit, M, N, n_tiles, gl);
+                const int z = wk.mend - wk.m0;
+                const int nlive = z > CW * cg ? (z - CW * cg - 1) / (4 * CW) + 1 : 0;   // chunk k covers columns CW*(cg + 4k) ...
+                const int n = wk.n0 + quad * 32 + lane;
+                float acc[CK][CW];
+#pragma unroll
+                for (int k = 0; k < CK; k++)
+#pragma unroll
+                    for (int j = 0; j < CW; j++) acc[k][j] = 0.f;
+                const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16) + CW * cg;
+                const float *stage = nullptr;
+                const int ngroups = wk.g1 - wk.g0;
+                for (int gi = 0; gi < ngroups; gi += GPK) {             // one K-tile = up to GPK groups = one commit
+                    const int ngk = min(GPK, ngroups - gi);
+                    if (!ptx::mbar_wait_warp(BAR(SW_FULL + rs.stage), rs.phase)) { dev_set_error(ERR_EPILOGUE | 1); ok = false; break; }
+                    stage = reinterpret_cast<const float *>(base_ptr + OFF_SW + rs.stage * SW_STAGE);
+                    if (!ptx::mbar_wait_warp(BAR(KT_DONE + kce % KD), (uint32_t)(kce / KD) & 1u)) { dev_set_error(ERR_EPILOGUE | 2); ok = false; break; }
+                    ptx::tc_fence_after_sync();
+                    kce++;
+                    if (nlive <= 1) {
+                        // at most one chunk of columns per group and warp (z <= 32 tokens): fetch the chunk of EVERY group of the
+                        // K-tile, hand all accumulator buffers back at once, then convert and scale — the MMAs of the next
+                        // K-tile run meanwhile
+                        uint32_t d[GPK][CW];
+                        int st = rt.stage;
+#pragma unroll
+                        for (int g = 0; g < GPK; g++) {
+                            if (g < ngk && nlive) ptx::tmem_ld(tlane + st * BN, d[g]);
+                            if (++st == TB) st = 0;
+                        }
+                        ptx::tmem_ld_wait();
+                        ptx::tc_fence_before_sync();
+                        __syncwarp();
+                        for (int g = 0; g < ngk; g++) {
+                            if (lane == 0) ptx::mbar_arrive(BAR(TM_EMPTY + rt.stage));
+                            rt.advance();
+                        }
+                        if (nlive) {
+#pragma unroll
+                            for (int g = 0; g < GPK; g++)
+                                if (g < ngk) epi_chunk_t<CW>(d[g], stage + GPK * BN + g * BM + CW * cg, stage[g * BN + quad * 32 + lane], acc[0]);
+                        }
+                    } else {
+                        for (int g = 0; g < ngk; g++) {
+                            uint32_t d[CK][CW];
+#pragma unroll
+                            for (int k = 0; k < CK; k++)
+                                if (k < nlive) ptx::tmem_ld(tlane + rt.stage * BN + 4 * CW * k, d[k]);
+                            ptx::tmem_ld_wait();
+                            ptx::tc_fence_before_sync();
+                            __syncwarp();
+                            if (lane == 0) ptx::mbar_arrive(BAR(TM_EMPTY + rt.stage));
+                            rt.advance();
+                            const float swl = stage[g * BN + quad * 32 + lane];                   // this lane's weight scale / 16
+                            const float *xsg = stage + GPK * BN + g * BM + CW * cg;               // the tokens' scales of this group
+#pragma unroll
+                            for (int k = 0; k < CK; k++)
+                                if (k < nlive) epi_chunk_t<CW>(d[k], xsg + 4 * CW * k, swl, acc[k]);
+                            ptx::tc_fence_after_sync();
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(BAR(SW_EMPTY + rs.stage));
+                    rs.advance();
+                }
+                if (!ok) break;
+                if (n < N) {   // consecutive lanes write consecutive floats of a row of Y
+#pragma unroll
+                    for (int k = 0; k < CK; k++)
+#pragma unroll
+                        for (int j = 0; j < CW; j++) {
+                            const int col = CW * (cg + 4 * k) + j;
+                            if (k < nlive && col < z) Y[(size_t)(wk.m0 + col) * N + n] = acc[k][j];
+                        }
+                }
+            }
+        }
+        for (int wi = blockIdx.x; !GROUPED && wi < num_work && ok; wi += gridDim.x) {
             const Work wk = decode_work<GROUPED>(wi, m_tiles, num_tiles, nb, gsplit, M, N, n_tiles, gl);
             const int m0 = wk.m0, n0 = wk.n0;
             const int m = m0 + quad * 32 + lane;

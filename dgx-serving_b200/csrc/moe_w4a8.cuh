@@ -23,7 +23,10 @@ namespace w4a8 {
 namespace moe {
 
 constexpr int MAX_EXPERTS = 1024;
-constexpr int TILE_ROWS = gemm::BM;
+#ifndef W4A8_MOE_TILE_ROWS
+#define W4A8_MOE_TILE_ROWS 128
+#endif
+constexpr int TILE_ROWS = W4A8_MOE_TILE_ROWS;   // rows per item of the grouped GEMM (at most gemm::BM)
 
 // Byte offsets of the block's intermediates inside the caller's workspace (all 256-byte aligned).
 struct Layout {
@@ -60,37 +63,92 @@ inline Layout layout_for(int S, int topk, int H, int MI, int experts) {
     return l;
 }
 
-// One CTA.  Stable counting sort of the slots by local expert id (idx[slot] - expert_base; ids outside
+// One CTA of 1024 threads.  Stable counting sort of the slots by local expert id (idx[slot] - expert_base; ids outside
 // [0, experts) belong to another rank or are invalid and get pos = -1), and the item list of the grouped GEMM.
+//   1. every warp owns a contiguous segment of the slots and counts its experts (per-warp histogram rows in shared
+//      memory when experts <= FAST_EXPERTS, else one shared histogram);
+//   2. warp 0 scans the expert totals 32 at a time (offsets, number of 128-row tiles) and writes the item list;
+//   3. thread e turns column e of the per-warp histograms into the warps' first positions for expert e;
+//   4. every warp walks its segment 32 slots at a time: a slot's position = its warp's running position for the
+//      expert + its rank among the equal ids of the 32 (match_any), so an expert's rows keep the slots' order.
+// More than FAST_EXPERTS experts: step 4 is done expert by expert (a warp takes an expert and walks all slots).
 __global__ void __launch_bounds__(1024) moe_sort_kernel(const int32_t *__restrict__ idx, int nslots, int expert_base, int experts,
                                                         int *__restrict__ perm, int *__restrict__ pos, int *__restrict__ offsets,
                                                         int4 *__restrict__ items, int *__restrict__ num_items) {
+    constexpr int FAST_EXPERTS = 256, NW = 32;
     __shared__ int cnt[MAX_EXPERTS];
     __shared__ int off[MAX_EXPERTS + 1];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    __shared__ int wpos[NW][FAST_EXPERTS];     // fast path: per-warp counts, then per-warp running positions
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool fast = experts <= FAST_EXPERTS;
+    const int seg = ((nslots + NW - 1) / NW + 31) & ~31;             // slots per warp, a multiple of 32
+    const int s_begin = warp * seg, s_end = min(nslots, s_begin + seg);
     for (int e = tid; e < experts; e += blockDim.x) cnt[e] = 0;
+    if (fast)
+        for (int i = tid; i < NW * FAST_EXPERTS; i += blockDim.x) (&wpos[0][0])[i] = 0;
     __syncthreads();
-    for (int s = tid; s < nslots; s += blockDim.x) {
+    for (int s = s_begin + lane; s < s_end; s += 32) {
         const int e = idx[s] - expert_base;
-        if (e >= 0 && e < experts) atomicAdd(&cnt[e], 1);
-        else pos[s] = -1;
-    }
-    __syncthreads();
-    if (tid == 0) {
-        int run = 0, n = 0;
-        for (int e = 0; e < experts; e++) {
-            off[e] = run;
-            offsets[e] = run;
-            for (int t = 0; t < cnt[e]; t += TILE_ROWS) items[n++] = make_int4(e, run + t, min(TILE_ROWS, cnt[e] - t), 0);
-            run += cnt[e];
+        if (e >= 0 && e < experts) {
+            atomicAdd(&cnt[e], 1);
+            if (fast) atomicAdd(&wpos[warp][e], 1);
+        } else {
+            pos[s] = -1;
         }
-        off[experts] = run;
-        offsets[experts] = run;
-        *num_items = n;
     }
     __syncthreads();
-    // placement: a warp takes an expert and walks the slots 32 at a time, so an expert's rows keep the slots' order
-    for (int e = warp; e < experts; e += nwarps) {
+    if (warp == 0) {
+        int run = 0, n = 0;
+        for (int e0 = 0; e0 < experts; e0 += 32) {
+            const int e = e0 + lane;
+            const int c = e < experts ? cnt[e] : 0;
+            const int t = (c + TILE_ROWS - 1) / TILE_ROWS;
+            int ic = c, it = t;                                        // inclusive scans over the 32 experts
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int uc = __shfl_up_sync(0xffffffffu, ic, d), ut = __shfl_up_sync(0xffffffffu, it, d);
+                if (lane >= d) { ic += uc; it += ut; }
+            }
+            const int first = run + ic - c, item0 = n + it - t;
+            if (e < experts) {
+                off[e] = first;
+                offsets[e] = first;
+                for (int k = 0; k < t; k++) items[item0 + k] = make_int4(e, first + k * TILE_ROWS, min(TILE_ROWS, c - k * TILE_ROWS), 0);
+            }
+            run += __shfl_sync(0xffffffffu, ic, 31);
+            n += __shfl_sync(0xffffffffu, it, 31);
+        }
+        if (lane == 0) {
+            off[experts] = run;
+            offsets[experts] = run;
+            *num_items = n;
+        }
+    }
+    __syncthreads();
+    if (fast) {
+        for (int e = tid; e < experts; e += blockDim.x) {               // counts -> first positions, warps in order
+            int p = off[e];
+            for (int w = 0; w < NW; w++) { const int c = wpos[w][e]; wpos[w][e] = p; p += c; }
+        }
+        __syncthreads();
+        for (int s0 = s_begin; s0 < s_end; s0 += 32) {                  // uniform per warp
+            const int s = s0 + lane;
+            int e = s < s_end ? idx[s] - expert_base : -1;
+            if (e < 0 || e >= experts) e = -1;
+            const unsigned same = __match_any_sync(0xffffffffu, e);
+            if (e >= 0) {
+                const int p = wpos[warp][e] + __popc(same & ((1u << lane) - 1u));
+                perm[p] = s;
+                pos[s] = p;
+            }
+            __syncwarp();
+            if (e >= 0 && lane == 31 - __clz(same)) wpos[warp][e] += __popc(same);   // the last of the equal ids moves the position on
+            __syncwarp();
+        }
+        return;
+    }
+    // many experts: a warp takes an expert and walks all slots 32 at a time
+    for (int e = warp; e < experts; e += NW) {
         if (cnt[e] == 0) continue;
         int placed = 0;
         for (int s0 = 0; s0 < nslots; s0 += 32) {

@@ -84,6 +84,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void *tmap,
 __device__ __forceinline__ void tma_prefetch_desc(const void *tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
+// Brings `bytes` (a multiple of 16) of global memory starting at a 16-byte aligned address into L2; nothing waits for it.
+__device__ __forceinline__ void prefetch_l2_bulk(const void *gptr, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gptr), "r"(bytes) : "memory");
+}
 
 // ---- tensor memory ------------------------------------------------------------------------------
 // Whole-warp calls (.sync.aligned).  ncols: power of two in [32, 512].

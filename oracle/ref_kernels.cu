@@ -14,6 +14,7 @@
 #include "kernels/gemm_mmq.cuh"
 #include "kernels/gemm_mmq_tmpl.cuh"
 #include "kernels/gemm_mmq_raster.cuh"
+#include "kernels/moe_fused.cuh"
 
 #define REF_API extern "C" __attribute__((visibility("default")))
 static inline int ref_status() { return (int)cudaPeekAtLastError(); }
@@ -68,5 +69,20 @@ REF_API int ref_rmsnorm(const float *X, const float *W, float *Y, int rows, int 
 REF_API int ref_glu(const float *g, const float *u, float *Y, long n, int act, void *st) {
     if (act == 0) launch_swiglu(g, u, Y, (size_t)n, (cudaStream_t)st);
     else launch_geglu(g, u, Y, (size_t)n, (cudaStream_t)st);
+    return ref_status();
+}
+
+// The reference's device-fused routed-expert path exactly as models/moe_block.cuh:45-52 enqueues it (W4A32: fp32
+// activations against the packed int4 experts): grouped gate_up, swiglu, grouped down, fixed-order reduce.
+// fgu [nslot][2*MI], fhid [nslot][MI], fsout [nslot][H] are the caller's scratch.
+REF_API int ref_moe_fused_block(const float *n2, const uint8_t *gu_wq, const void *gu_sc, const uint8_t *dn_wq, const void *dn_sc,
+                                const int *didx, const float *dw, float *fgu, float *fhid, float *fsout, float *out, int S, int H,
+                                int MI, int K, int sd, void *st) {
+    const long nslot = (long)S * K;
+    const long gu_w = 2L * MI * H, dn_w = (long)H * MI;
+    launch_moe_fused_gu(n2, gu_wq, gu_sc, didx, fgu, H, 2 * MI, K, nslot, gu_w, sd, (cudaStream_t)st);
+    launch_moe_fused_swiglu(fgu, fhid, MI, nslot, (cudaStream_t)st);
+    launch_moe_fused_down(fhid, dn_wq, dn_sc, didx, dw, fsout, MI, H, K, nslot, dn_w, sd, (cudaStream_t)st);
+    launch_moe_fused_reduce(fsout, out, H, K, S, (cudaStream_t)st);
     return ref_status();
 }

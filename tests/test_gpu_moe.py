@@ -115,6 +115,7 @@ def check_stages(oracle, case, lay, ws, out, S, topk, E, H, MI, gemm, act=0):
     (37, 3, 5, 256, 96, 1, 1),          # fp16 scales, GEMV path
     (300, 3, 3, 128, 64, 2, 1),         # every expert gets 300 rows: three tiles per expert, fp16 scales
     (5, 2, 7, 160, 32, 0, 0),           # auto
+    (40, 2, 300, 64, 32, 2, 0),         # more experts than the sort kernel's per-warp histograms hold
 ])
 def test_moe_block_stages(w4a8, oracle, cuda, S, topk, E, H, MI, kernel, sd):
     case = make_block(oracle, S, topk, E, H, MI, seed=300 + S + E, sd=sd)
