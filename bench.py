@@ -219,12 +219,13 @@ def run_ours(args):
 
     timing_log = {}
 
-    def time_steps(step_fn, steps, warmup, graph, after_fn=None, tag=None, min_ms=MIN_TIMED_MS):
+    def time_steps(step_fn, steps, warmup, graph, after_fn=None, tag=None, min_ms=None):
         """step_fn(i, stream_handle) enqueues one step; after_fn(n, stream_handle), if given, is enqueued after every
         block of n steps (eager warm-up block, and as the last node of the captured graph).  One block = `steps` steps
         (a CUDA graph of them, or an eager loop); blocks are replayed back to back, each between its own pair of CUDA
         events on the launching stream, until at least `min_ms` of device time is covered.  Returns the MEDIAN block time
         in ms (max over ranks); the minimum and the number of blocks go to timing_log[tag]."""
+        min_ms = args.min_timed_ms if min_ms is None else min(min_ms, args.min_timed_ms)
         s = torch.cuda.Stream()
         with torch.cuda.stream(s):
             nw = max(warmup, 3)
@@ -437,7 +438,7 @@ def run_ours(args):
             shard = {}
             for tok_ in (8, 512):
                 n2_ = torch.randn(tok_, H_, device=dev, generator=gm)
-                idx_ = torch.stack([torch.randperm(E_, device=dev, generator=gm)[:topk_] for _ in range(tok_)]).reshape(-1).to(torch.int32)
+                idx_ = torch.rand(tok_, E_, device=dev, generator=gm).argsort(dim=1)[:, :topk_].reshape(-1).to(torch.int32)
                 dw_ = torch.rand(tok_ * topk_, device=dev, generator=gm)
                 out_ = torch.empty((tok_, H_), dtype=torch.float32, device=dev)
                 lay_ = w.moe_layout_for(tok_, topk_, H_, MI_, per_)
@@ -554,7 +555,7 @@ def run_ours(args):
         del lw
         # ---- BASELINE configs[4]: 128 experts, top-8, M=8 tokens, gate/up 2048->768 and down 768->2048 -----------------
         E, topk, tok = 128, 8, 8
-        idx = torch.stack([torch.randperm(E, device=dev, generator=g)[:topk] for _ in range(tok)]).reshape(-1).to(torch.int32)
+        idx = torch.rand(tok, E, device=dev, generator=g).argsort(dim=1)[:, :topk].reshape(-1).to(torch.int32)   # top-k distinct experts per token
         moe = {}
         for name, (k_, n_, per_slot) in {"gate_or_up": (2048, 768, 0), "down": (768, 2048, 1)}.items():
             nrow = tok * topk if per_slot else tok
@@ -580,7 +581,7 @@ def run_ours(args):
         per_expert = 2 * MI_ * (H_ // 2 + (H_ // 32) * 4) + H_ * (MI_ // 2 + (MI_ // 32) * 4)     # 2,949,120 B: gate+up+down, fp32 scales
         for tok_ in (8, 512):
             n2_ = torch.randn(tok_, H_, device=dev, generator=g)
-            idx_ = torch.stack([torch.randperm(E, device=dev, generator=g)[:topk] for _ in range(tok_)]).reshape(-1).to(torch.int32)
+            idx_ = torch.rand(tok_, E, device=dev, generator=g).argsort(dim=1)[:, :topk].reshape(-1).to(torch.int32)
             dw_ = torch.rand(tok_ * topk, device=dev, generator=g)
             out_ = torch.empty((tok_, H_), dtype=torch.float32, device=dev)
             lay_ = w.moe_layout_for(tok_, topk, H_, MI_, E)
@@ -709,7 +710,7 @@ def run_ours(args):
                        if world > 1 else "single GPU",
                        "l2": "rotating %d distinct weight copies per rank (%.0f MB > 126 MB L2)" % (nbuf, nbuf * shard_bytes / 1e6),
                        "launch": "CUDA graph of %d steps, replayed %d times (>= %.0f ms timed); value from the median replay, min in `timing`"
-                                 % (timing_log["headline"]["steps_per_block"], timing_log["headline"]["blocks"], MIN_TIMED_MS)},
+                                 % (timing_log["headline"]["steps_per_block"], timing_log["headline"]["blocks"], args.min_timed_ms)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": NCU_TRAFFIC["gemv_m1"] if world == 1 else None, "peak_kind": "of " + peak_kind,
                          "kernel": "gemv_w4a8_dp4a_kernel (w4a8_gemv, M=1, auto policy), rank-local slice of %d rows" % rows, "us_per_launch": per_launch_us,
@@ -763,7 +764,7 @@ def run_kernel_case(args):
         dn_w = torch.randint(0, 256, (E, H_, MI_ // 2), dtype=torch.uint8, device=dev, generator=g)
         dn_s = torch.randn(E, H_, MI_ // 32, device=dev, generator=g).abs() * (0.02 / 7.0)
         n2 = torch.randn(M, H_, device=dev, generator=g)
-        idx = torch.stack([torch.randperm(E, device=dev, generator=g)[:topk] for _ in range(M)]).reshape(-1).to(torch.int32)
+        idx = torch.rand(M, E, device=dev, generator=g).argsort(dim=1)[:, :topk].reshape(-1).to(torch.int32)
         dw = torch.rand(M * topk, device=dev, generator=g)
         out = torch.empty((M, H_), dtype=torch.float32, device=dev)
         ws = torch.empty(w.moe_layout_for(M, topk, H_, MI_, E).bytes, dtype=torch.uint8, device=dev)
@@ -799,7 +800,11 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--kernel-case", default=None, help="profiler helper: gemv_m1, gemv_m8, gemv_m16 or gemm_m512 (see run_kernel_case)")
+    ap.add_argument("--kernel-case", default=None,
+                    help="profiler helper: gemv_m1, gemv_m8, gemv_m16, gemm_m512, quantize_m2048, moe_m8 or moe_m512 (see run_kernel_case)")
+    ap.add_argument("--min-timed-ms", type=float, default=MIN_TIMED_MS,
+                    help="every timed leg replays its block of steps until this much device time is covered (at least 3 blocks); "
+                         "0 keeps a profiler's launch list short")
     args = ap.parse_args()
     if args.kernel_case:
         run_kernel_case(args)

@@ -62,7 +62,9 @@ int w4a8_device_status(uint32_t *detail);
  *                  matrix is large (96 MB of weights or more) or its scales are fp16; one row with fp16 scales outside
  *                  that range uses the tensor-path kernel.  1 = dp4a kernel for every S; 2 = tensor-path kernel for
  *                  every S it supports (K % 256 == 0, 16-byte aligned Wq and sw); 3 = bulk-copy kernel for every
- *                  single row it supports (K % 128 == 0, K <= 8192, 16-byte aligned Wq and sw), dp4a otherwise.
+ *                  single row it supports (K % 128 == 0, K <= 8192, 16-byte aligned Wq and sw), dp4a otherwise;
+ *                  5 = tcgen05 kernel (weights on the MMA's M side, MMQ order) for up to 16 rows per pass where it
+ *                  applies (16-byte aligned Wq and sw; slower than the default kernels, kept as a measured alternative).
  *                  The tensor-path kernel evaluates fp32 in the MMQ order (bit-identical to w4a8_gemm and to the
  *                  reference's MMQ kernels); the dp4a and bulk-copy kernels share one fixed order of their own (within
  *                  1e-5).  Policy 2 therefore makes a row's bits independent of S for all S >= 1 (the reference's
@@ -72,7 +74,9 @@ int w4a8_device_status(uint32_t *detail);
  *                  the epilogue (default, the faster one); 0 = operands converted to fp16 on the way into shared
  *                  memory (every int4 and int8 value is exact in fp16), tcgen05.mma kind::f16 with fp32
  *                  accumulation of one 32-element group, which is exact as well (|sum| <= 32*127*8 < 2^24).
- *                  Both give the same bits. */
+ *                  Both give the same bits.
+ *   "moe_kernel":  w4a8_moe_block's expert products: 0 = by slot count (default), 1 = grouped GEMV, 2 = sorted grouped
+ *                  tensor-core GEMM. */
 int w4a8_config(const char *key, int value);
 
 /* ---- a1: activation quantization ------------------------------------------------------------------

@@ -48,6 +48,40 @@ def test_quantize_bit_exact(w4a8, oracle, cuda, S, K):
     assert np.array_equal(xsum.cpu().numpy(), xsum_o)
 
 
+def test_quantize_quotients_at_half_integers(w4a8, oracle, cuda):
+    """Every element is built to land on, or within two ulp of, a half-integer quotient (k + 0.5) * d: the cases where
+    q = rintf(x / d) (kernels/quantize_x.cuh:36) depends on the last bit of the IEEE division (a reciprocal multiply in its
+    place was measured — no faster — and would have to fall back to the division exactly here)."""
+    rng = np.random.default_rng(4242)
+    S, K = 64, 2048
+    X = np.empty((S, K), dtype=np.float32)
+    for s_ in range(S):
+        for b in range(K // 32):
+            A = np.float32(rng.uniform(0.01, 300.0))
+            d = np.float32(A / np.float32(127.0))
+            blk = np.empty(32, dtype=np.float32)
+            blk[0] = A
+            for j in range(1, 32):
+                x = np.float32(d * np.float32(rng.integers(0, 126) + 0.5))
+                for _ in range(abs(j % 5 - 2)):
+                    x = np.nextafter(x, np.float32(np.inf) if j % 5 > 2 else np.float32(0), dtype=np.float32)
+                blk[j] = x if rng.random() < 0.5 else -x
+            X[s_, b * 32:(b + 1) * 32] = blk
+    xq_o, xs_o, xsum_o = oracle.quantize_x_q8(X)
+    xq, xs, xsum = quantize_dev(w4a8, to_dev(X, cuda))
+    torch.cuda.synchronize()
+    assert np.array_equal(xq.cpu().numpy(), xq_o)
+    assert np.array_equal(xs.cpu().numpy().view(np.uint32), xs_o.view(np.uint32)) and np.array_equal(xsum.cpu().numpy(), xsum_o)
+    # the one-lane-per-element kernel (4-byte aligned input)
+    buf = torch.zeros(S * K + 1, dtype=torch.float32, device=cuda)
+    buf[1:] = to_dev(X, cuda).reshape(-1)
+    xq2 = torch.empty((S, K), dtype=torch.int8, device=cuda)
+    xs2 = torch.empty((S, K // 32), dtype=torch.float32, device=cuda)
+    w4a8.launch_quantize_x_q8(buf.data_ptr() + 4, xq2, xs2, None, K, S)
+    torch.cuda.synchronize()
+    assert np.array_equal(xq2.cpu().numpy(), xq_o) and np.array_equal(xs2.cpu().numpy().view(np.uint32), xs_o.view(np.uint32))
+
+
 def test_quantize_unaligned_and_null_xsum(w4a8, oracle, cuda):
     S, K = 3, 256
     X = oracle.make_activations(S, K, seed=7)
