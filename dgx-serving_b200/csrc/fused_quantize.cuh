@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(256) glu_quantize_kernel(const float4 *__restr
     // [S][2*IN] has pitch 2*IN/4 and U = G + IN)
     const long stride = (long)gridDim.x * blockDim.x;
     pdl_launch_dependents();
+    pdl_wait();   // G and U come from the kernel before this one (a no-op unless launched for programmatic dependent launch)
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i - (threadIdx.x & 31) < nvec; i += stride) {
         const bool live = i < nvec;
         float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -128,7 +129,8 @@ inline int launch_rmsnorm_quantize(const float *X, const float *W, float eps, in
 }
 
 inline int launch_glu_quantize(const float *G, const float *U, int act, float *Y, int8_t *xq, float *xs, int32_t *xsum, int IN,
-                               int S, cudaStream_t st, long pitch = 0 /* floats between rows of G / U; 0 = IN */) {
+                               int S, cudaStream_t st, long pitch = 0 /* floats between rows of G / U; 0 = IN */,
+                               bool pdl = false /* launch for programmatic dependent launch (inside a chain of such kernels) */) {
     const long nvec = (long)S * IN / 4;
     long want = (nvec + 255) / 256, cap = (long)sm_count() * 8;
     const unsigned grid = (unsigned)(want < cap ? want : cap);
@@ -136,7 +138,11 @@ inline int launch_glu_quantize(const float *G, const float *U, int act, float *Y
     float4 *y = reinterpret_cast<float4 *>(Y);
     uint32_t *q = reinterpret_cast<uint32_t *>(xq);
     const long pv = (pitch > 0 ? pitch : IN) / 4;
-    if (act == 0) glu_quantize_kernel<0><<<grid, 256, 0, st>>>(g, u, y, q, xs, xsum, nvec, IN / 4, pv);
+    if (pdl) {
+        cudaError_t e = act == 0 ? launch_pdl(glu_quantize_kernel<0>, dim3(grid), dim3(256), 0, st, g, u, y, q, xs, xsum, nvec, IN / 4, pv)
+                                 : launch_pdl(glu_quantize_kernel<1>, dim3(grid), dim3(256), 0, st, g, u, y, q, xs, xsum, nvec, IN / 4, pv);
+        if (e != cudaSuccess) return cuda_fail(e, "glu_quantize_x_q8 launch");
+    } else if (act == 0) glu_quantize_kernel<0><<<grid, 256, 0, st>>>(g, u, y, q, xs, xsum, nvec, IN / 4, pv);
     else glu_quantize_kernel<1><<<grid, 256, 0, st>>>(g, u, y, q, xs, xsum, nvec, IN / 4, pv);
     return launch_status("glu_quantize_x_q8");
 }

@@ -186,6 +186,8 @@ __global__ void __launch_bounds__(128) moe_gather_rows_kernel(const int8_t *__re
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float4 *__restrict__ Sout, const int *__restrict__ pos, const float *__restrict__ dw,
                                                           float4 *__restrict__ out, int H4, int topk, long total /* = S * H4 */) {
     const long stride = (long)gridDim.x * blockDim.x;
+    pdl_launch_dependents();
+    pdl_wait();   // the down outputs come from the kernel before this one
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const long b = i / H4;
         const int o = (int)(i - b * H4);
@@ -305,7 +307,7 @@ inline int launch_experts(const BlockArgs &a, const Buffers &b, bool use_gemm, l
     } else {
         rc = launch_moe_gemv(b.xq, b.xs, a.gu_wq, a.gu_sc, a.idx, b.gu, nslots, a.topk, 0, 2 * a.MI, a.H, a.experts, a.scale_dtype, st, a.expert_base);
         if (rc != W4A8_OK) return rc;
-        rc = launch_glu_quantize(b.gu, b.gu + a.MI, a.act, nullptr, b.xq_h, b.xs_h, nullptr, a.MI, nslots, st, 2L * a.MI);
+        rc = launch_glu_quantize(b.gu, b.gu + a.MI, a.act, nullptr, b.xq_h, b.xs_h, nullptr, a.MI, nslots, st, 2L * a.MI, true);
         if (rc != W4A8_OK) return rc;
         rc = launch_moe_gemv(b.xq_h, b.xs_h, a.dn_wq, a.dn_sc, a.idx, b.sout, nslots, a.topk, 1, a.H, a.MI, a.experts, a.scale_dtype, st, a.expert_base);
         if (rc != W4A8_OK) return rc;
@@ -338,7 +340,10 @@ inline int launch_block(const BlockArgs &a, cudaStream_t st) {
     const long total = (long)a.S * (a.H / 4);
     const long want = (total + 255) / 256;
     const unsigned cg = (unsigned)(want < (long)sms * 8 ? (want > 0 ? want : 1) : (long)sms * 8);
-    moe_combine_kernel<<<cg, 256, 0, st>>>(src, pos, a.dw, reinterpret_cast<float4 *>(a.out), a.H / 4, a.topk, total);
+    // the grouped GEMVs before it are launched for programmatic dependent launch; so is the combine (it waits first)
+    const cudaError_t le = launch_pdl(moe_combine_kernel, dim3(cg), dim3(256), 0, st, src, pos, a.dw, reinterpret_cast<float4 *>(a.out), a.H / 4,
+                                      a.topk, total);
+    if (le != cudaSuccess) return cuda_fail(le, "moe_combine launch");
     return launch_status("moe_combine");
 }
 
