@@ -70,6 +70,8 @@ constexpr int OFF_B8 = OFF_A + SA * A_STAGE;
 constexpr int OFF_BP = OFF_B8 + S8 * B8_STAGE;
 constexpr int OFF_SW = OFF_BP + SB * BP_STAGE;
 constexpr int OFF_BAR = OFF_SW + SS * SW_STAGE;
+constexpr int BNG = 64;          // GROUPED: accumulator columns per group = most rows of an item (MMA N); 8 buffers of 64 columns,
+                                 // i.e. two K-tiles of accumulators in tensor memory: K-tile j+1's MMAs run while j is fetched
 constexpr int KD = 12;           // K-tile-done ring (GROUPED): a multiple of SA and S8, deeper than any role can lag
 constexpr int NUM_BARS = 2 * (SA + SB + S8 + SS + TB) + KD;
 constexpr int OFF_TMEM = OFF_BAR + NUM_BARS * 8;
@@ -201,9 +203,9 @@ __device__ __forceinline__ void epi_dump(const uint32_t (&d)[NC], int32_t *__res
 }
 
 // Grouped experts (GROUPED instantiation): the activation rows are sorted by expert, item i of the list says
-// "expert x, sorted rows [y, y + z)" with z <= BM (one item per 128-row tile of an expert, written on the device by
+// "expert x, sorted rows [y, y + z)" with z <= BNG (one item per 64-row tile of an expert, written on the device by
 // moe_sort_kernel), the weights are the flat [experts * N][K/2] tensor of the reference (kernels/moe_fused.cuh:21-24:
-// expert e starts e * N rows in), and one unit of work is (item, 128-column tile of the expert's N outputs).
+// expert e starts e * N rows in), and one unit of work is (item, 128 of the expert's N outputs).
 struct GroupList {
     const int4 *items = nullptr;
     const int *num_items = nullptr;
@@ -329,7 +331,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             Ring ra(SA), r8(S8), rt(TB);
-            const uint32_t idesc = ptx::umma_idesc_s8(BM, BN);
+            const uint32_t idesc = ptx::umma_idesc_s8(BM, BN), idesc_g = ptx::umma_idesc_s8(BN, BNG);
             bool ok = true;
             int kc = 0;
             for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
@@ -342,20 +344,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
                     const uint64_t bdesc = ptx::umma_desc_k_sw128(base + OFF_B8 + r8.stage * B8_STAGE);
                     const int ng = min(GPK, wk.g1 - (wk.g0 + kt * GPK));
                     if (KT_COMMIT) {
-                        // all of the K-tile's accumulator buffers free, its MMAs back to back, one commit
-                        int st = rt.stage; uint32_t ph = rt.phase;
-                        for (int g = 0; g < ng && ok; g++) {
-                            if (!ptx::mbar_wait(BAR(TM_EMPTY + st), ph ^ 1u)) { dev_set_error(ERR_MMA | 3); ok = false; }
-                            if (++st == TB) { st = 0; ph ^= 1u; }
-                        }
-                        if (!ok) break;
+                        // K-tile kc uses the accumulator half kc & 1 (GPK buffers of BNG columns); wait until the epilogue has
+                        // fetched the K-tile that used it before (kc - 2), then the K-tile's MMAs back to back and ONE commit
+                        const int half = kc & 1;
+                        if (!ptx::mbar_wait(BAR(TM_EMPTY + half), ((uint32_t)(kc >> 1) & 1u) ^ 1u)) { dev_set_error(ERR_MMA | 3); ok = false; break; }
                         ptx::tc_fence_after_sync();
                         for (int g = 0; g < ng; g++) {
                             // the expanded weights are the MMA's A operand (accumulator lanes = weight rows), the activations
-                            // its B operand (columns = tokens): an expert's tile has few live tokens, and the epilogue's work
-                            // follows the live COLUMNS while all 128 lanes stay busy
-                            ptx::umma_i8(tmem_base + rt.stage * BN, bdesc + (uint64_t)(g * 2), adesc + (uint64_t)(g * 2), idesc, 0u);
-                            rt.advance();
+                            // its B operand (columns = tokens, BNG of them): an expert's tile has few live tokens, and the
+                            // epilogue's work follows the live COLUMNS while all 128 lanes stay busy
+                            ptx::umma_i8(tmem_base + (half * GPK + g) * BNG, bdesc + (uint64_t)(g * 2), adesc + (uint64_t)(g * 2), idesc_g, 0u);
                         }
                         ptx::umma_commit(BAR(KT_DONE + kc % KD));
                         ra.advance();
@@ -497,14 +495,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
         Ring rs(SS), rt(TB);
         bool ok = true;
         if (GROUPED) {
-            // Transposed accumulator: lanes are weight rows (all 128 live), columns are the item's tokens (z <= 128 live,
-            // 32 on average).  The 4 warps that share a quad of lanes deal the live columns out in chunks of CW: warp
-            // group cg takes chunks cg, cg + 4, ... so that at z = 32 every one of the 16 warps converts and scales
-            // 8 columns per group instead of 4 warps doing 32 each.  The accumulator buffer is released as soon as the
-            // chunks are in registers.
-            constexpr int CW = 8, CK = BM / (4 * CW);      // 4 chunks of 8 columns per warp at most
+            // Transposed accumulator: lanes are weight rows (all 128 live), columns are the item's tokens (z <= BNG live, 32
+            // on average).  The 4 warps that share a quad of lanes deal the live columns out in chunks of CW: warp group cg
+            // takes chunks cg and cg + 4, so that at z = 32 every one of the 16 warps converts and scales 8 columns per
+            // group.  A K-tile's accumulators (one half of tensor memory) are handed back once all of its groups have been
+            // fetched; the other half is being written by the next K-tile's MMAs meanwhile.
+            constexpr int CW = 8, CK = BNG / (4 * CW);     // 2 chunks of 8 columns per warp at most
             const int cg = ew >> 2;
-            int kce = 0;                                   // kce: K-tiles of this CTA so far (the index every role counts)
+            int kce = 0;                                   // K-tiles of this CTA so far (the index every role counts)
             for (int wi = blockIdx.x; wi < num_work && ok; wi += gridDim.x) {
                 const Work wk = decode_work<GROUPED>(wi, m_tiles, num_tiles, nb, gsplit, M, N, n_tiles, gl);
                 const int z = wk.mend - wk.m0;
@@ -515,57 +513,43 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
                 for (int k = 0; k < CK; k++)
 #pragma unroll
                     for (int j = 0; j < CW; j++) acc[k][j] = 0.f;
-                const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16) + CW * cg;
-                const float *stage = nullptr;
                 const int ngroups = wk.g1 - wk.g0;
                 for (int gi = 0; gi < ngroups; gi += GPK) {             // one K-tile = up to GPK groups = one commit
                     const int ngk = min(GPK, ngroups - gi);
                     if (!ptx::mbar_wait_warp(BAR(SW_FULL + rs.stage), rs.phase)) { dev_set_error(ERR_EPILOGUE | 1); ok = false; break; }
-                    stage = reinterpret_cast<const float *>(base_ptr + OFF_SW + rs.stage * SW_STAGE);
+                    const float *stage = reinterpret_cast<const float *>(base_ptr + OFF_SW + rs.stage * SW_STAGE);
                     if (!ptx::mbar_wait_warp(BAR(KT_DONE + kce % KD), (uint32_t)(kce / KD) & 1u)) { dev_set_error(ERR_EPILOGUE | 2); ok = false; break; }
                     ptx::tc_fence_after_sync();
+                    const int half = kce & 1;
                     kce++;
-                    if (nlive <= 1) {
-                        // at most one chunk of columns per group and warp (z <= 32 tokens): fetch the chunk of EVERY group of the
-                        // K-tile, hand all accumulator buffers back at once, then convert and scale — the MMAs of the next
-                        // K-tile run meanwhile
-                        uint32_t d[GPK][CW];
-                        int st = rt.stage;
-#pragma unroll
-                        for (int g = 0; g < GPK; g++) {
-                            if (g < ngk && nlive) ptx::tmem_ld(tlane + st * BN, d[g]);
-                            if (++st == TB) st = 0;
-                        }
+                    const uint32_t tl = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * GPK * BNG + CW * cg);
+                    // chunks (group g, k) in order; the load of the next chunk is in flight while the current one is
+                    // converted and scaled (two register sets)
+                    uint32_t da[CW], db[CW];
+                    const int nch = ngk * nlive;                        // live chunks of this K-tile for this warp
+                    if (nch > 0) ptx::tmem_ld(tl, da);
+                    for (int c = 0; c < nch; c++) {
+                        const int g = nlive == 2 ? (c >> 1) : c, k = nlive == 2 ? (c & 1) : 0;
                         ptx::tmem_ld_wait();
-                        ptx::tc_fence_before_sync();
-                        __syncwarp();
-                        for (int g = 0; g < ngk; g++) {
-                            if (lane == 0) ptx::mbar_arrive(BAR(TM_EMPTY + rt.stage));
-                            rt.advance();
-                        }
-                        if (nlive) {
-#pragma unroll
-                            for (int g = 0; g < GPK; g++)
-                                if (g < ngk) epi_chunk_t<CW>(d[g], stage + GPK * BN + g * BM + CW * cg, stage[g * BN + quad * 32 + lane], acc[0]);
-                        }
-                    } else {
-                        for (int g = 0; g < ngk; g++) {
-                            uint32_t d[CK][CW];
-#pragma unroll
-                            for (int k = 0; k < CK; k++)
-                                if (k < nlive) ptx::tmem_ld(tlane + rt.stage * BN + 4 * CW * k, d[k]);
-                            ptx::tmem_ld_wait();
+                        if (c + 1 < nch) {
+                            const int g1 = nlive == 2 ? ((c + 1) >> 1) : c + 1, k1 = nlive == 2 ? ((c + 1) & 1) : 0;
+                            if (c & 1) ptx::tmem_ld(tl + g1 * BNG + 4 * CW * k1, da);
+                            else ptx::tmem_ld(tl + g1 * BNG + 4 * CW * k1, db);
+                        } else {
+                            // the K-tile's last chunk is in registers: hand its half of tensor memory back
                             ptx::tc_fence_before_sync();
                             __syncwarp();
-                            if (lane == 0) ptx::mbar_arrive(BAR(TM_EMPTY + rt.stage));
-                            rt.advance();
-                            const float swl = stage[g * BN + quad * 32 + lane];                   // this lane's weight scale / 16
-                            const float *xsg = stage + GPK * BN + g * BM + CW * cg;               // the tokens' scales of this group
-#pragma unroll
-                            for (int k = 0; k < CK; k++)
-                                if (k < nlive) epi_chunk_t<CW>(d[k], xsg + 4 * CW * k, swl, acc[k]);
-                            ptx::tc_fence_after_sync();
+                            if (lane == 0) ptx::mbar_arrive(BAR(TM_EMPTY + half));
                         }
+                        const float swl = stage[g * BN + quad * 32 + lane];                     // this lane's weight scale / 16
+                        const float *xsg = stage + GPK * BN + g * BM + CW * cg + 4 * CW * k;  // the tokens' scales of this group
+                        if (k == 0) { if (c & 1) epi_chunk_t<CW>(db, xsg, swl, acc[0]); else epi_chunk_t<CW>(da, xsg, swl, acc[0]); }
+                        else        { if (c & 1) epi_chunk_t<CW>(db, xsg, swl, acc[1]); else epi_chunk_t<CW>(da, xsg, swl, acc[1]); }
+                    }
+                    if (nch == 0) {
+                        ptx::tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(BAR(TM_EMPTY + half));
                     }
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(BAR(SW_EMPTY + rs.stage));

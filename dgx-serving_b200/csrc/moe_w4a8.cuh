@@ -8,7 +8,7 @@
 //
 // Few slots (decode): one grouped GEMV launch per projection, one CTA column per slot.  Many slots (prefill): the slots
 // are sorted by expert on the device and both projections run as grouped GEMMs on the tensor cores — work unit =
-// (expert, tile of up to 128 of its rows) x 128 output columns, every expert's weights streamed once.
+// (expert, tile of up to 64 of its rows) x 128 output columns, every expert's weights streamed once.
 // An expert shard (experts [expert_base, expert_base + experts) on this rank) computes only the slots routed to its
 // experts; the slots' down outputs are then sent to every rank's arena (moe_push_rows_kernel) and every rank combines.
 #pragma once
@@ -23,10 +23,7 @@ namespace w4a8 {
 namespace moe {
 
 constexpr int MAX_EXPERTS = 1024;
-#ifndef W4A8_MOE_TILE_ROWS
-#define W4A8_MOE_TILE_ROWS 128
-#endif
-constexpr int TILE_ROWS = W4A8_MOE_TILE_ROWS;   // rows per item of the grouped GEMM (at most gemm::BM)
+constexpr int TILE_ROWS = gemm::BNG;   // rows per item of the grouped GEMM = its accumulator's columns
 
 // Byte offsets of the block's intermediates inside the caller's workspace (all 256-byte aligned).
 struct Layout {
@@ -67,7 +64,7 @@ inline Layout layout_for(int S, int topk, int H, int MI, int experts) {
 // [0, experts) belong to another rank or are invalid and get pos = -1), and the item list of the grouped GEMM.
 //   1. every warp owns a contiguous segment of the slots and counts its experts (per-warp histogram rows in shared
 //      memory when experts <= FAST_EXPERTS, else one shared histogram);
-//   2. warp 0 scans the expert totals 32 at a time (offsets, number of 128-row tiles) and writes the item list;
+//   2. warp 0 scans the expert totals 32 at a time (offsets, number of 64-row tiles) and writes the item list;
 //   3. thread e turns column e of the per-warp histograms into the warps' first positions for expert e;
 //   4. every warp walks its segment 32 slots at a time: a slot's position = its warp's running position for the
 //      expert + its rank among the equal ids of the 32 (match_any), so an expert's rows keep the slots' order.

@@ -218,7 +218,7 @@ int w4a8_moe_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const vo
  * (runtime/weights_qwen.cu:62-63).  idx (global expert ids) and dw (router weights) are device arrays of S*topk
  * entries written by earlier work of the stream; every id must name an existing expert.
  * Up to 128 slots run as one grouped GEMV launch per projection; above that the slots are sorted by expert on the
- * device and both projections run as grouped tensor-core GEMMs whose work units are (expert, up to 128 of its
+ * device and both projections run as grouped tensor-core GEMMs whose work units are (expert, up to 64 of its
  * rows) x 128 outputs (w4a8_config("moe_kernel", 1 | 2) forces one).  Nothing is allocated: the intermediates live
  * in the caller's workspace at the offsets w4a8_moe_layout_for reports (256-byte aligned device memory of
  * layout.bytes bytes).  H and MI multiples of 32, at most 1024 experts. */

@@ -73,7 +73,7 @@ def test_moe_layout_is_disjoint_and_aligned(w4a8):
     S, topk, H, MI, E = 512, 8, 2048, 768, 128
     lay = w4a8.moe_layout_for(S, topk, H, MI, E)
     n = S * topk
-    sizes = {"perm": n * 4, "pos": n * 4, "offsets": (E + 1) * 4, "items": (E + n // 128 + 1) * 16, "num_items": 4, "xq": S * H,
+    sizes = {"perm": n * 4, "pos": n * 4, "offsets": (E + 1) * 4, "items": (E + n // 64 + 1) * 16, "num_items": 4, "xq": S * H,
              "xs": S * (H // 32) * 4, "xq_g": n * H, "xs_g": n * (H // 32) * 4, "gu": n * 2 * MI * 4, "xq_h": n * MI, "xs_h": n * (MI // 32) * 4,
              "sout": n * H * 4}
     spans = sorted((getattr(lay, k), getattr(lay, k) + v) for k, v in sizes.items())

@@ -67,8 +67,8 @@ def check_stages(oracle, case, lay, ws, out, S, topk, E, H, MI, gemm, act=0):
         assert np.array_equal(offs, np.concatenate([[0], np.cumsum(np.bincount(idx, minlength=E))]))
         n_items = int(ws_view(ws, lay.num_items, (1,), torch.int32).item())
         items = ws_view(ws, lay.items, (n_items, 4), torch.int32).cpu().numpy()
-        assert n_items == int(np.sum((np.bincount(idx, minlength=E) + 127) // 128))
-        assert np.all(items[:, 2] >= 1) and np.all(items[:, 2] <= 128) and int(items[:, 2].sum()) == nslots
+        assert n_items == int(np.sum((np.bincount(idx, minlength=E) + 63) // 64))        # an expert's rows in tiles of up to 64
+        assert np.all(items[:, 2] >= 1) and np.all(items[:, 2] <= 64) and int(items[:, 2].sum()) == nslots
     else:
         pos = np.arange(nslots)
     gu = ws_view(ws, lay.gu, (nslots, 2 * MI), torch.float32).cpu().numpy()[pos]
@@ -113,7 +113,7 @@ def check_stages(oracle, case, lay, ws, out, S, topk, E, H, MI, gemm, act=0):
     (8, 8, 128, 2048, 768, 2, 0),       # the same through the sorted grouped GEMM
     (37, 3, 5, 256, 96, 2, 0),          # ragged: partial tiles, MI not a multiple of the K-tile
     (37, 3, 5, 256, 96, 1, 1),          # fp16 scales, GEMV path
-    (300, 3, 3, 128, 64, 2, 1),         # every expert gets 300 rows: three tiles per expert, fp16 scales
+    (300, 3, 3, 128, 64, 2, 1),         # every expert gets 300 rows: five tiles per expert, fp16 scales
     (5, 2, 7, 160, 32, 0, 0),           # auto
     (40, 2, 300, 64, 32, 2, 0),         # more experts than the sort kernel's per-warp histograms hold
 ])
