@@ -4,8 +4,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Headline (BASELINE.json `metric`): HBM throughput of the W4A8 decode GEMV at M=1 on the
-Qwen3.5-27B-class MLP up/gate shape K=5120, N=17408 (BASELINE.json configs[1]); one step = one GEMV launch
+Headline metric: HBM throughput of the W4A8 decode GEMV at M=1 on the
+Qwen3.5-27B-class MLP up/gate shape K=5120, N=17408 (benchmark configuration 2 of 5); one step = one GEMV launch
 through the C ABI over the next of several distinct weight copies (more bytes than the 126 MB L2, so every
 step streams its weights from HBM).  `value` = algorithmic bytes / time with all inputs resident in HBM;
 `e2e` = the same product through w4a8_linear (quantize + GEMV) with HOST activations and outputs, the
@@ -37,7 +37,7 @@ NCU_TRAFFIC = {  # dram__bytes_read.sum + dram__bytes_write.sum per launch, from
     "gemv_m1": 55.77e6,   # the dp4a streaming kernel, M=1, K=5120, N=17408
 }
 # One string for both arms (the driver compares the two arms' `config.workload`).
-WORKLOAD = "W4A8 decode GEMV M=1 K=5120 N=17408, int4 group-32 weights + fp32 scales (BASELINE configs[1])"
+WORKLOAD = "W4A8 decode GEMV M=1 K=5120 N=17408, int4 group-32 weights + fp32 scales (benchmark configuration 2 of 5)"
 MIN_TIMED_MS = 20.0       # every timed leg replays its steps until at least this much device time is covered
 
 
@@ -424,7 +424,7 @@ def run_ours(args):
                                          "ms_per_step_nccl_allgather": ms_g, "int8_tops_whole_job_nccl_allgather": tops(ms_g),
                                          "ms_rank_local_quantize_gemm": ms_gl, "int8_tops_without_allgather": tops(ms_gl)}
         del Yl2
-        # ---- BASELINE configs[4] split over the ranks: 128 experts, 128 / world per GPU, top-8, M = 8 and 512 tokens; every
+        # ---- benchmark configuration 5 (128 experts, top-8) split over the ranks: 128 experts, 128 / world per GPU, top-8, M = 8 and 512 tokens; every
         # rank computes the slots routed to its experts, the slots' down outputs are exchanged through the arenas and every
         # rank combines (w4a8_moe_block_shard).  Timed without a graph: the step's epoch is an argument of the call. ----------
         if 128 % world == 0:
@@ -474,7 +474,7 @@ def run_ours(args):
             us = ms_m * 1e3 / max(20, args.steps // 2)
             sweep[str(M)] = {"us": us, "gbps": gb_m, "frac_of_measured_hbm": gb_m / hbm_peak, "frac_of_8tbs": gb_m / 8000.0}
         extra["gemv_sweep_k5120_n17408"] = sweep
-        # ---- prefill GEMM, quantize_x inside the timed region (BASELINE configs[3]) ------------------------
+        # ---- prefill GEMM, quantize_x inside the timed region (benchmark configuration 4) ------------------------
         gemm, quant = {}, {}
         for M in (512, 2048, 8192):
             Xh2, Xd2, xq2, xs2, xsum2 = make_x(M, outliers=True)
@@ -532,7 +532,7 @@ def run_ours(args):
         gb_v = gemv_bytes(1, Nv, K) / (us_v * 1e-6) / 1e9
         extra["gemv_m1_lm_head_k5120_n151936"] = {"us": us_v, "gbps": gb_v, "frac_of_measured_hbm": gb_v / hbm_peak}
         del vq, vs, Yv
-        # ---- BASELINE configs[2]: Gemma4-12B-class layer set at M=8, launched back to back --------------------------
+        # ---- benchmark configuration 3: Gemma4-12B-class layer set at M=8, launched back to back --------------------------
         layer = [(3840, 4096), (3840, 3840), (3840, 15360), (3840, 15360), (15360, 3840)]
         reps = 5                                                     # 5 distinct layers' worth of weights (648 MB > L2)
         lw = [[(torch.randint(0, 256, (n_, k_ // 2), dtype=torch.uint8, device=dev, generator=g),
@@ -553,7 +553,7 @@ def run_ours(args):
         extra["gemma4_12b_layer_set_m8"] = {"us_per_layer": ms_l * 1e3 / 20, "gbps": lbytes / (ms_l / 20 * 1e-3) / 1e9,
                                             "algorithmic_bytes_per_layer": lbytes}
         del lw
-        # ---- BASELINE configs[4]: 128 experts, top-8, M=8 tokens, gate/up 2048->768 and down 768->2048 -----------------
+        # ---- benchmark configuration 5: 128 experts, top-8, M=8 tokens, gate/up 2048->768 and down 768->2048 -----------------
         E, topk, tok = 128, 8, 8
         idx = torch.rand(tok, E, device=dev, generator=g).argsort(dim=1)[:, :topk].reshape(-1).to(torch.int32)   # top-k distinct experts per token
         moe = {}
@@ -730,7 +730,7 @@ def run_ours(args):
 
 def run_kernel_case(args):
     """Small single-kernel run for profiler captures: `--kernel-case gemv_m1 | gemv_m8 | gemv_m16 | gemm_m512 | quantize_m2048 |
-    moe_m512 | moe_m8` launches that kernel (moe: the routed-expert block of BASELINE configs[4], all of its kernels)
+    moe_m512 | moe_m8` launches that kernel (moe: the routed-expert block of benchmark configuration 5 (128 experts, top-8), all of its kernels)
     `--steps` times (eagerly, no graph) over 3 rotating copies of the K=5120 x N=17408 weights (167 MB, larger than L2,
     well under 1 GB on the device; moe: one 378 MB set of 128 experts) and prints its CUDA-event time.  Not a bench line."""
     import torch

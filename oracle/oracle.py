@@ -4,7 +4,7 @@ TEST INFRASTRUCTURE ONLY.  Imported by tests/, by __graft_entry__.smoke() and by
 cpu_baseline / --impl reference legs; never by the shipped library or its Python binding.
 
 The arithmetic lives in w4a8_oracle.c (each function cites the reference file:line it restates).  The
-generators below produce the input distributions BASELINE.json's configs name: int4 weights uniform in
+generators below produce the input distributions the benchmark configurations name: int4 weights uniform in
 [-8, 7] packed two per byte in the reference layout, group-32 fp32 scales |N(0, 0.02)|/7, activations
 N(0, 1) (optionally 1 % of entries scaled 20x), all from numpy's PCG64 with an explicit seed.
 """
@@ -209,7 +209,7 @@ def gemv_b200_order(xq, xs, Wq, sw):
     return Y
 
 
-# ---- seeded synthetic inputs of BASELINE.json's shapes ------------------------------------------------
+# ---- seeded synthetic inputs of the benchmark configurations' shapes ------------------------------------------------
 def make_weights(N, K, seed, scale_dtype=0):
     """Packed int4 weights (every nibble uniform in 0..15, i.e. value uniform in [-8,7]) and group scales
     |N(0, 0.02)|/7, fp32 or fp16."""

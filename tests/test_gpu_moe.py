@@ -109,7 +109,7 @@ def check_stages(oracle, case, lay, ws, out, S, topk, E, H, MI, gemm, act=0):
 
 
 @pytest.mark.parametrize("S,topk,E,H,MI,kernel,sd", [
-    (8, 8, 128, 2048, 768, 1, 0),       # BASELINE configs[4] at M = 8: grouped GEMV
+    (8, 8, 128, 2048, 768, 1, 0),       # benchmark configuration 5 (128 experts, top-8) at M = 8: grouped GEMV
     (8, 8, 128, 2048, 768, 2, 0),       # the same through the sorted grouped GEMM
     (37, 3, 5, 256, 96, 2, 0),          # ragged: partial tiles, MI not a multiple of the K-tile
     (37, 3, 5, 256, 96, 1, 1),          # fp16 scales, GEMV path
@@ -125,7 +125,7 @@ def test_moe_block_stages(w4a8, oracle, cuda, S, topk, E, H, MI, kernel, sd):
 
 
 def test_moe_block_config5_m512(w4a8, oracle, cuda):
-    """BASELINE configs[4] at M = 512: 128 experts, top-8, H = 2048, MI = 768 — 4096 slots through the sorted grouped GEMM,
+    """benchmark configuration 5 (128 experts, top-8) at M = 512: 128 experts, top-8, H = 2048, MI = 768 — 4096 slots through the sorted grouped GEMM,
     every stage against the oracle."""
     S, topk, E, H, MI = 512, 8, 128, 2048, 768
     case = make_block(oracle, S, topk, E, H, MI, seed=512)

@@ -1,13 +1,13 @@
 """GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle.
 
-Bars (BASELINE north_star): quantized activations and int32 group dots bit-exact; fp32 outputs within
+Bars: quantized activations and int32 group dots bit-exact; fp32 outputs within
 1e-5 relative.  The library's fp32 orders are fixed and restated in the oracle, so most fp32 checks here
 are in fact bit-exact too: the GEMM family reproduces the reference MMQ order
 (kernels/gemm_mmq.cuh:104-105) and so does the GEMV family's tensor-path kernel (S >= 2), the single-row dp4a GEMV
 kernel has its own documented order; against the *other* order the
 reference's own gate max|d|/rms < 1e-5 (tests/test_gemm_mmq.cu:28) applies.
 Shapes follow the reference tests: tests/test_w4a8.cu:95-98, tests/test_gemm_mmq.cu:38,
-tests/test_gemm_mma.cu:40, plus BASELINE.json config 1 and ragged / partial-K-tile cases.
+tests/test_gemm_mma.cu:40, plus benchmark configuration 1 and ragged / partial-K-tile cases.
 """
 import numpy as np
 import pytest
@@ -115,7 +115,7 @@ def test_group_dots_bit_exact(w4a8, oracle, cuda, path, M, N, K):
 
 
 GEMV_SHAPES = [(1024, 256, 1), (1024, 2048, 1), (3584, 1024, 1), (1024, 4096, 5),   # tests/test_w4a8.cu:95-98
-               (4096, 4096, 1),                                                     # BASELINE config 1
+               (4096, 4096, 1),                                                     # benchmark configuration 1
                (160, 37, 3), (96, 9, 2), (5120, 1000, 16), (15360, 384, 8), (2048, 768, 7), (768, 2048, 12)]
 
 
@@ -343,7 +343,7 @@ def test_linear_host_entry(w4a8, oracle, cuda, S, N, K, pinned):
     assert np.array_equal(Yh.numpy().view(np.uint32), want.view(np.uint32))
 
 
-# ---- BASELINE.json configs at their full shapes -----------------------------------------------------------------
+# ---- benchmark configurations at their full shapes -----------------------------------------------------------------
 @pytest.mark.parametrize("K,N", [(3840, 4096), (3840, 3840), (3840, 15360), (15360, 3840)])
 def test_config3_gemma_layer_shapes_m8(w4a8, oracle, cuda, K, N):
     xq, xs, Wq, sw = make_case(oracle, 8, N, K, seed=K + N)
