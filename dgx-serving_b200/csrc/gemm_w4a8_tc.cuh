@@ -160,21 +160,19 @@ __device__ __forceinline__ void epi_chunk(const uint32_t (&d)[NC], float x, cons
 // xs[j] belongs to column j, sw16 to the lane.  t = (float)d * xs (rounded), acc = fma(t, sw16, acc): the same operations
 // on the same values as epi_chunk, so the same bits.
 template <int NC>
-__device__ __forceinline__ void epi_chunk_t(const uint32_t (&d)[NC], const float *__restrict__ xs, float sw16, float *__restrict__ acc) {
+__device__ __forceinline__ void epi_chunk_t(const uint32_t (&d)[NC], const float *__restrict__ xs, float sw16, uint64_t (&acc2)[NC / 2]) {
+    // accumulators stay packed two to a 64-bit register across groups; the tokens' scales are read as packed pairs
     const uint64_t ss = pack_f32x2(sw16, sw16);
 #pragma unroll
     for (int j4 = 0; j4 < NC / 4; j4++) {
-        const float4 x4 = *reinterpret_cast<const float4 *>(xs + j4 * 4);
+        const ulonglong2 x = *reinterpret_cast<const ulonglong2 *>(xs + j4 * 4);   // {xs[4j4], xs[4j4+1]}, {xs[4j4+2], xs[4j4+3]}
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const int j = j4 * 4 + 2 * h;
             const uint64_t f2 = pack_f32x2(__int2float_rn((int)d[j]), __int2float_rn((int)d[j + 1]));
-            const uint64_t x2 = h == 0 ? pack_f32x2(x4.x, x4.y) : pack_f32x2(x4.z, x4.w);
-            uint64_t a2 = pack_f32x2(acc[j], acc[j + 1]);
             uint64_t t2;
-            asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(t2) : "l"(f2), "l"(x2));
-            asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(a2) : "l"(t2), "l"(ss));
-            unpack_f32x2(a2, acc[j], acc[j + 1]);
+            asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(t2) : "l"(f2), "l"(h == 0 ? x.x : x.y));
+            asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc2[j / 2]) : "l"(t2), "l"(ss));
         }
     }
 }
@@ -508,11 +506,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
                 const int z = wk.mend - wk.m0;
                 const int nlive = z > CW * cg ? (z - CW * cg - 1) / (4 * CW) + 1 : 0;   // chunk k covers columns CW*(cg + 4k) ...
                 const int n = wk.n0 + quad * 32 + lane;
-                float acc[CK][CW];
+                uint64_t acc[CK][CW / 2];                              // packed pairs of fp32 accumulators
 #pragma unroll
                 for (int k = 0; k < CK; k++)
 #pragma unroll
-                    for (int j = 0; j < CW; j++) acc[k][j] = 0.f;
+                    for (int j = 0; j < CW / 2; j++) acc[k][j] = 0ull;
                 const int ngroups = wk.g1 - wk.g0;
                 for (int gi = 0; gi < ngroups; gi += GPK) {             // one K-tile = up to GPK groups = one commit
                     const int ngk = min(GPK, ngroups - gi);
@@ -523,33 +521,48 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
                     const int half = kce & 1;
                     kce++;
                     const uint32_t tl = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * GPK * BNG + CW * cg);
-                    // chunks (group g, k) in order; the load of the next chunk is in flight while the current one is
-                    // converted and scaled (two register sets)
-                    uint32_t da[CW], db[CW];
-                    const int nch = ngk * nlive;                        // live chunks of this K-tile for this warp
-                    if (nch > 0) ptx::tmem_ld(tl, da);
-                    for (int c = 0; c < nch; c++) {
-                        const int g = nlive == 2 ? (c >> 1) : c, k = nlive == 2 ? (c & 1) : 0;
-                        ptx::tmem_ld_wait();
-                        if (c + 1 < nch) {
-                            const int g1 = nlive == 2 ? ((c + 1) >> 1) : c + 1, k1 = nlive == 2 ? ((c + 1) & 1) : 0;
-                            if (c & 1) ptx::tmem_ld(tl + g1 * BNG + 4 * CW * k1, da);
-                            else ptx::tmem_ld(tl + g1 * BNG + 4 * CW * k1, db);
-                        } else {
-                            // the K-tile's last chunk is in registers: hand its half of tensor memory back
-                            ptx::tc_fence_before_sync();
-                            __syncwarp();
-                            if (lane == 0) ptx::mbar_arrive(BAR(TM_EMPTY + half));
-                        }
-                        const float swl = stage[g * BN + quad * 32 + lane];                     // this lane's weight scale / 16
-                        const float *xsg = stage + GPK * BN + g * BM + CW * cg + 4 * CW * k;  // the tokens' scales of this group
-                        if (k == 0) { if (c & 1) epi_chunk_t<CW>(db, xsg, swl, acc[0]); else epi_chunk_t<CW>(da, xsg, swl, acc[0]); }
-                        else        { if (c & 1) epi_chunk_t<CW>(db, xsg, swl, acc[1]); else epi_chunk_t<CW>(da, xsg, swl, acc[1]); }
-                    }
-                    if (nch == 0) {
+                    // Fetches are issued in batches of four chunks (32 registers) with one wait per batch, the K-tile's half of
+                    // tensor memory is handed back after the last fetch, and the loops are fully unrolled per case (one or two
+                    // chunks per group): the epilogue is bound by its instruction count, not by the arithmetic in it.
+                    auto release = [&]() {
                         ptx::tc_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(BAR(TM_EMPTY + half));
+                    };
+                    const float *xs0 = stage + GPK * BN + CW * cg;          // + g * BM (+ 4 * CW for the second chunk)
+                    const float *sw0 = stage + quad * 32 + lane;            // + g * BN
+                    uint32_t d[4][CW];
+                    if (nlive == 0) {
+                        release();
+                    } else if (nlive == 1) {
+#pragma unroll
+                        for (int g = 0; g < GPK; g++)
+                            if (g < ngk) ptx::tmem_ld(tl + g * BNG, d[g]);
+                        ptx::tmem_ld_wait();
+                        release();
+#pragma unroll
+                        for (int g = 0; g < GPK; g++)
+                            if (g < ngk) epi_chunk_t<CW>(d[g], xs0 + g * BM, sw0[g * BN], acc[0]);
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < GPK / 2; h++) {                 // groups 2h and 2h + 1, both chunks of each
+                            const int g0 = 2 * h, g1 = 2 * h + 1;
+                            if (g0 < ngk) { ptx::tmem_ld(tl + g0 * BNG, d[0]); ptx::tmem_ld(tl + g0 * BNG + 4 * CW, d[1]); }
+                            if (g1 < ngk) { ptx::tmem_ld(tl + g1 * BNG, d[2]); ptx::tmem_ld(tl + g1 * BNG + 4 * CW, d[3]); }
+                            ptx::tmem_ld_wait();
+                            if (h == GPK / 2 - 1) release();
+                            if (g0 < ngk) {
+                                const float swl = sw0[g0 * BN];
+                                epi_chunk_t<CW>(d[0], xs0 + g0 * BM, swl, acc[0]);
+                                epi_chunk_t<CW>(d[1], xs0 + g0 * BM + 4 * CW, swl, acc[1]);
+                            }
+                            if (g1 < ngk) {
+                                const float swl = sw0[g1 * BN];
+                                epi_chunk_t<CW>(d[2], xs0 + g1 * BM, swl, acc[0]);
+                                epi_chunk_t<CW>(d[3], xs0 + g1 * BM + 4 * CW, swl, acc[1]);
+                            }
+                            if (h == 0) ptx::tc_fence_after_sync();
+                        }
                     }
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(BAR(SW_EMPTY + rs.stage));
@@ -560,9 +573,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_w4a8_tc_kernel(
 #pragma unroll
                     for (int k = 0; k < CK; k++)
 #pragma unroll
-                        for (int j = 0; j < CW; j++) {
+                        for (int j = 0; j < CW; j += 2) {
                             const int col = CW * (cg + 4 * k) + j;
-                            if (k < nlive && col < z) Y[(size_t)(wk.m0 + col) * N + n] = acc[k][j];
+                            float lo, hi;
+                            unpack_f32x2(acc[k][j / 2], lo, hi);
+                            if (k < nlive && col < z) Y[(size_t)(wk.m0 + col) * N + n] = lo;
+                            if (k < nlive && col + 1 < z) Y[(size_t)(wk.m0 + col + 1) * N + n] = hi;
                         }
                 }
             }
