@@ -426,7 +426,7 @@ def run_ours(args):
         del Yl2
         # ---- benchmark configuration 5 (128 experts, top-8) split over the ranks: 128 experts, 128 / world per GPU, top-8, M = 8 and 512 tokens; every
         # rank computes the slots routed to its experts, the slots' down outputs are exchanged through the arenas and every
-        # rank combines (w4a8_moe_block_shard).  Timed without a graph: the step's epoch is an argument of the call. ----------
+        # rank combines (w4a8_moe_block_shard).  A CUDA graph of 10 blocks; its last node advances the arena's epoch base. ----
         if 128 % world == 0:
             E_, topk_, H_, MI_ = 128, 8, 2048, 768
             per_ = E_ // world
@@ -449,14 +449,12 @@ def run_ours(args):
                 dist.all_gather_object(mh, marena.export_handle())
                 marena.connect_handles(mh)
                 dist.barrier()
-                mep = [0]
 
-                def moe_step(i, st):
-                    mep[0] += 1
+                def moe_step(i, st):       # epochs are relative to the arena's base, which the last node of every block advances
                     w.moe_block_shard(n2_, gu_w, gu_s, dn_w, dn_s, idx_, dw_, out_, tok_, topk_, H_, MI_, rank * per_, per_, ws_, marena,
-                                      (mep[0] % 2) * sstride, mep[0], 0, 0, 5000000, 0, st)
+                                      (i % 2) * sstride, i + 1, 0, 0, 5000000, 0, st)
                 nst = 10
-                ms_ms = time_steps(moe_step, nst, 3, graph=False) / nst
+                ms_ms = time_steps(moe_step, nst, 4, graph=True, after_fn=lambda n, st: marena.advance_epoch(n, st)) / nst
                 w.device_status()
                 barrier()
                 marena.close()

@@ -204,16 +204,21 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float4 *__restri
     }
 }
 
-// Expert shard: the down outputs of this rank's slots (rows p < *count of `src`; src row = p when sorted != 0, else the
-// slot) go to row perm[p] of the slot-ordered buffer at y_off in EVERY rank's arena, 16-byte stores, consecutive lanes
+// Expert shard: the down outputs of this rank's slots (sorted rows p < *count of `src`, or — grouped GEMV path, no sort —
+// the slots whose expert id is local) go to row `slot` of the slot-ordered buffer at y_off in EVERY rank's arena, 16-byte stores, consecutive lanes
 // on consecutive pieces of a row; then one system fence per CTA, the last CTA publishes `epoch` and (wait_limit > 0)
 // waits for every rank's flag.
 __global__ void __launch_bounds__(256) moe_push_rows_kernel(const PeerDesc *p, const float4 *__restrict__ src, int sorted,
                                                             const int *__restrict__ perm, const int *__restrict__ count, int H4, size_t y_off,
-                                                            unsigned int epoch, long long wait_limit) {
-    const int n = *count, world = p->world;
+                                                            unsigned int epoch, long long wait_limit, const int32_t *__restrict__ idx,
+                                                            int nslots, int expert_base, int experts) {
+    // perm != nullptr: this rank's rows are sorted rows 0 .. *count - 1 (slot perm[r]); perm == nullptr (grouped GEMV
+    // path, src in slot order): every slot whose expert id lies in this rank's range
+    const int n = perm ? *count : nslots, world = p->world;
     for (int r = blockIdx.x; r < n; r += gridDim.x) {
-        const int slot = perm[r];
+        int slot = r;
+        if (perm) slot = perm[r];
+        else { const int e = idx[r] - expert_base; if (e < 0 || e >= experts) continue; }
         const float4 *s = src + (size_t)(sorted ? r : slot) * H4;
         for (int i = threadIdx.x; i < H4; i += blockDim.x) {
             const float4 v = s[i];
@@ -283,7 +288,7 @@ inline int launch_experts(const BlockArgs &a, const Buffers &b, bool use_gemm, l
     const int nslots = a.S * a.topk, sms = sm_count();
     int rc = launch_quantize_x(a.n2, b.xq, b.xs, nullptr, a.H, a.S, st);
     if (rc != W4A8_OK) return rc;
-    if (use_gemm || a.peers) {
+    if (use_gemm) {
         moe_sort_kernel<<<1, 1024, 0, st>>>(a.idx, nslots, a.expert_base, a.experts, b.perm, b.pos, b.offsets, b.items, b.num_items);
         rc = launch_status("moe_sort");
         if (rc != W4A8_OK) return rc;
@@ -311,8 +316,9 @@ inline int launch_experts(const BlockArgs &a, const Buffers &b, bool use_gemm, l
     }
     if (a.peers) {
         const unsigned pg = (unsigned)(nslots < sms * 4 ? nslots : sms * 4);
-        moe_push_rows_kernel<<<pg, 256, 0, st>>>(a.peers, reinterpret_cast<const float4 *>(b.sout), use_gemm ? 1 : 0, b.perm, b.offsets + a.experts,
-                                                  a.H / 4, a.sout_off, a.epoch, wait_limit);
+        moe_push_rows_kernel<<<pg, 256, 0, st>>>(a.peers, reinterpret_cast<const float4 *>(b.sout), use_gemm ? 1 : 0, use_gemm ? b.perm : nullptr,
+                                                  b.offsets + a.experts, a.H / 4, a.sout_off, a.epoch, wait_limit, a.idx, nslots, a.expert_base,
+                                                  a.experts);
         rc = launch_status("moe_push_rows");
     }
     return rc;
