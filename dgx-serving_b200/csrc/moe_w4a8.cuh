@@ -240,6 +240,59 @@ __global__ void __launch_bounds__(256) moe_push_rows_kernel(const PeerDesc *p, c
     if (wait_limit > 0 && threadIdx.x < 32) wait_flags(p, epoch, wait_limit);
 }
 
+// Expert shard, few slots (the decode form): the row exchange with tagged slots instead of fences and flags
+// (peer_allgather.cuh).  Every element of a local slot's down output goes to the slot buffer of every other arena as one
+// 8-byte store {value, tag of the step}; the combine reads local slots from this rank's own Sout and polls the slot
+// buffer for the others (bounded; error 0x209).  Needs nslots * H <= LL_MAX_SLOTS.
+__global__ void __launch_bounds__(256) moe_push_rows_ll_kernel(const PeerDesc *p, const float *__restrict__ sout, const int32_t *__restrict__ idx,
+                                                               int nslots, int H, int expert_base, int experts, unsigned int epoch) {
+    const unsigned int e = *p->epoch_base + epoch;
+    const unsigned long long tag = (unsigned long long)ll_tag(e) << 32;
+    const size_t off = p->ll_off + (size_t)(e & 1u) * LL_BUF_BYTES;
+    const int world = p->world, rank = p->rank;
+    for (int r = blockIdx.x; r < nslots; r += gridDim.x) {
+        const int le = idx[r] - expert_base;
+        if (le < 0 || le >= experts) continue;                  // another rank's slot
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const unsigned long long pk = tag | (unsigned long long)__float_as_uint(sout[(size_t)r * H + i]);
+            for (int k = 0; k < world; k++)
+                if (k != rank) asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p->base[k] + off + ((size_t)r * H + i) * 8), "l"(pk) : "memory");
+        }
+    }
+}
+__global__ void __launch_bounds__(256) moe_combine_ll_kernel(const PeerDesc *p, const float *__restrict__ sout, const int32_t *__restrict__ idx,
+                                                             const float *__restrict__ dw, float *__restrict__ out, int H, int topk, long total,
+                                                             int expert_base, int experts, unsigned int epoch, long long limit) {
+    const unsigned int e = *p->epoch_base + epoch, tag = ll_tag(e);
+    const unsigned long long *slots = reinterpret_cast<const unsigned long long *>(p->base[p->rank] + p->ll_off + (size_t)(e & 1u) * LL_BUF_BYTES);
+    const long stride = (long)gridDim.x * blockDim.x;
+    bool gave_up = false;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long b = i / H;
+        const int o = (int)(i - b * H);
+        float acc = 0.f;
+        for (int k = 0; k < topk; k++) {
+            const long slot = b * topk + k;
+            const int le = idx[slot] - expert_base;
+            float v = 0.f;
+            if (le >= 0 && le < experts) {
+                v = sout[slot * H + o];
+            } else {
+                const long long t0 = clock64();
+                for (;;) {
+                    unsigned long long x;
+                    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(x) : "l"(slots + slot * H + o) : "memory");
+                    if ((unsigned int)(x >> 32) == tag) { v = __uint_as_float((unsigned int)x); break; }
+                    if (gave_up) break;
+                    if (clock64() - t0 > limit) { dev_set_error(0x209u); gave_up = true; break; }
+                }
+            }
+            acc = __fadd_rn(acc, __fmul_rn(dw[slot], v));
+        }
+        out[i] = acc;
+    }
+}
+
 struct BlockArgs {
     const float *n2 = nullptr;                                   // [S][H] fp32 (post-attention norm output)
     const uint8_t *gu_wq = nullptr, *dn_wq = nullptr;            // this rank's experts: [experts][2*MI][H/2], [experts][H][MI/2]
@@ -282,6 +335,11 @@ inline Buffers buffers_of(const BlockArgs &a) {
     return b;
 }
 
+// Few slots on the grouped-GEMV path and a slot buffer that holds them: the tagged-slot row exchange.
+inline bool tagged_rows(const BlockArgs &a, bool use_gemm) {
+    return a.peers && !use_gemm && (size_t)a.S * a.topk * a.H <= LL_MAX_SLOTS;
+}
+
 // quantize, (sort, gather,) gate|up, activation + quantize, down; with peers: send this rank's rows on and publish
 // (wait_limit > 0: and wait for every rank).
 inline int launch_experts(const BlockArgs &a, const Buffers &b, bool use_gemm, long long wait_limit, cudaStream_t st) {
@@ -314,7 +372,11 @@ inline int launch_experts(const BlockArgs &a, const Buffers &b, bool use_gemm, l
         rc = launch_moe_gemv(b.xq_h, b.xs_h, a.dn_wq, a.dn_sc, a.idx, b.sout, nslots, a.topk, 1, a.H, a.MI, a.experts, a.scale_dtype, st, a.expert_base);
         if (rc != W4A8_OK) return rc;
     }
-    if (a.peers) {
+    if (a.peers && tagged_rows(a, use_gemm)) {
+        const unsigned pg = (unsigned)(nslots < sms * 4 ? nslots : sms * 4);
+        moe_push_rows_ll_kernel<<<pg, 256, 0, st>>>(a.peers, b.sout, a.idx, nslots, a.H, a.expert_base, a.experts, a.epoch);
+        rc = launch_status("moe_push_rows_ll");
+    } else if (a.peers) {
         const unsigned pg = (unsigned)(nslots < sms * 4 ? nslots : sms * 4);
         moe_push_rows_kernel<<<pg, 256, 0, st>>>(a.peers, reinterpret_cast<const float4 *>(b.sout), use_gemm ? 1 : 0, use_gemm ? b.perm : nullptr,
                                                   b.offsets + a.experts, a.H / 4, a.sout_off, a.epoch, wait_limit, a.idx, nslots, a.expert_base,
@@ -329,13 +391,25 @@ inline int launch_block(const BlockArgs &a, cudaStream_t st) {
     const Buffers b = buffers_of(a);
     const bool use_gemm = a.kernel == 2 || (a.kernel == 0 && nslots > GEMV_MAX_SLOTS);
     int rc = W4A8_OK;
+    const bool tagged = tagged_rows(a, use_gemm);
     if (a.peers && a.phase == 2) {
-        allgather_wait_kernel<<<1, 32, 0, st>>>(a.peers, a.epoch, a.wait_limit);
-        rc = launch_status("allgather_wait");
+        if (!tagged) {
+            allgather_wait_kernel<<<1, 32, 0, st>>>(a.peers, a.epoch, a.wait_limit);
+            rc = launch_status("allgather_wait");
+        }
     } else {
         rc = launch_experts(a, b, use_gemm, a.phase == 1 ? 0 : a.wait_limit, st);
     }
     if (rc != W4A8_OK || (a.peers && a.phase == 1)) return rc;
+    if (tagged) {
+        // local slots from this rank's own down outputs, the others from the slot buffer the other ranks fill
+        const long tot = (long)a.S * a.H;
+        const long wantc = (tot + 255) / 256;
+        const unsigned cgl = (unsigned)(wantc < (long)sms * 8 ? (wantc > 0 ? wantc : 1) : (long)sms * 8);
+        moe_combine_ll_kernel<<<cgl, 256, 0, st>>>(a.peers, b.sout, a.idx, a.dw, a.out, a.H, a.topk, tot, a.expert_base, a.experts, a.epoch,
+                                                    a.wait_limit);
+        return launch_status("moe_combine_ll");
+    }
     // one GPU: the down outputs as computed (sorted rows through pos, or slot order); expert shard: the slot-ordered
     // buffer of this rank's arena, complete once every rank's flag has arrived
     const float4 *src = a.peers ? reinterpret_cast<const float4 *>(a.arena_base + a.sout_off) : reinterpret_cast<const float4 *>(b.sout);

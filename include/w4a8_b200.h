@@ -241,7 +241,10 @@ int w4a8_moe_block(const float *n2, const uint8_t *gu_wq, const void *gu_sc, con
  * The rank computes only the slots routed to its experts, stores their down outputs into row `slot` of a
  * slot-ordered buffer Sout[S*topk][H] at sout_offset in EVERY rank's arena (16-byte peer stores), publishes `epoch`,
  * waits (bounded by timeout_us) for every rank's flag and then combines: every rank ends with the whole out[S][H],
- * bit-identical to w4a8_moe_block with all experts on one GPU.  Arena rules as for w4a8_gemv_allgather (alternate
+ * bit-identical to w4a8_moe_block with all experts on one GPU.  With few slots (grouped-GEMV path and S*topk*H <= 512 Ki)
+ * the rows travel as tagged 8-byte stores into the arenas' slot buffers instead and the combine polls for them — no
+ * fence, no flag, the Sout buffer at sout_offset is not touched (same rule as w4a8_gemv_allgather_sync: every
+ * all-gather step on the arena complete on the stream before the next one is issued).  Arena rules as for w4a8_gemv_allgather (alternate
  * sout_offset between consecutive steps); workspace from w4a8_moe_layout_for(S, topk, H, MI, experts_local).
  * phase 0: the whole block.  phase 1: everything up to and including the publish (no wait, no combine) and
  * phase 2: wait + combine only — for a caller that puts other work between the two, and for several ranks driven
