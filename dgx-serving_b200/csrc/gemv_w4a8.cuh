@@ -30,6 +30,7 @@ struct GroupedArgs {
     const int32_t *idx = nullptr;
     int topk = 1, x_per_slot = 0, num_experts = 0, nslots = 1;
     int expert_base = 0;   // experts [expert_base, expert_base + num_experts) live in this Wq / sw (an expert shard)
+    int shard_world = 1;   // expert shard: about 1 / shard_world of the slots are this rank's, the other slots' CTAs exit at once
 };
 
 __device__ __forceinline__ uint4 ldg_w16(const uint8_t *p, bool a16) {
@@ -248,7 +249,7 @@ inline int launch_gemv_dp4a_p(const int8_t *xq, const float *xs, const uint8_t *
     }
     long want = (OUT + GEMV_WARPS - 1) / GEMV_WARPS;
     long cap = (long)sm_count() * occ;
-    if (ga.idx) cap = cap / ga.nslots > 1 ? cap / ga.nslots : 1;
+    if (ga.idx) cap = cap * ga.shard_world / ga.nslots > 1 ? cap * ga.shard_world / ga.nslots : 1;   // CTAs per slot
     const dim3 grid((unsigned)(want < cap ? want : cap), (unsigned)(ga.idx ? ga.nslots : 1));
     // every expert's base stays 16-byte aligned when Wq is, because OUT*IN/2 is a multiple of 16
     cudaError_t le = launch_pdl(kern, grid, dim3(GEMV_WARPS * 32), smem, st, xq, xs, Wq, sw, Y, IN, OUT, S, aligned(Wq, 16), ga, oa);
@@ -426,7 +427,7 @@ inline int launch_gemv_short(const int8_t *xq, const float *xs, const uint8_t *W
     }
     const long units = (OUT + R - 1) / R;
     long want = (units + GEMV_WARPS - 1) / GEMV_WARPS, cap = (long)sm_count() * occ;
-    if (ga.idx) cap = cap / ga.nslots > 1 ? cap / ga.nslots : 1;
+    if (ga.idx) cap = cap * ga.shard_world / ga.nslots > 1 ? cap * ga.shard_world / ga.nslots : 1;   // CTAs per slot
     const dim3 grid((unsigned)(want < cap ? want : cap), (unsigned)(ga.idx ? ga.nslots : 1));
     cudaError_t le = launch_pdl(kern, grid, dim3(GEMV_WARPS * 32), 0, st, xq, xs, Wq, sw, Y, IN, OUT, aligned(Wq, 16), ga);
     if (le != cudaSuccess) return cuda_fail(le, "gemv_w4a8_short launch");
@@ -436,12 +437,13 @@ inline int launch_gemv_short(const int8_t *xq, const float *xs, const uint8_t *W
 // Grouped experts: one launch, grid.y = slots, each slot one activation row against its expert.
 inline int launch_moe_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, const int32_t *idx,
                            float *Y, int nslots, int topk, int x_per_slot, int N, int K, int num_experts,
-                           int scale_dtype, cudaStream_t st, int expert_base = 0) {
+                           int scale_dtype, cudaStream_t st, int expert_base = 0, int shard_world = 1) {
     if (nslots == 0 || N == 0) return W4A8_OK;
     if (nslots > 65535) return fail(W4A8_ERR_UNSUPPORTED, "moe_gemv: at most 65535 slots per launch (got %d)", nslots);
     GroupedArgs ga;
     ga.idx = idx; ga.topk = topk; ga.x_per_slot = x_per_slot; ga.num_experts = num_experts; ga.nslots = nslots;
     ga.expert_base = expert_base;
+    ga.shard_world = shard_world < 1 ? 1 : shard_world;
     if (K <= 32 * QBLK) {                                           // short rows: the R-rows-per-warp kernel
         if (scale_dtype == 1) return launch_gemv_short<__half>(xq, xs, Wq, (const __half *)sw, Y, K, N, st, ga);
         return launch_gemv_short<float>(xq, xs, Wq, (const float *)sw, Y, K, N, st, ga);

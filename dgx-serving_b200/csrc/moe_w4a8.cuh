@@ -302,6 +302,7 @@ struct BlockArgs {
     float *out = nullptr;                                        // [S][H]
     int S = 0, topk = 0, H = 0, MI = 0, expert_base = 0, experts = 0, scale_dtype = 0, act = 0;
     int kernel = 0;                                              // 0 auto, 1 grouped GEMV, 2 grouped GEMM
+    int world = 1;                                               // ranks the experts are split over (sizes the grouped GEMV's grid)
     unsigned char *ws = nullptr;
     const PeerDesc *peers = nullptr;                             // expert shard: every arena's slot-ordered Sout at sout_off
     unsigned char *arena_base = nullptr;
@@ -365,11 +366,11 @@ inline int launch_experts(const BlockArgs &a, const Buffers &b, bool use_gemm, l
         rc = gemm::launch_tc_grouped(b.xq_h, b.xs_h, a.dn_wq, a.dn_sc, b.sout, nslots, a.H, a.MI, a.scale_dtype, a.experts, gl, b.max_items, st);
         if (rc != W4A8_OK) return rc;
     } else {
-        rc = launch_moe_gemv(b.xq, b.xs, a.gu_wq, a.gu_sc, a.idx, b.gu, nslots, a.topk, 0, 2 * a.MI, a.H, a.experts, a.scale_dtype, st, a.expert_base);
+        rc = launch_moe_gemv(b.xq, b.xs, a.gu_wq, a.gu_sc, a.idx, b.gu, nslots, a.topk, 0, 2 * a.MI, a.H, a.experts, a.scale_dtype, st, a.expert_base, a.world);
         if (rc != W4A8_OK) return rc;
         rc = launch_glu_quantize(b.gu, b.gu + a.MI, a.act, nullptr, b.xq_h, b.xs_h, nullptr, a.MI, nslots, st, 2L * a.MI, true);
         if (rc != W4A8_OK) return rc;
-        rc = launch_moe_gemv(b.xq_h, b.xs_h, a.dn_wq, a.dn_sc, a.idx, b.sout, nslots, a.topk, 1, a.H, a.MI, a.experts, a.scale_dtype, st, a.expert_base);
+        rc = launch_moe_gemv(b.xq_h, b.xs_h, a.dn_wq, a.dn_sc, a.idx, b.sout, nslots, a.topk, 1, a.H, a.MI, a.experts, a.scale_dtype, st, a.expert_base, a.world);
         if (rc != W4A8_OK) return rc;
     }
     if (a.peers && tagged_rows(a, use_gemm)) {

@@ -891,6 +891,7 @@ static int moe_block_impl(const float *n2, const uint8_t *gu_wq, const void *gu_
     if (a) {
         b.peers = a->desc_dev; b.arena_base = a->base; b.sout_off = sout_offset; b.epoch = epoch; b.wait_limit = wait_cycles(timeout_us);
         b.phase = phase;
+        b.world = a->world;
     }
     return moe::launch_block(b, st);
 }
