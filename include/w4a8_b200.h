@@ -22,10 +22,10 @@
  *     any CUDA error, models/qwen35_decode.cu:24-25,229).  These return an int status instead:
  *     0 on success, a W4A8_ERR_* code otherwise, with w4a8_last_error() giving the text.  There is
  *     no CPU fallback: without a usable sm_100 device every launch entry point fails.
- *   - One host thread per device, like the reference: the kernel-selection switches of w4a8_config and the
- *     per-device launch caches (shared-memory opt-in, occupancy, tensor maps) are plain process-wide state without
- *     locks.  Several devices may be driven from one process, each from its own thread, as long as w4a8_config is
- *     not called while another thread is inside a launch entry point.
+ *   - One host thread at a time inside the library, like the reference (one process per GPU is the intended
+ *     deployment): the kernel-selection switches of w4a8_config and the launch caches (shared-memory opt-in and
+ *     occupancy per device, tensor maps) are plain process-wide state without locks.  One thread may drive several
+ *     devices (the caches are keyed by the current device); concurrent calls from several threads are not supported.
  */
 #ifndef W4A8_B200_H
 #define W4A8_B200_H
