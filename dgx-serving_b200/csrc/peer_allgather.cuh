@@ -14,10 +14,10 @@
 //    Fences were what made the flag protocol slow at this size: a system-scope fence behind remote stores waits for
 //    their NVLink round trip (2.4 us measured), and so does the device-scope fence of every storing thread.
 //
-//  * slice + flags (everything else).  Outputs go to the rank's own arena; the finished slice is sent to the other
-//    arenas with row-contiguous 16-byte stores (allgather_scatter_kernel, many CTAs; or, W4A8_ALLGATHER=direct, by the
-//    computing threads themselves), the last CTA issues ONE system-scope fence and publishes a per-rank flag on every
-//    peer with relaxed stores.  A consumer waits (bounded) until all `world` flags of its own arena have reached the
+//  * slice + flags (everything else).  Outputs go to the rank's own arena; a small slice is also stored to every other
+//    arena by the computing threads themselves (W4A8_ALLGATHER=push: copied by the last CTA instead), a large one is
+//    sent afterwards with row-contiguous 16-byte stores (allgather_scatter_kernel, many CTAs); the last CTA issues ONE
+//    system-scope fence and publishes a per-rank flag on every peer with relaxed stores.  A consumer waits (bounded) until all `world` flags of its own arena have reached the
 //    step's epoch: a small kernel of its own (w4a8_allgather_wait) or — oa.wait_limit > 0 — the publishing CTA itself.
 //
 // No TMA, no multicast: peer memory is only ever the target of ordinary stores.
