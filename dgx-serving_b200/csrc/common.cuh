@@ -104,6 +104,21 @@ __device__ __forceinline__ void unpack8_x16_seq(uint32_t w, uint32_t &lo, uint32
     lo = __byte_perm(even, odd, 0x5140);  // e0 o0 e1 o1
     hi = __byte_perm(even, odd, 0x7362);  // e2 o2 e3 o3
 }
+// Four quantized activations of one float4: q = rintf(x / d) clamped to +-127 (kernels/quantize_x.cuh:36-37), packed into
+// one word (byte i = q_i), and their sum.  The quotient is at most 127 * (1 + 2^-23) in magnitude because |x| <= amax
+// and d = amax / 127 rounded, so the clamp never changes a finite value: one cvt.rni.sat.s8.f32 per element does
+// round-to-nearest-even, the conversion and the saturation (a NaN quotient — amax infinite — gives 0 either way).
+__device__ __forceinline__ uint32_t quantize4_pack(float4 v, float d, int &sum) {
+    int q0, q1, q2, q3;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q0) : "f"(v.x / d));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q1) : "f"(v.y / d));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q2) : "f"(v.z / d));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q3) : "f"(v.w / d));
+    const uint32_t lo = __byte_perm((uint32_t)q0, (uint32_t)q1, 0x0040), hi = __byte_perm((uint32_t)q2, (uint32_t)q3, 0x0040);
+    const uint32_t w = __byte_perm(lo, hi, 0x5410);
+    sum = __dp4a((int)w, 0x01010101, 0);
+    return w;
+}
 // Activation bytes x[0..7] (two words) split the same way: even = x0 x2 x4 x6, odd = x1 x3 x5 x7.
 __device__ __forceinline__ void split_even_odd(uint32_t x0, uint32_t x1, uint32_t &even, uint32_t &odd) {
     even = __byte_perm(x0, x1, 0x6420);

@@ -20,19 +20,13 @@ __device__ __forceinline__ void quantize_store_vec4(float4 v, long i, bool live,
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
     const float d = amax / 127.0f;
-    int q0 = 0, q1 = 0, q2 = 0, q3 = 0;
-    if (amax != 0.0f) {
-        q0 = (int)rintf(v.x / d); q1 = (int)rintf(v.y / d);
-        q2 = (int)rintf(v.z / d); q3 = (int)rintf(v.w / d);
-    }
-    q0 = max(-127, min(127, q0)); q1 = max(-127, min(127, q1));
-    q2 = max(-127, min(127, q2)); q3 = max(-127, min(127, q3));
-    int sum = q0 + q1 + q2 + q3;
+    int sum = 0;
+    const uint32_t packed = amax != 0.0f ? quantize4_pack(v, d, sum) : 0u;
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     sum += __shfl_xor_sync(0xffffffffu, sum, 4);
     if (live) {
-        xq[i] = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+        xq[i] = packed;
         if ((i & 7) == 0) {
             xs[i >> 3] = d;
             if (xsum) xsum[i >> 3] = sum;

@@ -37,20 +37,13 @@ __global__ void __launch_bounds__(256) quantize_x_q8_vec_kernel(const float4 *__
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
             const float d = amax / 127.0f;
-            int q0 = 0, q1 = 0, q2 = 0, q3 = 0;
-            if (amax != 0.0f) {
-                q0 = (int)rintf(v[u].x / d); q1 = (int)rintf(v[u].y / d);
-                q2 = (int)rintf(v[u].z / d); q3 = (int)rintf(v[u].w / d);
-            }
-            q0 = max(-127, min(127, q0)); q1 = max(-127, min(127, q1));
-            q2 = max(-127, min(127, q2)); q3 = max(-127, min(127, q3));
-            int sum = q0 + q1 + q2 + q3;
+            int sum = 0;
+            const uint32_t packed = amax != 0.0f ? quantize4_pack(v[u], d, sum) : 0u;
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
             sum += __shfl_xor_sync(0xffffffffu, sum, 2);
             sum += __shfl_xor_sync(0xffffffffu, sum, 4);
             if (i < nvec) {
-                xq[i] = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) |
-                        ((uint32_t)(q3 & 0xFF) << 24);
+                xq[i] = packed;
                 if ((i & 7) == 0) {
                     xs[i >> 3] = d;
                     if (xsum) xsum[i >> 3] = sum;
