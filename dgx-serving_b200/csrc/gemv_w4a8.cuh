@@ -412,9 +412,135 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_short_kernel(
     }
 }
 
+// ---- rows of 24 groups (K = 768, the expert down projection of benchmark configuration 5), one activation row -------
+// With a lane per group the kernel above idles 8 lanes of 32 and pays a 5-level shuffle tree per row: 85 warp
+// instructions per 480-byte row, 2.3 TB/s.  Rows of 24 groups are contiguous in memory (384 bytes of nibbles, 24 scales),
+// so here a warp walks the matrix as a flat sequence of groups: a tile is 4 rows = 96 groups = three fully coalesced
+// 512-byte loads (+ three 128-byte scale loads), lane l of load j holding flat group 32 j + l, i.e. group (32 j + l) % 24
+// of row (32 j + l) / 24.  The per-group products go through shared memory and eight lanes per row add them in the
+// order of the shfl_down tree over lanes 0..23 of the lane-per-group kernel (lanes 24..31 there carry +0):
+// ((v[i] + v[i+16]) + (v[i+8] + 0)) for i < 8, then the offsets 4, 2, 1.  Same products, same order: identical bits.
+template <typename ST>
+__global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_flat24_kernel(
+    const int8_t *__restrict__ xq, const float *__restrict__ xs, const uint8_t *__restrict__ Wq,
+    const ST *__restrict__ sw, float *__restrict__ Y, int OUT, GroupedArgs ga) {
+    constexpr int NB = 24, TR = 4, TL = 3;                          // groups per row, rows and loads per tile
+    __shared__ float part[GEMV_WARPS][2][TR * NB];
+    if (ga.idx) {                                                   // blockIdx.y = slot (see the persistent kernel)
+        const int slot = blockIdx.y;
+        pdl_wait();   // the routing indices are written by an earlier kernel of the stream: wait before reading them
+        const int e = ga.idx[slot] - ga.expert_base;
+        if (e < 0 || e >= ga.num_experts) return;
+        const int row = ga.x_per_slot ? slot : slot / ga.topk;
+        xq += (size_t)row * (NB * QBLK);
+        xs += (size_t)row * NB;
+        Wq += (size_t)e * ((size_t)OUT * (NB * 16));
+        sw += (size_t)e * ((size_t)OUT * NB);
+        Y += (size_t)slot * OUT;
+    }
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tiles = (OUT + TR - 1) / TR, ngroups = OUT * NB;
+    const int gw = blockIdx.x * GEMV_WARPS + warp, nw = gridDim.x * GEMV_WARPS;
+    uint4 wa[TL], wb[TL];
+    float sa[TL], sb_[TL];
+    auto load = [&](int tile, uint4 (&w)[TL], float (&sc)[TL]) {
+#pragma unroll
+        for (int j = 0; j < TL; j++) {
+            const int f = tile * (TR * NB) + 32 * j + lane;
+            if (f < ngroups) { w[j] = __ldcs(reinterpret_cast<const uint4 *>(Wq) + f); sc[j] = load_scale(sw, f); }
+            else { w[j] = make_uint4(0, 0, 0, 0); sc[j] = 0.f; }
+        }
+    };
+    pdl_launch_dependents();
+    if (gw < tiles) load(gw, wa, sa);                               // weights only: allowed before the dependency wait
+    pdl_wait();
+    // the three activation groups a lane meets (the pattern repeats every tile), split into even / odd bytes and kept
+    // in shared memory as two planes of 16-byte words indexed [j][lane] (conflict-free); warp j fills plane set j
+    __shared__ uint4 xpat[TL][2][32];
+    __shared__ float xspat[TL][32];
+    if (warp < TL) {
+        const int b = (32 * warp + lane) % NB;
+        const uint4 *src = reinterpret_cast<const uint4 *>(xq + (size_t)b * QBLK);
+        const uint4 v0 = src[0], v1 = src[1];
+        uint4 p0, p1;
+        split_even_odd(v0.x, v0.y, p0.x, p0.y);
+        split_even_odd(v0.z, v0.w, p0.z, p0.w);
+        split_even_odd(v1.x, v1.y, p1.x, p1.y);
+        split_even_odd(v1.z, v1.w, p1.z, p1.w);
+        xpat[warp][0][lane] = p0;
+        xpat[warp][1][lane] = p1;
+        xspat[warp][lane] = xs[b];
+    }
+    __syncthreads();
+    int parity = 0;
+    auto compute = [&](int tile, const uint4 (&w)[TL], const float (&sc)[TL]) {
+        float *pp = part[warp][parity];
+        parity ^= 1;
+#pragma unroll
+        for (int j = 0; j < TL; j++) {
+            uint32_t e0, o0, e1, o1, e2, o2, e3, o3;
+            unpack8_x16(w[j].x, e0, o0); unpack8_x16(w[j].y, e1, o1);
+            unpack8_x16(w[j].z, e2, o2); unpack8_x16(w[j].w, e3, o3);
+            const uint4 p0 = xpat[j][0][lane], p1 = xpat[j][1][lane];
+            const float xsj = xspat[j][lane];
+            int d = __dp4a((int)p0.x, (int)e0, 0);
+            d = __dp4a((int)p0.y, (int)o0, d);
+            d = __dp4a((int)p0.z, (int)e1, d);
+            d = __dp4a((int)p0.w, (int)o1, d);
+            d = __dp4a((int)p1.x, (int)e2, d);
+            d = __dp4a((int)p1.y, (int)o2, d);
+            d = __dp4a((int)p1.z, (int)e3, d);
+            d = __dp4a((int)p1.w, (int)o3, d);                      // d = 16 * D[o,b], exact
+            const float scv = (xsj * sc[j]) * 0.0625f;              // exact 1/16
+            pp[32 * j + lane] = fmaf(scv, (float)d, 0.f);
+        }
+        __syncwarp();
+        // lane = 8 r + i adds groups i, i + 16 and i + 8 of row r; a second buffer (parity) spares the barrier that
+        // would otherwise have to keep the next tile's stores behind these loads
+        const float *v = pp + (lane >> 3) * NB + (lane & 7);
+        float a = __fadd_rn(__fadd_rn(v[0], v[16]), __fadd_rn(v[8], 0.f));
+        a = __fadd_rn(a, __shfl_down_sync(0xffffffffu, a, 4));
+        a = __fadd_rn(a, __shfl_down_sync(0xffffffffu, a, 2));
+        a = __fadd_rn(a, __shfl_down_sync(0xffffffffu, a, 1));
+        const int r = tile * TR + (lane >> 3);
+        if ((lane & 7) == 0 && r < OUT) Y[r] = a;
+    };
+    for (int u = gw; u < tiles; u += 2 * nw) {
+        if (u + nw < tiles) load(u + nw, wb, sb_);
+        compute(u, wa, sa);
+        if (u + nw >= tiles) break;
+        if (u + 2 * nw < tiles) load(u + 2 * nw, wa, sa);
+        compute(u + nw, wb, sb_);
+    }
+}
+
+template <typename ST>
+inline int launch_gemv_flat24(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int OUT,
+                              cudaStream_t st, const GroupedArgs &ga) {
+    auto kern = gemv_w4a8_flat24_kernel<ST>;
+    static PerDevice<int> occ_dev;
+    int &occ = occ_dev.get();
+    if (occ == 0) {
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, GEMV_WARPS * 32, 0);
+        if (e != cudaSuccess) return cuda_fail(e, "gemv_flat24 occupancy query");
+        occ = n > 0 ? n : 1;
+    }
+    const long tiles = (OUT + 3) / 4;
+    long want = (tiles + GEMV_WARPS - 1) / GEMV_WARPS, cap = (long)sm_count() * occ;
+    if (ga.idx) cap = cap * ga.shard_world / ga.nslots > 1 ? cap * ga.shard_world / ga.nslots : 1;   // CTAs per slot
+    const dim3 grid((unsigned)(want < cap ? want : cap), (unsigned)(ga.idx ? ga.nslots : 1));
+    cudaError_t le = launch_pdl(kern, grid, dim3(GEMV_WARPS * 32), 0, st, xq, xs, Wq, sw, Y, OUT, ga);
+    if (le != cudaSuccess) return cuda_fail(le, "gemv_w4a8_flat24 launch");
+    return launch_status("gemv_w4a8_flat24");
+}
+
 template <typename ST>
 inline int launch_gemv_short(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int IN, int OUT,
                              cudaStream_t st, const GroupedArgs &ga) {
+    // rows of exactly 24 groups, 16-byte aligned everywhere: the flat-group kernel (the tile loop indexes with int)
+    if (IN == 24 * QBLK && aligned(Wq, 16) && aligned(xq, 16) && (long)OUT * 24 < (1L << 30))
+        return launch_gemv_flat24<ST>(xq, xs, Wq, sw, Y, OUT, st, ga);
     constexpr int R = 4;
     auto kern = gemv_w4a8_short_kernel<R, ST>;
     static PerDevice<int> occ_dev;

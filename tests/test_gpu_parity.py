@@ -116,7 +116,8 @@ def test_group_dots_bit_exact(w4a8, oracle, cuda, path, M, N, K):
 
 GEMV_SHAPES = [(1024, 256, 1), (1024, 2048, 1), (3584, 1024, 1), (1024, 4096, 5),   # tests/test_w4a8.cu:95-98
                (4096, 4096, 1),                                                     # benchmark configuration 1
-               (160, 37, 3), (96, 9, 2), (5120, 1000, 16), (15360, 384, 8), (2048, 768, 7), (768, 2048, 12)]
+               (160, 37, 3), (96, 9, 2), (5120, 1000, 16), (15360, 384, 8), (2048, 768, 7), (768, 2048, 12),
+               (768, 2048, 1), (768, 1030, 1), (768, 3, 1)]                         # rows of 24 groups: the flat-group kernel, ragged last tile
 
 
 def gemv_expected(oracle, xq, xs, Wq, sw, policy=0):
