@@ -321,17 +321,19 @@ inline int launch_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, con
     return launch_gemv_st<float>(xq, xs, Wq, (const float *)sw, Y, IN, OUT, S, st, oa);
 }
 
-// ---- short rows (K <= 1024: at most one group per lane), one activation row, optional expert grouping -----------
-// With one group per lane the persistent kernel above keeps only two 16-byte loads per lane in flight (its batches
-// are "groups of one row"), far too few to stream at HBM speed: the 768-wide expert down projection ran at 2.3 TB/s.
-// Here a warp takes R consecutive output rows at a time — lane b loads group b of each of them, with the next R rows'
-// loads issued before the current ones are used — so 2R loads are in flight per lane.  Same arithmetic per row as the
-// persistent kernel (acc = fma((xs*sw)/16, (float)(16*D), 0) in lane b, then the shfl_down tree): identical bits.
-template <int R, typename ST>
+// ---- short rows (K <= 2048: NG = one or two groups per lane), one activation row, optional expert grouping --------
+// On rows this short the persistent kernel above keeps only two batches of 16-byte loads per lane in flight and spends
+// most of its instructions on its item bookkeeping (194 warp instructions per 64-group row of the expert gate|up
+// projection, 2.3 TB/s on the 768-wide down projection).  Here a warp takes R consecutive output rows at a time — lane l
+// loads groups l, l + 32, ... of each of them, with the next R rows' loads issued before the current ones are used — so
+// 2 R NG loads are in flight per lane.  Same arithmetic per row as the persistent kernel (lane l chains
+// acc = fma((xs*sw)/16, (float)(16*D), acc) over its groups in ascending order from 0, then the shfl_down tree):
+// identical bits.
+template <int R, int NG, typename ST>
 __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_short_kernel(
     const int8_t *__restrict__ xq, const float *__restrict__ xs, const uint8_t *__restrict__ Wq,
     const ST *__restrict__ sw, float *__restrict__ Y, int IN, int OUT, bool w_a16, GroupedArgs ga) {
-    const int nb = IN / QBLK;                                       // <= 32
+    const int nb = IN / QBLK;                                       // <= 32 * NG
     if (ga.idx) {                                                   // blockIdx.y = slot (see the persistent kernel)
         const int slot = blockIdx.y;
         pdl_wait();   // the routing indices are written by an earlier kernel of the stream: wait before reading them
@@ -349,49 +351,66 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_short_kernel(
     // units of R rows, dealt round-robin to the warps of the grid
     const int units = (OUT + R - 1) / R;
     const int gw = blockIdx.x * GEMV_WARPS + warp, nw = gridDim.x * GEMV_WARPS;
-    const bool live = lane < nb;
-    uint4 wa[R], wb[R];
-    float sa[R], sb_[R];
-    auto load = [&](int unit, uint4 (&w)[R], float (&sc)[R]) {
+    bool live[NG];
+#pragma unroll
+    for (int g = 0; g < NG; g++) live[g] = lane + 32 * g < nb;
+    uint4 wa[R * NG], wb[R * NG];
+    float sa[R * NG], sb_[R * NG];
+    auto load = [&](int unit, uint4 (&w)[R * NG], float (&sc)[R * NG]) {
 #pragma unroll
         for (int i = 0; i < R; i++) {
             const int r = unit * R + i;
-            if (live && r < OUT) { w[i] = ldg_w16(Wq + (size_t)r * wpitch + 16 * lane, w_a16); sc[i] = load_scale(sw + (size_t)r * nb, lane); }
-            else { w[i] = make_uint4(0, 0, 0, 0); sc[i] = 0.f; }
+#pragma unroll
+            for (int g = 0; g < NG; g++) {
+                const int b = lane + 32 * g;
+                if (live[g] && r < OUT) { w[i * NG + g] = ldg_w16(Wq + (size_t)r * wpitch + 16 * b, w_a16); sc[i * NG + g] = load_scale(sw + (size_t)r * nb, b); }
+                else { w[i * NG + g] = make_uint4(0, 0, 0, 0); sc[i * NG + g] = 0.f; }
+            }
         }
     };
     pdl_launch_dependents();
     if (gw < units) load(gw, wa, sa);                               // weights only: allowed before the dependency wait
     pdl_wait();
-    // this lane's group of the activation row, split into even / odd bytes to match unpack8_x16
-    uint32_t xe[4] = {0u, 0u, 0u, 0u}, xo[4] = {0u, 0u, 0u, 0u};
-    float xsv = 0.f;
-    if (live) {
-        const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + (size_t)lane * QBLK);
-        uint32_t v[8];
+    // this lane's groups of the activation row (lane, lane + 32, ...), split into even / odd bytes to match unpack8_x16
+    uint32_t xe[NG][4], xo[NG][4];
+    float xsv[NG];
 #pragma unroll
-        for (int i = 0; i < 8; i++) v[i] = src[i];
+    for (int g = 0; g < NG; g++) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) split_even_odd(v[2 * i], v[2 * i + 1], xe[i], xo[i]);
-        xsv = xs[lane];
+        for (int i = 0; i < 4; i++) xe[g][i] = xo[g][i] = 0u;
+        xsv[g] = 0.f;
+        if (live[g]) {
+            const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + (size_t)(lane + 32 * g) * QBLK);
+            uint32_t v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = src[i];
+#pragma unroll
+            for (int i = 0; i < 4; i++) split_even_odd(v[2 * i], v[2 * i + 1], xe[g][i], xo[g][i]);
+            xsv[g] = xs[lane + 32 * g];
+        }
     }
-    auto compute = [&](int unit, const uint4 (&w)[R], const float (&sc)[R]) {
+    auto compute = [&](int unit, const uint4 (&w)[R * NG], const float (&sc)[R * NG]) {
         float acc[R];
 #pragma unroll
         for (int i = 0; i < R; i++) {
-            uint32_t e0, o0, e1, o1, e2, o2, e3, o3;
-            unpack8_x16(w[i].x, e0, o0); unpack8_x16(w[i].y, e1, o1);
-            unpack8_x16(w[i].z, e2, o2); unpack8_x16(w[i].w, e3, o3);
-            int d = __dp4a((int)xe[0], (int)e0, 0);
-            d = __dp4a((int)xo[0], (int)o0, d);
-            d = __dp4a((int)xe[1], (int)e1, d);
-            d = __dp4a((int)xo[1], (int)o1, d);
-            d = __dp4a((int)xe[2], (int)e2, d);
-            d = __dp4a((int)xo[2], (int)o2, d);
-            d = __dp4a((int)xe[3], (int)e3, d);
-            d = __dp4a((int)xo[3], (int)o3, d);                     // d = 16 * D[o,b], exact
-            const float scv = (xsv * sc[i]) * 0.0625f;              // exact 1/16
-            acc[i] = live ? fmaf(scv, (float)d, 0.f) : 0.f;
+            acc[i] = 0.f;
+#pragma unroll
+            for (int g = 0; g < NG; g++) {
+                const uint4 wv = w[i * NG + g];
+                uint32_t e0, o0, e1, o1, e2, o2, e3, o3;
+                unpack8_x16(wv.x, e0, o0); unpack8_x16(wv.y, e1, o1);
+                unpack8_x16(wv.z, e2, o2); unpack8_x16(wv.w, e3, o3);
+                int d = __dp4a((int)xe[g][0], (int)e0, 0);
+                d = __dp4a((int)xo[g][0], (int)o0, d);
+                d = __dp4a((int)xe[g][1], (int)e1, d);
+                d = __dp4a((int)xo[g][1], (int)o1, d);
+                d = __dp4a((int)xe[g][2], (int)e2, d);
+                d = __dp4a((int)xo[g][2], (int)o2, d);
+                d = __dp4a((int)xe[g][3], (int)e3, d);
+                d = __dp4a((int)xo[g][3], (int)o3, d);              // d = 16 * D[o,b], exact
+                const float scv = (xsv[g] * sc[i * NG + g]) * 0.0625f;   // exact 1/16
+                if (live[g]) acc[i] = fmaf(scv, (float)d, acc[i]);  // the persistent kernel's chain: groups lane, lane + 32, ...
+            }
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1)
@@ -535,14 +554,10 @@ inline int launch_gemv_flat24(const int8_t *xq, const float *xs, const uint8_t *
     return launch_status("gemv_w4a8_flat24");
 }
 
-template <typename ST>
-inline int launch_gemv_short(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int IN, int OUT,
-                             cudaStream_t st, const GroupedArgs &ga) {
-    // rows of exactly 24 groups, 16-byte aligned everywhere: the flat-group kernel (the tile loop indexes with int)
-    if (IN == 24 * QBLK && aligned(Wq, 16) && aligned(xq, 16) && (long)OUT * 24 < (1L << 30))
-        return launch_gemv_flat24<ST>(xq, xs, Wq, sw, Y, OUT, st, ga);
-    constexpr int R = 4;
-    auto kern = gemv_w4a8_short_kernel<R, ST>;
+template <int R, int NG, typename ST>
+inline int launch_gemv_short_rn(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int IN, int OUT,
+                                cudaStream_t st, const GroupedArgs &ga) {
+    auto kern = gemv_w4a8_short_kernel<R, NG, ST>;
     static PerDevice<int> occ_dev;
     int &occ = occ_dev.get();
     if (occ == 0) {
@@ -560,6 +575,18 @@ inline int launch_gemv_short(const int8_t *xq, const float *xs, const uint8_t *W
     return launch_status("gemv_w4a8_short");
 }
 
+// K <= 2048.  Rows of at most 32 groups take four rows per warp step; rows of 33..64 groups two rows with two groups per
+// lane (the same eight loads in flight per lane).
+template <typename ST>
+inline int launch_gemv_short(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int IN, int OUT,
+                             cudaStream_t st, const GroupedArgs &ga) {
+    // rows of exactly 24 groups, 16-byte aligned everywhere: the flat-group kernel (the tile loop indexes with int)
+    if (IN == 24 * QBLK && aligned(Wq, 16) && aligned(xq, 16) && (long)OUT * 24 < (1L << 30))
+        return launch_gemv_flat24<ST>(xq, xs, Wq, sw, Y, OUT, st, ga);
+    if (IN > 32 * QBLK) return launch_gemv_short_rn<2, 2, ST>(xq, xs, Wq, sw, Y, IN, OUT, st, ga);
+    return launch_gemv_short_rn<4, 1, ST>(xq, xs, Wq, sw, Y, IN, OUT, st, ga);
+}
+
 // Grouped experts: one launch, grid.y = slots, each slot one activation row against its expert.
 inline int launch_moe_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, const int32_t *idx,
                            float *Y, int nslots, int topk, int x_per_slot, int N, int K, int num_experts,
@@ -570,7 +597,7 @@ inline int launch_moe_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq,
     ga.idx = idx; ga.topk = topk; ga.x_per_slot = x_per_slot; ga.num_experts = num_experts; ga.nslots = nslots;
     ga.expert_base = expert_base;
     ga.shard_world = shard_world < 1 ? 1 : shard_world;
-    if (K <= 32 * QBLK) {                                           // short rows: the R-rows-per-warp kernel
+    if (K <= 64 * QBLK) {                                           // short rows: the R-rows-per-warp kernels
         if (scale_dtype == 1) return launch_gemv_short<__half>(xq, xs, Wq, (const __half *)sw, Y, K, N, st, ga);
         return launch_gemv_short<float>(xq, xs, Wq, (const float *)sw, Y, K, N, st, ga);
     }
