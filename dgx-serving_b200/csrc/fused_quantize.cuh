@@ -34,6 +34,27 @@ __device__ __forceinline__ void quantize_store_vec4(float4 v, long i, bool live,
     }
 }
 
+// The same for a row that stays in shared memory (the prologue of a GEMV that quantizes its own activation row): word i
+// of the row -> xrow[i], the scale of block i / 8 -> xs_row[i / 8]; g_xq / g_xs (null: skipped) receive the same values.
+__device__ __forceinline__ void quantize_row_vec4(float4 v, int i, bool live, uint32_t *xrow, float *xs_row,
+                                                  uint32_t *__restrict__ g_xq, float *__restrict__ g_xs) {
+    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    const float d = amax / 127.0f;
+    int sum = 0;
+    const uint32_t packed = amax != 0.0f ? quantize4_pack(v, d, sum) : 0u;
+    if (live) {
+        xrow[i] = packed;
+        if (g_xq) g_xq[i] = packed;
+        if ((i & 7) == 0) {
+            xs_row[i >> 3] = d;
+            if (g_xs) g_xs[i >> 3] = d;
+        }
+    }
+}
+
 // VARIANT 0: y = x * inv * W (launch_rmsnorm); 1: y = x * inv * (1 + W) (launch_rmsnorm_zc); 2: y = x * inv
 // (launch_rmsnorm_noscale).  One CTA of 256 threads per row, as in the reference (the reduction order depends on it).
 template <int VARIANT>

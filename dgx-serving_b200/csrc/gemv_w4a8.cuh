@@ -16,6 +16,7 @@
 // tests compare families with max|d|/rms < 1e-5, tests/test_gemm_mmq.cu:28.)
 #pragma once
 #include "common.cuh"
+#include "fused_quantize.cuh"
 #include "peer_allgather.cuh"
 
 namespace w4a8 {
@@ -31,6 +32,14 @@ struct GroupedArgs {
     int topk = 1, x_per_slot = 0, num_experts = 0, nslots = 1;
     int expert_base = 0;   // experts [expert_base, expert_base + num_experts) live in this Wq / sw (an expert shard)
     int shard_world = 1;   // expert shard: about 1 / shard_world of the slots are this rank's, the other slots' CTAs exit at once
+    // Short-row kernels only: the slot's activation row is produced in the kernel's prologue instead of being read from
+    // xq / xs.  1: quantize_x of row slot / topk of src_f32 [tokens][IN]; 2: activation (act 0 SwiGLU, 1 GeGLU) of row slot
+    // of src_f32 [nslots][2 IN] (gate | up), then quantize_x.  The first CTA of every slot also stores the row to
+    // xq_out / xs_out (row slot / topk resp. slot), so the stage can still be read back.
+    int src_mode = 0, act = 0;
+    const float *src_f32 = nullptr;
+    int8_t *xq_out = nullptr;
+    float *xs_out = nullptr;
 };
 
 __device__ __forceinline__ uint4 ldg_w16(const uint8_t *p, bool a16) {
@@ -334,12 +343,15 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_short_kernel(
     const int8_t *__restrict__ xq, const float *__restrict__ xs, const uint8_t *__restrict__ Wq,
     const ST *__restrict__ sw, float *__restrict__ Y, int IN, int OUT, bool w_a16, GroupedArgs ga) {
     const int nb = IN / QBLK;                                       // <= 32 * NG
+    __shared__ __align__(16) uint32_t xrow_s[NG * 32 * 8];          // src_mode 1: the quantized activation row
+    __shared__ float xs_s[NG * 32];
+    int row = 0;
     if (ga.idx) {                                                   // blockIdx.y = slot (see the persistent kernel)
         const int slot = blockIdx.y;
         pdl_wait();   // the routing indices are written by an earlier kernel of the stream: wait before reading them
         const int e = ga.idx[slot] - ga.expert_base;
         if (e < 0 || e >= ga.num_experts) return;
-        const int row = ga.x_per_slot ? slot : slot / ga.topk;
+        row = ga.x_per_slot ? slot : slot / ga.topk;
         xq += (size_t)row * IN;
         xs += (size_t)row * nb;
         Wq += (size_t)e * ((size_t)OUT * (IN / 2));
@@ -348,6 +360,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_short_kernel(
     }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t wpitch = (size_t)(IN / 2);
+    const bool fused = ga.src_mode == 1;
     // units of R rows, dealt round-robin to the warps of the grid
     const int units = (OUT + R - 1) / R;
     const int gw = blockIdx.x * GEMV_WARPS + warp, nw = gridDim.x * GEMV_WARPS;
@@ -371,6 +384,20 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_short_kernel(
     pdl_launch_dependents();
     if (gw < units) load(gw, wa, sa);                               // weights only: allowed before the dependency wait
     pdl_wait();
+    if (fused) {
+        // quantize_x of the token's row, every CTA of the slot for itself (IN <= 2048 floats out of L2); the values and
+        // their order are quantize_x_q8_vec_kernel's
+        const float4 *xr = reinterpret_cast<const float4 *>(ga.src_f32 + (size_t)row * IN);
+        uint32_t *gq = blockIdx.x == 0 ? reinterpret_cast<uint32_t *>(ga.xq_out + (size_t)row * IN) : nullptr;
+        float *gs = blockIdx.x == 0 ? ga.xs_out + (size_t)row * nb : nullptr;
+        const int nvec = IN / 4;
+        for (int i = tid; i - lane < nvec; i += GEMV_WARPS * 32) {
+            const bool lv = i < nvec;
+            const float4 v = lv ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            quantize_row_vec4(v, i, lv, xrow_s, xs_s, gq, gs);
+        }
+        __syncthreads();
+    }
     // this lane's groups of the activation row (lane, lane + 32, ...), split into even / odd bytes to match unpack8_x16
     uint32_t xe[NG][4], xo[NG][4];
     float xsv[NG];
@@ -380,13 +407,20 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_short_kernel(
         for (int i = 0; i < 4; i++) xe[g][i] = xo[g][i] = 0u;
         xsv[g] = 0.f;
         if (live[g]) {
-            const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + (size_t)(lane + 32 * g) * QBLK);
             uint32_t v[8];
+            if (fused) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(xrow_s + (lane + 32 * g) * 8);
+                const uint4 v0 = src[0], v1 = src[1];
+                v[0] = v0.x; v[1] = v0.y; v[2] = v0.z; v[3] = v0.w; v[4] = v1.x; v[5] = v1.y; v[6] = v1.z; v[7] = v1.w;
+                xsv[g] = xs_s[lane + 32 * g];
+            } else {
+                const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + (size_t)(lane + 32 * g) * QBLK);
 #pragma unroll
-            for (int i = 0; i < 8; i++) v[i] = src[i];
+                for (int i = 0; i < 8; i++) v[i] = src[i];
+                xsv[g] = xs[lane + 32 * g];
+            }
 #pragma unroll
             for (int i = 0; i < 4; i++) split_even_odd(v[2 * i], v[2 * i + 1], xe[g][i], xo[g][i]);
-            xsv[g] = xs[lane + 32 * g];
         }
     }
     auto compute = [&](int unit, const uint4 (&w)[R * NG], const float (&sc)[R * NG]) {
@@ -445,8 +479,10 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_flat24_kernel(
     const ST *__restrict__ sw, float *__restrict__ Y, int OUT, GroupedArgs ga) {
     constexpr int NB = 24, TR = 4, TL = 3;                          // groups per row, rows and loads per tile
     __shared__ float part[GEMV_WARPS][2][TR * NB];
+    __shared__ __align__(16) uint32_t xrow_s[NB * 8];               // src_mode 2: the quantized activation row
+    __shared__ float xs_s[NB];
+    const int slot = blockIdx.y;
     if (ga.idx) {                                                   // blockIdx.y = slot (see the persistent kernel)
-        const int slot = blockIdx.y;
         pdl_wait();   // the routing indices are written by an earlier kernel of the stream: wait before reading them
         const int e = ga.idx[slot] - ga.expert_base;
         if (e < 0 || e >= ga.num_experts) return;
@@ -473,13 +509,30 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_flat24_kernel(
     pdl_launch_dependents();
     if (gw < tiles) load(gw, wa, sa);                               // weights only: allowed before the dependency wait
     pdl_wait();
+    const bool fused = ga.src_mode == 2;
+    if (fused) {
+        // activation of the slot's gate | up row and quantize_x of the result, every CTA of the slot for itself (1536 floats
+        // out of L2); the values and their order are glu_quantize_kernel's
+        const float4 *G = reinterpret_cast<const float4 *>(ga.src_f32 + (size_t)slot * (2 * NB * QBLK)), *U = G + NB * 8;
+        uint32_t *gq = blockIdx.x == 0 ? reinterpret_cast<uint32_t *>(ga.xq_out + (size_t)slot * (NB * QBLK)) : nullptr;
+        float *gs = blockIdx.x == 0 ? ga.xs_out + (size_t)slot * NB : nullptr;
+        const bool lv = tid < NB * 8;
+        float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (lv) {
+            const float4 g = G[tid], u = U[tid];
+            if (ga.act == 0) y = make_float4(glu_value<0>(g.x, u.x), glu_value<0>(g.y, u.y), glu_value<0>(g.z, u.z), glu_value<0>(g.w, u.w));
+            else y = make_float4(glu_value<1>(g.x, u.x), glu_value<1>(g.y, u.y), glu_value<1>(g.z, u.z), glu_value<1>(g.w, u.w));
+        }
+        quantize_row_vec4(y, tid, lv, xrow_s, xs_s, gq, gs);
+        __syncthreads();
+    }
     // the three activation groups a lane meets (the pattern repeats every tile), split into even / odd bytes and kept
     // in shared memory as two planes of 16-byte words indexed [j][lane] (conflict-free); warp j fills plane set j
     __shared__ uint4 xpat[TL][2][32];
     __shared__ float xspat[TL][32];
     if (warp < TL) {
         const int b = (32 * warp + lane) % NB;
-        const uint4 *src = reinterpret_cast<const uint4 *>(xq + (size_t)b * QBLK);
+        const uint4 *src = fused ? reinterpret_cast<const uint4 *>(xrow_s + b * 8) : reinterpret_cast<const uint4 *>(xq + (size_t)b * QBLK);
         const uint4 v0 = src[0], v1 = src[1];
         uint4 p0, p1;
         split_even_odd(v0.x, v0.y, p0.x, p0.y);
@@ -488,7 +541,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_flat24_kernel(
         split_even_odd(v1.z, v1.w, p1.z, p1.w);
         xpat[warp][0][lane] = p0;
         xpat[warp][1][lane] = p1;
-        xspat[warp][lane] = xs[b];
+        xspat[warp][lane] = fused ? xs_s[b] : xs[b];
     }
     __syncthreads();
     int parity = 0;
@@ -581,19 +634,23 @@ template <typename ST>
 inline int launch_gemv_short(const int8_t *xq, const float *xs, const uint8_t *Wq, const ST *sw, float *Y, int IN, int OUT,
                              cudaStream_t st, const GroupedArgs &ga) {
     // rows of exactly 24 groups, 16-byte aligned everywhere: the flat-group kernel (the tile loop indexes with int)
-    if (IN == 24 * QBLK && aligned(Wq, 16) && aligned(xq, 16) && (long)OUT * 24 < (1L << 30))
+    if (ga.src_mode != 1 && IN == 24 * QBLK && aligned(Wq, 16) && aligned(xq, 16) && (long)OUT * 24 < (1L << 30))
         return launch_gemv_flat24<ST>(xq, xs, Wq, sw, Y, OUT, st, ga);
+    if (ga.src_mode == 2) return fail(W4A8_ERR_UNSUPPORTED, "gemv_short: the fused activation prologue needs rows of 24 groups");
     if (IN > 32 * QBLK) return launch_gemv_short_rn<2, 2, ST>(xq, xs, Wq, sw, Y, IN, OUT, st, ga);
     return launch_gemv_short_rn<4, 1, ST>(xq, xs, Wq, sw, Y, IN, OUT, st, ga);
 }
 
-// Grouped experts: one launch, grid.y = slots, each slot one activation row against its expert.
+// Grouped experts: one launch, grid.y = slots, each slot one activation row against its expert.  fused (optional): the
+// src_mode / act / src_f32 / xq_out / xs_out fields of a GroupedArgs, for K <= 2048 only (see the struct).
 inline int launch_moe_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const void *sw, const int32_t *idx,
                            float *Y, int nslots, int topk, int x_per_slot, int N, int K, int num_experts,
-                           int scale_dtype, cudaStream_t st, int expert_base = 0, int shard_world = 1) {
+                           int scale_dtype, cudaStream_t st, int expert_base = 0, int shard_world = 1,
+                           const GroupedArgs *fused = nullptr) {
     if (nslots == 0 || N == 0) return W4A8_OK;
     if (nslots > 65535) return fail(W4A8_ERR_UNSUPPORTED, "moe_gemv: at most 65535 slots per launch (got %d)", nslots);
     GroupedArgs ga;
+    if (fused) ga = *fused;
     ga.idx = idx; ga.topk = topk; ga.x_per_slot = x_per_slot; ga.num_experts = num_experts; ga.nslots = nslots;
     ga.expert_base = expert_base;
     ga.shard_world = shard_world < 1 ? 1 : shard_world;
@@ -601,6 +658,7 @@ inline int launch_moe_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq,
         if (scale_dtype == 1) return launch_gemv_short<__half>(xq, xs, Wq, (const __half *)sw, Y, K, N, st, ga);
         return launch_gemv_short<float>(xq, xs, Wq, (const float *)sw, Y, K, N, st, ga);
     }
+    if (ga.src_mode != 0) return fail(W4A8_ERR_UNSUPPORTED, "moe_gemv: fused prologues need K <= 2048");
     if (scale_dtype == 1) return launch_gemv_dp4a_u<1, __half>(xq, xs, Wq, (const __half *)sw, Y, K, N, 1, st, ga);
     return launch_gemv_dp4a_u<1, float>(xq, xs, Wq, (const float *)sw, Y, K, N, 1, st, ga);
 }

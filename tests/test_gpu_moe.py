@@ -115,6 +115,8 @@ def check_stages(oracle, case, lay, ws, out, S, topk, E, H, MI, gemm, act=0):
     (37, 3, 5, 256, 96, 1, 1),          # fp16 scales, GEMV path
     (300, 3, 3, 128, 64, 2, 1),         # every expert gets 300 rows: five tiles per expert, fp16 scales
     (5, 2, 7, 160, 32, 0, 0),           # auto
+    (5, 2, 7, 256, 768, 1, 1),          # MI = 768 on the GEMV path: both activation rows produced inside the GEMVs (H <= 1024), fp16 scales
+    (3, 4, 6, 1536, 768, 0, 0),         # the same with two groups per lane in gate|up
     (40, 2, 300, 64, 32, 2, 0),         # more experts than the sort kernel's per-warp histograms hold
 ])
 def test_moe_block_stages(w4a8, oracle, cuda, S, topk, E, H, MI, kernel, sd):
@@ -144,6 +146,14 @@ def test_moe_block_geglu_and_unused_experts(w4a8, oracle, cuda):
     case[5] = np.stack([rng.permutation(6)[:topk] * 9 for _ in range(S)]).astype(np.int32).reshape(-1)   # experts 0, 9, ..., 45 only
     lay, ws, out = run_block(w4a8, cuda, case, S, topk, E, H, MI, 2, act=1)
     check_stages(oracle, case, lay, ws, out, S, topk, E, H, MI, True, act=1)
+
+
+def test_moe_block_geglu_inside_the_down_gemv(w4a8, oracle, cuda):
+    """act = 1 on the decode path whose down GEMV computes the activation in its prologue (MI = 768, H <= 2048)."""
+    S, topk, E, H, MI = 6, 2, 8, 512, 768
+    case = make_block(oracle, S, topk, E, H, MI, seed=78)
+    lay, ws, out = run_block(w4a8, cuda, case, S, topk, E, H, MI, 1, act=1)
+    check_stages(oracle, case, lay, ws, out, S, topk, E, H, MI, False, act=1)
 
 
 def test_moe_gemv_idx_written_on_the_stream(w4a8, oracle, cuda):
