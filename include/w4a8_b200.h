@@ -220,7 +220,10 @@ int w4a8_moe_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, const vo
  * gu_wq / gu_sc: flat [E][2*MI][H/2] bytes and [E][2*MI][H/32] scales; dn_wq / dn_sc: [E][H][MI/2], [E][H][MI/32]
  * (runtime/weights_qwen.cu:62-63).  idx (global expert ids) and dw (router weights) are device arrays of S*topk
  * entries written by earlier work of the stream; every id must name an existing expert.
- * Up to 128 slots run as one grouped GEMV launch per projection; above that the slots are sorted by expert on the
+ * Up to 128 slots run as one grouped GEMV launch per projection (with H <= 2048 and MI = 768 those two launches also
+ * produce their own activation rows — quantize_x of the token, activation + quantize_x of the slot's gate|up row — and
+ * store them to the same xq / xs / xq_h / xs_h stages; on an expert shard the stage rows of tokens and slots whose
+ * experts all live on other ranks stay unwritten); above that the slots are sorted by expert on the
  * device and both projections run as grouped tensor-core GEMMs whose work units are (expert, up to 64 of its
  * rows) x 128 outputs (w4a8_config("moe_kernel", 1 | 2) forces one).  Nothing is allocated: the intermediates live
  * in the caller's workspace at the offsets w4a8_moe_layout_for reports (256-byte aligned device memory of
