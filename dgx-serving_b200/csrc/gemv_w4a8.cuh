@@ -22,6 +22,8 @@
 namespace w4a8 {
 
 constexpr int GEMV_WARPS = 8;      // warps (= output rows) per CTA
+constexpr int SHORT_WARPS = 4;     // warps per CTA of the short-row kernel: at about 78 registers six such CTAs fit an SM, and a
+                                   // grouped launch's CTAs-per-slot then fill 94 % of a wave (three 8-warp CTAs: 86 %)
 constexpr int GEMV_MT_MAX = 4;     // activation rows handled per pass of the dp4a kernel
 
 // Grouped-expert addressing (idx == nullptr: plain dense GEMV).  Expert e's weights start
@@ -339,7 +341,7 @@ inline int launch_gemv(const int8_t *xq, const float *xs, const uint8_t *Wq, con
 // acc = fma((xs*sw)/16, (float)(16*D), acc) over its groups in ascending order from 0, then the shfl_down tree):
 // identical bits.
 template <int R, int NG, typename ST>
-__global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_short_kernel(
+__global__ void __launch_bounds__(SHORT_WARPS * 32) gemv_w4a8_short_kernel(
     const int8_t *__restrict__ xq, const float *__restrict__ xs, const uint8_t *__restrict__ Wq,
     const ST *__restrict__ sw, float *__restrict__ Y, int IN, int OUT, bool w_a16, GroupedArgs ga) {
     const int nb = IN / QBLK;                                       // <= 32 * NG
@@ -363,7 +365,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_short_kernel(
     const bool fused = ga.src_mode == 1;
     // units of R rows, dealt round-robin to the warps of the grid
     const int units = (OUT + R - 1) / R;
-    const int gw = blockIdx.x * GEMV_WARPS + warp, nw = gridDim.x * GEMV_WARPS;
+    const int gw = blockIdx.x * SHORT_WARPS + warp, nw = gridDim.x * SHORT_WARPS;
     bool live[NG];
 #pragma unroll
     for (int g = 0; g < NG; g++) live[g] = lane + 32 * g < nb;
@@ -391,7 +393,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_w4a8_short_kernel(
         uint32_t *gq = blockIdx.x == 0 ? reinterpret_cast<uint32_t *>(ga.xq_out + (size_t)row * IN) : nullptr;
         float *gs = blockIdx.x == 0 ? ga.xs_out + (size_t)row * nb : nullptr;
         const int nvec = IN / 4;
-        for (int i = tid; i - lane < nvec; i += GEMV_WARPS * 32) {
+        for (int i = tid; i - lane < nvec; i += SHORT_WARPS * 32) {
             const bool lv = i < nvec;
             const float4 v = lv ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
             quantize_row_vec4(v, i, lv, xrow_s, xs_s, gq, gs);
@@ -615,15 +617,15 @@ inline int launch_gemv_short_rn(const int8_t *xq, const float *xs, const uint8_t
     int &occ = occ_dev.get();
     if (occ == 0) {
         int n = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, GEMV_WARPS * 32, 0);
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, SHORT_WARPS * 32, 0);
         if (e != cudaSuccess) return cuda_fail(e, "gemv_short occupancy query");
         occ = n > 0 ? n : 1;
     }
     const long units = (OUT + R - 1) / R;
-    long want = (units + GEMV_WARPS - 1) / GEMV_WARPS, cap = (long)sm_count() * occ;
+    long want = (units + SHORT_WARPS - 1) / SHORT_WARPS, cap = (long)sm_count() * occ;
     if (ga.idx) cap = cap * ga.shard_world / ga.nslots > 1 ? cap * ga.shard_world / ga.nslots : 1;   // CTAs per slot
     const dim3 grid((unsigned)(want < cap ? want : cap), (unsigned)(ga.idx ? ga.nslots : 1));
-    cudaError_t le = launch_pdl(kern, grid, dim3(GEMV_WARPS * 32), 0, st, xq, xs, Wq, sw, Y, IN, OUT, aligned(Wq, 16), ga);
+    cudaError_t le = launch_pdl(kern, grid, dim3(SHORT_WARPS * 32), 0, st, xq, xs, Wq, sw, Y, IN, OUT, aligned(Wq, 16), ga);
     if (le != cudaSuccess) return cuda_fail(le, "gemv_w4a8_short launch");
     return launch_status("gemv_w4a8_short");
 }
